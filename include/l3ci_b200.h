@@ -1,0 +1,151 @@
+/*
+ * l3ci_b200.h — C ABI of the sm_100a decode kernels (libl3ci_b200.so).
+ *
+ * Plain pointers and sizes only: no torch types cross this boundary.  Every
+ * pointer is a DEVICE pointer on the device that is current for the calling
+ * thread unless the comment says "host".  All tensors are bf16 (2-byte,
+ * round-to-nearest-even) unless stated; strides are in ELEMENTS, not bytes.
+ * Every call is asynchronous on `stream` and returns an l3ci_status.
+ *
+ * Each entry point names the reference interface it replaces
+ * (paths are relative to the reference project root).
+ */
+#ifndef L3CI_B200_H_
+#define L3CI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define L3CI_API __attribute__((visibility("default")))
+#else
+#define L3CI_API
+#endif
+
+/* Same object as cudaStream_t / CUstream; 0 is the legacy default stream. */
+typedef struct CUstream_st* l3ci_stream_t;
+
+typedef enum l3ci_status {
+  L3CI_OK = 0,
+  L3CI_ERR_INVALID = 1,      /* null pointer, non-positive size, heads not divisible ...   */
+  L3CI_ERR_UNSUPPORTED = 2,  /* head size not 64/128, or q/kv head ratio outside 1..16      */
+  L3CI_ERR_ALIGNMENT = 3,    /* a row does not start on 16 bytes / stride not 8-element      */
+  L3CI_ERR_SCRATCH = 4,      /* scratch buffer smaller than l3ci_flash_decode_scratch_bytes  */
+  L3CI_ERR_CUDA = 5,         /* a CUDA runtime/driver call failed; see l3ci_last_error()     */
+  L3CI_ERR_DEVICE_WAIT = 6   /* a bounded device-side wait ran out (read back by _poll)      */
+} l3ci_status;
+
+/* Static description of a status code. */
+L3CI_API const char* l3ci_status_string(int status);
+/* Thread-local detail text of the last failing call on this thread ("" if none). */
+L3CI_API const char* l3ci_last_error(void);
+/* Library version, "major.minor.patch". */
+L3CI_API const char* l3ci_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * RMSNorm.   out[r, :] = bf16( (float(x[r, :]) * rsqrt(mean(x[r, :]^2) + eps)) * float(w) )
+ * fp32 arithmetic, one rounding.  Replaces `rms_norm(input, weight, eps)` and
+ * `custom_rms_norm_kernel` (custom_kernels/custom_kernels.cu:340-389, bound at
+ * custom_kernels/main.cpp:7; caller model.py:70-72).  `rows` is B*S of the reference's
+ * [B, S, E] input.  Rows must start on 16 bytes and `embed` be a multiple of 8.
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API int l3ci_rms_norm(const void* x, const void* weight, void* out,
+                           int64_t rows, int64_t embed,
+                           int64_t x_row_stride, int64_t out_row_stride,
+                           float eps, l3ci_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Rotary embedding, interleaved-pair (Meta) convention:
+ *   (x', y') = (x*c - y*s, x*s + y*c) for (x, y) = in[.., 2i], in[.., 2i+1] and
+ *   (c, s) = freq[tok*D + 2i], freq[tok*D + 2i + 1]; fp32, products rounded separately,
+ *   one rounding to bf16.
+ * `x` is [B, S, H, D] with element strides (sb, ss, sh, 1); `freq` is fp32 [S, D];
+ * `out` is dense [B, S, H, D].  Replaces `rot_embed(input, freq)` and
+ * `custom_rot_embed_kernel` (custom_kernels/custom_kernels.cu:391-442, bound at
+ * custom_kernels/main.cpp:8; callers model.py:100-101).
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API int l3ci_rot_embed(const void* x, const float* freq, void* out,
+                            int64_t B, int64_t S, int64_t H, int64_t D,
+                            int64_t sb, int64_t ss, int64_t sh,
+                            l3ci_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Rotary embedding fused with the KV-cache write: one pass over the fused projection output
+ * qkv[B, T, (Hq + 2*Hkv) * D] (q heads, then k heads, then v heads along the last axis):
+ *   q_out[b, t, h, :]                 = rope(q)       dense [B, T, Hq, D]
+ *   cache_k[b, start_pos + t, h, :]   = rope(k)
+ *   cache_v[b, start_pos + t, h, :]   = v
+ * Replaces the two `rot_embed` calls plus the two cache copies of
+ * CausalSelfAttention.forward (model.py:100-108).  `freq` is already sliced to the T
+ * positions of this step, as model.py:209 does.  Caches are [maxB, maxLen, Hkv, D] with
+ * element strides (cache_sb, cache_st, D, 1).
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void* q_out,
+                                     void* cache_k, void* cache_v,
+                                     int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                                     int64_t qkv_sb, int64_t qkv_st,
+                                     int64_t cache_sb, int64_t cache_st,
+                                     int64_t start_pos, l3ci_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Split-KV flash-decode attention for one query token per sequence over a GQA KV cache.
+ * Replaces `flash_attention_decode(query, keys, values)` with its split-KV and combine
+ * kernels (custom_kernels/custom_kernels.cu:13-177, 179-223, 233-338, bound at
+ * custom_kernels/main.cpp:6; caller model.py:118, benchmark_kernel.py:25).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct l3ci_flash_decode_args {
+  const void* q;         /* [B, Hq, 1, D], element strides (q_sb, q_sh, -, 1)                  */
+  const void* k;         /* [B, Hkv, n_seq, D], element strides (k_sb, k_sh, k_st, 1)          */
+  const void* v;         /* [B, Hkv, n_seq, D], element strides (v_sb, v_sh, v_st, 1)          */
+  void* out;             /* bf16 [B, Hq, 1, D], element strides (o_sb, o_sh, -, 1); may be NULL
+                            when o_partial/lse are given                                       */
+  float* o_partial;      /* optional fp32 [B, Hq, D] dense: softmax-normalised output of THIS
+                            KV range, for a later l3ci_lse_merge across KV shards             */
+  float* lse;            /* optional fp32 [B, Hq]: natural-log sum-exp of the scaled scores of
+                            this KV range (-inf for an empty range); required with o_partial  */
+  const int32_t* seq_lens; /* optional int32 [B]: valid tokens per sequence (clamped to
+                            [0, n_seq]); NULL = every sequence has n_seq tokens               */
+  void* scratch;         /* >= l3ci_flash_decode_scratch_bytes(...) bytes, 256-byte aligned,
+                            zero-filled ONCE before its first use; the kernel leaves it ready
+                            for the next call on the same stream                              */
+  size_t scratch_bytes;
+  int32_t B, Hq, Hkv, D, n_seq;
+  int64_t q_sb, q_sh;
+  int64_t k_sb, k_sh, k_st;
+  int64_t v_sb, v_sh, v_st;
+  int64_t o_sb, o_sh;
+  float scale;           /* softmax scale; <= 0 selects 1/sqrt(D) (custom_kernels.cu:253)      */
+  int32_t max_ctas;      /* 0 = fill the device; >0 caps the persistent grid (tests, tuning)   */
+  l3ci_stream_t stream;
+} l3ci_flash_decode_args;
+
+/* Bytes of scratch one call needs on the current device (depends on its SM count). */
+L3CI_API size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D);
+
+L3CI_API int l3ci_flash_decode(const l3ci_flash_decode_args* args);
+
+/* Reads back (synchronising `stream`) the device-side status word kept in `scratch`:
+ * L3CI_OK, or L3CI_ERR_DEVICE_WAIT if a bounded wait on a bulk copy ran out in an earlier
+ * call.  Clears the word and the arrival counters so the scratch can be used again. */
+L3CI_API int l3ci_flash_decode_poll(void* scratch, size_t scratch_bytes, l3ci_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Log-sum-exp merge of `parts` partial results of the same queries over disjoint KV ranges
+ * (the per-GPU results of a sequence-sharded cache):
+ *   L = logsumexp_p lse[p, r];  out[r, :] = bf16( sum_p exp(lse[p, r] - L) * o[p, r, :] )
+ * o is fp32 [parts, rows, D] dense, lse fp32 [parts, rows], rows = B*Hq; out is bf16 with
+ * element strides (o_sb, o_sh) over (b, h).  Does for GPU shards what the reference's combine
+ * kernel intends for its 64-token steps (custom_kernels/custom_kernels.cu:179-223).
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API int l3ci_lse_merge(const float* o, const float* lse, void* out,
+                            int32_t parts, int32_t B, int32_t Hq, int32_t D,
+                            int64_t o_sb, int64_t o_sh, l3ci_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* L3CI_B200_H_ */

@@ -1,0 +1,749 @@
+// Split-KV flash-decode attention for sm_100a: one query token per sequence against a bf16
+// GQA KV cache, head size 64 or 128, one launch per call.
+//
+// Replaces flash_attention_decode with its split-KV and combine kernels
+// (custom_kernels/custom_kernels.cu:13-177, 179-223, 233-338).  What is kept from the
+// reference: every K/V byte is read from HBM once per KV head and shared by the R query heads
+// of the group, fp32 softmax statistics, and a log-sum-exp combine of partial results.
+// What is different:
+//
+//  * Persistent grid.  The work is the list of "columns" (sequence b, head group g, tile j of
+//    kTile tokens); a column covers the same tokens for HG = gcd(Hkv, 8) neighbouring KV heads.
+//    The list is cut into gridDim.x equal contiguous ranges, so every SM streams the same number
+//    of bytes whatever the sequence lengths are.  A CTA has HG warps; warp w owns KV head
+//    g*HG + w of every column, so a CTA walks HG*D*2 contiguous bytes per token.
+//  * Each warp runs its own kStages-deep pipeline of TMA tile loads (cp.async.bulk.tensor, 128-byte
+//    swizzle) signalled through its own mbarriers: no CTA-wide barrier in the loop.
+//  * Q.K^T and P.V run on tensor cores (mma.sync m16n8k16 bf16, the R <= 16 query heads of the
+//    group padded to the 16-row A tile), which leaves the issue slots to the memory pipeline.
+//    Online softmax statistics live in registers; row reductions are 4-lane shuffles.
+//  * A (sequence, head) unit that is cut by a range boundary leaves an fp32 (m, l, o) record per
+//    CTA; the warp that arrives last (one atomic counter per unit) merges the records and writes
+//    the result.  The counter is reset by that warp, so scratch stays ready for the next call.
+//  * Every wait on an mbarrier is bounded; if it runs out the warp records L3CI_ERR_DEVICE_WAIT in
+//    the scratch header and leaves.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "bf16x8.cuh"
+#include "flash_decode_plan.h"
+#include "host_common.h"
+#include "warp_reduce.cuh"
+
+namespace l3ci {
+namespace {
+
+constexpr int kStages = 3;            // tiles in flight per warp
+constexpr int kStageBytes = 8192;     // K tile + V tile of one stage
+constexpr int kHeaderBytes = 256;     // scratch header: status word
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bound of one mbarrier wait
+
+template <int D>
+struct FdCfg {
+  static_assert(D == 64 || D == 128, "head size");
+  static constexpr int kTile = fd_tile_tokens(D);         // tokens per tile
+  static constexpr int kHalves = D / 64;                  // 128-byte column blocks per row
+  static constexpr int kBoxBytes = kTile * 128;           // one TMA box: kTile rows of 128 bytes
+  static constexpr int kKBytes = kHalves * kBoxBytes;     // K part of a stage
+  static_assert(2 * kKBytes == kStageBytes, "stage size");
+  static constexpr int KS = D / 16;        // k-steps of Q.K^T
+  static constexpr int NT_S = kTile / 8;   // 8-token score tiles
+  static constexpr int NT_O = D / 8;       // 8-column output tiles
+  static constexpr int KS_PV = kTile / 16; // k-steps of P.V
+};
+
+struct FdParams {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;   // may be null
+  float* o_partial;     // may be null
+  float* lse;           // may be null
+  const int* seq_lens;  // may be null
+  float* records;       // scratch: per-CTA (m, l, o) records
+  int* counters;        // scratch: one arrival counter per (b, kv head)
+  int* status;          // scratch header
+  int B, Hq, Hkv, R, n_seq, n_groups;
+  long long q_sb, q_sh, o_sb, o_sh;
+  float scale_log2e;
+  int rec_floats;       // floats per record = R * (D + 2)
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity, at most kWaitLimitNs.  Warp-uniform result.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  bool ok = mbar_try_wait(bar, parity);
+  if (!__all_sync(kFullMask, ok)) {
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 0;; ++it) {
+      ok = mbar_try_wait(bar, parity);
+      if (__all_sync(kFullMask, ok)) break;
+      if ((it & 63u) == 63u) {
+        const bool late = global_ns() - t0 > kWaitLimitNs;
+        if (__any_sync(kFullMask, late)) return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+// One tile (box) of a rank-4 tensor map into shared memory; completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+      "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+// c += a(16x16, row) * b(16x8, col), bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t ld_global_u32(const __nv_bfloat16* p) {
+  return __ldg(reinterpret_cast<const uint32_t*>(p));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel.  blockDim.x = 32 * HG; dynamic shared memory (1024-byte aligned by hand):
+//   [HG][kStages][kStageBytes] tiles | [HG][kStages] mbarriers | prefix[B+1] | len[B]
+// ---------------------------------------------------------------------------------------------
+template <int D, bool RHI>
+__global__ void __launch_bounds__(256, 1)
+flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                    const FdParams p) {
+  using C = FdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int HG = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int gid = lane >> 2;  // MMA row within the 8-row half
+  const int tig = lane & 3;   // MMA column pair
+
+  uint8_t* stages = smem + warp * (kStages * kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + HG * (kStages * kStageBytes)) + warp * kStages;
+  int* s_pref = reinterpret_cast<int*>(smem + HG * (kStages * kStageBytes) + HG * kStages * 8);
+  int* s_len = s_pref + (p.B + 1);
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&vmap)) : "memory");
+  }
+  __syncwarp();
+
+  // ---- column prefix over sequences (only when lengths differ) ----
+  FdWalker wk;
+  wk.B = p.B; wk.n_groups = p.n_groups; wk.n_seq = p.n_seq; wk.tile = C::kTile;
+  wk.pref = nullptr; wk.lens = nullptr;
+  int total;
+  if (p.seq_lens) {
+    for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
+      const int len = min(max(__ldg(p.seq_lens + b), 0), p.n_seq);
+      s_len[b] = len;
+      s_pref[b + 1] = p.n_groups * fd_tiles(len, C::kTile);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const int chunk = (p.B + 31) >> 5;
+      const int beg = min(lane * chunk, p.B), end = min(beg + chunk, p.B);
+      int sum = 0;
+      for (int b = beg; b < end; ++b) sum += s_pref[b + 1];
+      int incl = sum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(kFullMask, incl, d);
+        if (lane >= d) incl += n;
+      }
+      int run = incl - sum;
+      for (int b = beg; b < end; ++b) {
+        run += s_pref[b + 1];
+        s_pref[b + 1] = run;
+      }
+      if (lane == 0) s_pref[0] = 0;
+    }
+    __syncthreads();
+    wk.pref = s_pref;
+    wk.lens = s_len;
+    total = s_pref[p.B];
+  } else {
+    total = p.B * p.n_groups * fd_tiles(p.n_seq, C::kTile);
+  }
+
+  // The host sizes the grid from the padded length; with shorter sequences there may be fewer
+  // columns than CTAs.  Only the first G CTAs work, so that every working CTA owns >= 1 column.
+  const int G = fd_active_ctas((int)gridDim.x, total);
+  const int cta = blockIdx.x;
+  if (cta >= G) return;
+  const int c0 = fd_range_begin(cta, total, G);
+  const int c1 = fd_range_begin(cta + 1, total, G);
+
+  const uint64_t policy = l2_evict_first_policy();
+  const uint32_t stage0 = smem_u32(stages);
+  const uint32_t bar0 = smem_u32(bars);
+
+  // ---- producer side: lane 0 issues the loads of one column ----
+  auto issue = [&](const FdCursor& cu, int stage) {
+    const uint32_t bar = bar0 + stage * 8;
+    const uint32_t dst = stage0 + stage * kStageBytes;
+    const int tok = cu.j * C::kTile;
+    const int head = cu.g * HG + warp;
+    mbar_expect_tx(bar, kStageBytes);
+#pragma unroll
+    for (int h = 0; h < C::kHalves; ++h) tma_load_4d(dst + h * C::kBoxBytes, &kmap, bar, h * 64, tok, head, cu.b, policy);
+#pragma unroll
+    for (int h = 0; h < C::kHalves; ++h)
+      tma_load_4d(dst + C::kKBytes + h * C::kBoxBytes, &vmap, bar, h * 64, tok, head, cu.b, policy);
+  };
+
+  FdCursor prod = wk.seek(c0);
+  FdCursor cons = prod;
+  int issued = 0;
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) {
+    if (prod.col < c1) {
+      if (lane == 0) issue(prod, s);
+      wk.advance(prod);
+      ++issued;
+    }
+  }
+
+  // ---- lane constants of the ldmatrix addresses ----
+  const int mat = lane >> 3, r8 = lane & 7;
+  // K (non-transposed): matrices (tok 0-7, chunk c), (tok 0-7, c+1), (tok 8-15, c), (tok 8-15, c+1)
+  const uint32_t k_row_off = (r8 + 8 * (mat >> 1)) * 128;
+  const uint32_t k_x = (mat & 1) ^ r8;
+  // V (transposed): matrices (tok 0-7, chunk c), (tok 8-15, c), (tok 0-7, c+1), (tok 8-15, c+1)
+  const uint32_t v_row_off = (r8 + 8 * (mat & 1)) * 128;
+  const uint32_t v_x = (mat >> 1) ^ r8;
+
+  // ---- per-segment state ----
+  uint32_t qa[C::KS][RHI ? 4 : 2];
+  float o[C::NT_O][4];
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  bool seg_start = true;
+  int k_iter = 0;
+  const int R = p.R;
+  bool ok = true;
+
+  while (cons.col < c1) {
+    const int head = cons.g * HG + warp;
+    if (seg_start) {
+      const __nv_bfloat16* qb = p.q + (long long)cons.b * p.q_sb + (long long)(head * R) * p.q_sh;
+#pragma unroll
+      for (int ks = 0; ks < C::KS; ++ks) {
+        const int col = ks * 16 + 2 * tig;
+        qa[ks][0] = gid < R ? ld_global_u32(qb + gid * p.q_sh + col) : 0u;
+        qa[ks][1] = gid < R ? ld_global_u32(qb + gid * p.q_sh + col + 8) : 0u;
+        if constexpr (RHI) {
+          qa[ks][2] = gid + 8 < R ? ld_global_u32(qb + (gid + 8) * p.q_sh + col) : 0u;
+          qa[ks][3] = gid + 8 < R ? ld_global_u32(qb + (gid + 8) * p.q_sh + col + 8) : 0u;
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < C::NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+      m_lo = m_hi = -INFINITY;
+      l_lo = l_hi = 0.f;
+      seg_start = false;
+    }
+
+    const int stage = k_iter % kStages;
+    const uint32_t parity = (k_iter / kStages) & 1;
+    if (!mbar_wait_bounded(bar0 + stage * 8, parity)) { ok = false; break; }
+    const uint32_t kb = stage0 + stage * kStageBytes;
+    const uint32_t vb = kb + C::kKBytes;
+
+    // ---- S = Q K^T for kTile tokens ----
+    float s[C::NT_S][4];
+#pragma unroll
+    for (int nt = 0; nt < C::NT_S; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < C::KS; ++ks) {
+#pragma unroll
+      for (int ntp = 0; ntp < C::NT_S / 2; ++ntp) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = kb + (ks >> 2) * C::kBoxBytes + ntp * 2048 + k_row_off +
+                              (((2u * (ks & 3)) ^ k_x) << 4);
+        ldsm_x4(addr, b0, b1, b2, b3);
+        if constexpr (RHI) {
+          mma_bf16(s[2 * ntp], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b0, b1);
+          mma_bf16(s[2 * ntp + 1], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b2, b3);
+        } else {
+          mma_bf16(s[2 * ntp], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+          mma_bf16(s[2 * ntp + 1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+      }
+    }
+
+    // ---- mask the tail of the sequence, online softmax (log2 domain) ----
+    const int tok0 = cons.j * C::kTile;
+    if (tok0 + C::kTile > cons.len) {
+#pragma unroll
+      for (int nt = 0; nt < C::NT_S; ++nt) {
+        const int t = tok0 + nt * 8 + 2 * tig;
+        if (t >= cons.len) s[nt][0] = s[nt][2] = -INFINITY;
+        if (t + 1 >= cons.len) s[nt][1] = s[nt][3] = -INFINITY;
+      }
+    }
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < C::NT_S; ++nt) {
+      mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
+      if constexpr (RHI) mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
+    }
+    mx_lo = group_max<4>(mx_lo) * p.scale_log2e;
+    const float mn_lo = fmaxf(m_lo, mx_lo);
+    const float mu_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+    const float al_lo = fast_exp2(m_lo - mu_lo);
+    m_lo = mn_lo;
+    float mu_hi = 0.f, al_hi = 1.f;
+    if constexpr (RHI) {
+      mx_hi = group_max<4>(mx_hi) * p.scale_log2e;
+      const float mn_hi = fmaxf(m_hi, mx_hi);
+      mu_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      al_hi = fast_exp2(m_hi - mu_hi);
+      m_hi = mn_hi;
+    }
+    float ps_lo = 0.f, ps_hi = 0.f;
+    uint32_t pa[C::KS_PV][4];
+#pragma unroll
+    for (int nt = 0; nt < C::NT_S; ++nt) {
+      const float p0 = fast_exp2(fmaf(s[nt][0], p.scale_log2e, -mu_lo));
+      const float p1 = fast_exp2(fmaf(s[nt][1], p.scale_log2e, -mu_lo));
+      ps_lo += p0 + p1;
+      pa[nt >> 1][(nt & 1) * 2] = pack_bf16x2(p0, p1);
+      if constexpr (RHI) {
+        const float p2 = fast_exp2(fmaf(s[nt][2], p.scale_log2e, -mu_hi));
+        const float p3 = fast_exp2(fmaf(s[nt][3], p.scale_log2e, -mu_hi));
+        ps_hi += p2 + p3;
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
+      } else {
+        pa[nt >> 1][(nt & 1) * 2 + 1] = 0u;
+      }
+    }
+    l_lo = fmaf(l_lo, al_lo, ps_lo);
+    if constexpr (RHI) l_hi = fmaf(l_hi, al_hi, ps_hi);
+    // Rescale the accumulator only when some row's maximum moved (warp-uniform test).
+    if (__any_sync(kFullMask, al_lo != 1.f || al_hi != 1.f)) {
+#pragma unroll
+      for (int nt = 0; nt < C::NT_O; ++nt) {
+        o[nt][0] *= al_lo;
+        o[nt][1] *= al_lo;
+        if constexpr (RHI) {
+          o[nt][2] *= al_hi;
+          o[nt][3] *= al_hi;
+        }
+      }
+    }
+
+    // ---- O += P V ----
+#pragma unroll
+    for (int kk = 0; kk < C::KS_PV; ++kk) {
+#pragma unroll
+      for (int np = 0; np < C::NT_O / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = vb + (np >> 2) * C::kBoxBytes + kk * 2048 + v_row_off +
+                              (((2u * (np & 3)) ^ v_x) << 4);
+        ldsm_x4_trans(addr, b0, b1, b2, b3);
+        mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+        mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+      }
+    }
+
+    // ---- release the stage and refill it ----
+    __syncwarp();
+    if (prod.col < c1) {
+      if (lane == 0) issue(prod, stage);
+      wk.advance(prod);
+      ++issued;
+    }
+    ++k_iter;
+
+    // ---- end of this (sequence, head) unit inside the CTA's range? ----
+    if (fd_unit_ends(cons, c1)) {
+      seg_start = true;
+      l_lo = group_sum<4>(l_lo);
+      if constexpr (RHI) l_hi = group_sum<4>(l_hi);
+      const int u0 = wk.unit_begin(cons);
+      const int cfirst = fd_cta_of(u0, total, G);
+      const int clast = fd_cta_of(u0 + cons.tc - 1, total, G);
+      const long long hq0 = (long long)head * R;
+
+      if (cfirst == clast) {
+        // The whole unit was seen by this warp: normalise and write.
+        const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f;
+        const float inv_hi = (RHI && l_hi > 0.f) ? 1.f / l_hi : 0.f;
+        if (p.out) {
+          __nv_bfloat16* ob = p.out + (long long)cons.b * p.o_sb + hq0 * p.o_sh;
+#pragma unroll
+          for (int nt = 0; nt < C::NT_O; ++nt) {
+            const int d = nt * 8 + 2 * tig;
+            if (gid < R)
+              *reinterpret_cast<uint32_t*>(ob + gid * p.o_sh + d) = pack_bf16x2(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
+            if constexpr (RHI) {
+              if (gid + 8 < R)
+                *reinterpret_cast<uint32_t*>(ob + (gid + 8) * p.o_sh + d) =
+                    pack_bf16x2(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
+            }
+          }
+        }
+        if (p.o_partial) {
+          float* ob = p.o_partial + ((long long)cons.b * p.Hq + hq0) * D;
+          float* lb = p.lse + (long long)cons.b * p.Hq + hq0;
+#pragma unroll
+          for (int nt = 0; nt < C::NT_O; ++nt) {
+            const int d = nt * 8 + 2 * tig;
+            if (gid < R) *reinterpret_cast<float2*>(ob + gid * D + d) = make_float2(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
+            if constexpr (RHI) {
+              if (gid + 8 < R)
+                *reinterpret_cast<float2*>(ob + (gid + 8) * D + d) = make_float2(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
+            }
+          }
+          if (tig == 0) {
+            if (gid < R) lb[gid] = l_lo > 0.f ? (m_lo + log2f(l_lo)) * 0.6931471805599453f : -INFINITY;
+            if constexpr (RHI) {
+              if (gid + 8 < R) lb[gid + 8] = l_hi > 0.f ? (m_hi + log2f(l_hi)) * 0.6931471805599453f : -INFINITY;
+            }
+          }
+        }
+      } else {
+        // Leave an unnormalised record; the last warp to arrive for this unit merges them all.
+        float* rec = p.records + (long long)fd_record_index(cta, cfirst, HG, warp) * p.rec_floats;
+#pragma unroll
+        for (int nt = 0; nt < C::NT_O; ++nt) {
+          const int d = nt * 8 + 2 * tig;
+          if (gid < R) __stcg(reinterpret_cast<float2*>(rec + gid * D + d), make_float2(o[nt][0], o[nt][1]));
+          if constexpr (RHI) {
+            if (gid + 8 < R) __stcg(reinterpret_cast<float2*>(rec + (gid + 8) * D + d), make_float2(o[nt][2], o[nt][3]));
+          }
+        }
+        if (tig == 0) {
+          if (gid < R) {
+            __stcg(rec + R * D + gid, m_lo);
+            __stcg(rec + R * D + R + gid, l_lo);
+          }
+          if constexpr (RHI) {
+            if (gid + 8 < R) {
+              __stcg(rec + R * D + gid + 8, m_hi);
+              __stcg(rec + R * D + R + gid + 8, l_hi);
+            }
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        int* counter = p.counters + cons.b * p.Hkv + head;
+        int last = 0;
+        if (lane == 0) {
+          const int n = clast - cfirst + 1;
+          last = atomicAdd(counter, 1) == n - 1;
+          if (last) *counter = 0;  // ready for the next launch
+        }
+        last = __shfl_sync(kFullMask, last, 0);
+        if (last) {
+          __threadfence();
+          constexpr int EPL = D / 32;  // output elements per lane
+          for (int r = 0; r < R; ++r) {
+            float M = -INFINITY;
+            for (int c = cfirst; c <= clast; ++c) {
+              const float* rc = p.records + (long long)fd_record_index(c, cfirst, HG, warp) * p.rec_floats;
+              M = fmaxf(M, __ldcg(rc + R * D + r));
+            }
+            const float Mu = M == -INFINITY ? 0.f : M;
+            float acc[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+            float L = 0.f;
+            for (int c = cfirst; c <= clast; ++c) {
+              const float* rc = p.records + (long long)fd_record_index(c, cfirst, HG, warp) * p.rec_floats;
+              const float w = fast_exp2(__ldcg(rc + R * D + r) - Mu);
+              L = fmaf(__ldcg(rc + R * D + R + r), w, L);
+              if constexpr (EPL == 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(rc + r * D) + lane);
+                acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
+                acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
+              } else {
+                const float2 v = __ldcg(reinterpret_cast<const float2*>(rc + r * D) + lane);
+                acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
+              }
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            if (p.out) {
+              __nv_bfloat16* ob = p.out + (long long)cons.b * p.o_sb + (hq0 + r) * p.o_sh + lane * EPL;
+#pragma unroll
+              for (int e = 0; e < EPL; e += 2)
+                *reinterpret_cast<uint32_t*>(ob + e) = pack_bf16x2(acc[e] * inv, acc[e + 1] * inv);
+            }
+            if (p.o_partial) {
+              float* ob = p.o_partial + ((long long)cons.b * p.Hq + hq0 + r) * D + lane * EPL;
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) ob[e] = acc[e] * inv;
+              if (lane == 0)
+                p.lse[(long long)cons.b * p.Hq + hq0 + r] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+            }
+          }
+        }
+      }
+    }
+    wk.advance(cons);
+  }
+
+  if (!ok) {
+    // A bulk copy never signalled.  Record it, then give the other copies of this warp a bounded
+    // chance to land before the shared memory goes away.
+    if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+    for (int k = k_iter + 1; k < issued; ++k)
+      (void)mbar_wait_bounded(bar0 + (k % kStages) * 8, (k / kStages) & 1);
+  }
+}
+
+// Writes zeros for a call without any cached token.
+__global__ void zero_out_kernel(__nv_bfloat16* out, float* o_partial, float* lse, int B, int Hq, int D,
+                                long long o_sb, long long o_sh) {
+  const long long n = (long long)B * Hq * D;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D);
+    const long long bh = i / D;
+    const int h = (int)(bh % Hq);
+    const long long b = bh / Hq;
+    if (out) out[b * o_sb + h * o_sh + d] = __float2bfloat16(0.f);
+    if (o_partial) o_partial[i] = 0.f;
+    if (lse && d == 0) lse[bh] = -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(f);
+  });
+  return fn;
+}
+
+// Rank-4 map over a [B, Hkv, n_seq, D] view: dims (d, token, head, batch), box 64 x tile tokens.
+int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, int B, long long st,
+                long long sh, long long sb, int tile) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return fail(L3CI_ERR_CUDA, "flash_decode: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t row_bytes = (cuuint64_t)D * 2;
+  // A dimension of extent 1 may carry any stride in the caller's view; give it a valid one.
+  const cuuint64_t st_b = n_seq > 1 ? (cuuint64_t)st * 2 : row_bytes;
+  const cuuint64_t sh_b = Hkv > 1 ? (cuuint64_t)sh * 2 : row_bytes;
+  const cuuint64_t sb_b = B > 1 ? (cuuint64_t)sb * 2 : row_bytes;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)n_seq, (cuuint64_t)Hkv, (cuuint64_t)B};
+  cuuint64_t strides[3] = {st_b, sh_b, sb_b};
+  cuuint32_t box[4] = {64u, (cuuint32_t)tile, 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         D == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(L3CI_ERR_CUDA, "flash_decode: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return L3CI_OK;
+}
+
+size_t counters_bytes(int B, int Hkv) { return (((size_t)B * Hkv * sizeof(int)) + 255) & ~(size_t)255; }
+
+size_t smem_bytes(int HG, int B, bool ragged) {
+  size_t s = 1024 + (size_t)HG * kStages * kStageBytes + (size_t)HG * kStages * 8;
+  if (ragged) s += (size_t)(2 * B + 1) * sizeof(int);
+  return s;
+}
+
+template <int D, bool RHI>
+int launch_fd(const CUtensorMap& kmap, const CUtensorMap& vmap, const FdParams& p, int grid, int HG,
+              size_t smem, cudaStream_t stream) {
+  static size_t configured[64] = {0};
+  int dev = 0;
+  L3CI_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 64 || configured[dev] < smem) {
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_kernel<D, RHI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    if (dev < 64) configured[dev] = smem;
+  }
+  flash_decode_kernel<D, RHI><<<grid, HG * 32, smem, stream>>>(kmap, vmap, p);
+  L3CI_CHECK_LAUNCH("flash_decode_kernel");
+  return L3CI_OK;
+}
+
+}  // namespace
+}  // namespace l3ci
+
+extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D) {
+  using namespace l3ci;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || Hq % Hkv) return 0;
+  const int R = Hq / Hkv;
+  const int sms = sm_count();
+  if (sms <= 0) return 0;
+  // Records: 2 per CTA per warp; CTAs * warps is 8 per SM whatever the head grouping is.
+  const size_t records = (size_t)fd_max_ctas(sms, fd_head_group(Hkv)) * fd_head_group(Hkv) * 2;
+  return kHeaderBytes + counters_bytes(B, Hkv) + records * (size_t)R * (D + 2) * sizeof(float);
+}
+
+extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) {
+  using namespace l3ci;
+  clear_error();
+  if (!a) return fail(L3CI_ERR_INVALID, "flash_decode: null args");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  const int B = a->B, Hq = a->Hq, Hkv = a->Hkv, D = a->D, n_seq = a->n_seq;
+  if (B < 0 || Hq <= 0 || Hkv <= 0 || n_seq < 0) return fail(L3CI_ERR_INVALID, "flash_decode: bad size B=%d Hq=%d Hkv=%d n_seq=%d", B, Hq, Hkv, n_seq);
+  if (Hq % Hkv) return fail(L3CI_ERR_INVALID, "flash_decode: %d query heads not divisible by %d kv heads", Hq, Hkv);
+  if (D != 64 && D != 128) return fail(L3CI_ERR_UNSUPPORTED, "Unsupported head size for flash_decode kernel: %d", D);
+  const int R = Hq / Hkv;
+  if (R > 16) return fail(L3CI_ERR_UNSUPPORTED, "Unsupported QKV head ratio for flash_decode kernel: %d", R);
+  if (B == 0) return L3CI_OK;
+  if (!a->q || (!a->out && !a->o_partial)) return fail(L3CI_ERR_INVALID, "flash_decode: null q or no output");
+  if ((a->o_partial == nullptr) != (a->lse == nullptr)) return fail(L3CI_ERR_INVALID, "flash_decode: o_partial and lse go together");
+  if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (a->q_sb & 1) || (a->q_sh & 1) ||
+      (a->out && ((reinterpret_cast<uintptr_t>(a->out) & 3) || (a->o_sb & 1) || (a->o_sh & 1))) ||
+      (a->o_partial && !aligned16(a->o_partial)))
+    return fail(L3CI_ERR_ALIGNMENT, "flash_decode: q/out rows must start on 4 bytes");
+
+  if (n_seq == 0) {
+    zero_out_kernel<<<64, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(a->out), a->o_partial, a->lse, B, Hq, D,
+                                            a->o_sb, a->o_sh);
+    L3CI_CHECK_LAUNCH("zero_out_kernel");
+    return L3CI_OK;
+  }
+  if (!a->k || !a->v) return fail(L3CI_ERR_INVALID, "flash_decode: null k or v");
+  if (!aligned16(a->k) || !aligned16(a->v) || (n_seq > 1 && (a->k_st % 8 || a->v_st % 8)) ||
+      (Hkv > 1 && (a->k_sh % 8 || a->v_sh % 8)) || (B > 1 && (a->k_sb % 8 || a->v_sb % 8)))
+    return fail(L3CI_ERR_ALIGNMENT, "flash_decode: k/v rows must start on 16 bytes and strides be multiples of 8 elements");
+  if ((n_seq > 1 && (a->k_st <= 0 || a->v_st <= 0)) || (Hkv > 1 && (a->k_sh <= 0 || a->v_sh <= 0)) ||
+      (B > 1 && (a->k_sb <= 0 || a->v_sb <= 0)))
+    return fail(L3CI_ERR_INVALID, "flash_decode: k/v strides must be positive");
+
+  const int tile = fd_tile_tokens(D);
+  const int HG = fd_head_group(Hkv);
+  const int n_groups = Hkv / HG;
+  const long long max_cols = (long long)B * n_groups * fd_tiles(n_seq, tile);
+  if (max_cols > 0x3fffffffLL) return fail(L3CI_ERR_INVALID, "flash_decode: too many tiles (%lld)", max_cols);
+  const bool ragged = a->seq_lens != nullptr;
+  if (ragged && B > 4096) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: seq_lens supports at most 4096 sequences, got %d", B);
+
+  const int sms = sm_count();
+  if (sms <= 0) return fail(L3CI_ERR_CUDA, "flash_decode: no CUDA device");
+  int grid = fd_max_ctas(sms, HG);
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  if (max_cols < grid) grid = (int)max_cols;
+
+  const size_t need = l3ci_flash_decode_scratch_bytes(B, Hq, Hkv, D);
+  if (!a->scratch || a->scratch_bytes < need)
+    return fail(L3CI_ERR_SCRATCH, "flash_decode: scratch has %zu bytes, needs %zu", a->scratch_bytes, need);
+  if (reinterpret_cast<uintptr_t>(a->scratch) & 255) return fail(L3CI_ERR_ALIGNMENT, "flash_decode: scratch must be 256-byte aligned");
+
+  const size_t smem = smem_bytes(HG, B, ragged);
+  if ((long long)smem > max_smem_optin()) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: needs %zu bytes of shared memory", smem);
+
+  CUtensorMap kmap, vmap;
+  if (int st = make_kv_map(&kmap, a->k, D, n_seq, Hkv, B, a->k_st, a->k_sh, a->k_sb, tile)) return st;
+  if (int st = make_kv_map(&vmap, a->v, D, n_seq, Hkv, B, a->v_st, a->v_sh, a->v_sb, tile)) return st;
+
+  FdParams p;
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.o_partial = a->o_partial;
+  p.lse = a->lse;
+  p.seq_lens = a->seq_lens;
+  uint8_t* sc = static_cast<uint8_t*>(a->scratch);
+  p.status = reinterpret_cast<int*>(sc);
+  p.counters = reinterpret_cast<int*>(sc + kHeaderBytes);
+  p.records = reinterpret_cast<float*>(sc + kHeaderBytes + counters_bytes(B, Hkv));
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.R = R; p.n_seq = n_seq; p.n_groups = n_groups;
+  p.q_sb = a->q_sb; p.q_sh = a->q_sh; p.o_sb = a->o_sb; p.o_sh = a->o_sh;
+  const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)D);
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.rec_floats = R * (D + 2);
+
+  if (D == 64) {
+    return R > 8 ? launch_fd<64, true>(kmap, vmap, p, grid, HG, smem, stream)
+                 : launch_fd<64, false>(kmap, vmap, p, grid, HG, smem, stream);
+  }
+  return R > 8 ? launch_fd<128, true>(kmap, vmap, p, grid, HG, smem, stream)
+               : launch_fd<128, false>(kmap, vmap, p, grid, HG, smem, stream);
+}
+
+extern "C" int l3ci_flash_decode_poll(void* scratch, size_t scratch_bytes, l3ci_stream_t stream_) {
+  using namespace l3ci;
+  clear_error();
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!scratch || scratch_bytes < (size_t)kHeaderBytes) return fail(L3CI_ERR_INVALID, "flash_decode_poll: no scratch");
+  int status = 0;
+  L3CI_CUDA_TRY(cudaMemcpyAsync(&status, scratch, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  L3CI_CUDA_TRY(cudaStreamSynchronize(stream));
+  if (status != 0) {
+    // Records need no clearing; the header and every counter do.
+    L3CI_CUDA_TRY(cudaMemsetAsync(scratch, 0, scratch_bytes, stream));
+    return fail(status, "flash_decode: a bounded wait on a bulk copy ran out in an earlier launch");
+  }
+  return L3CI_OK;
+}

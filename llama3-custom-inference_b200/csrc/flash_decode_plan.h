@@ -1,0 +1,125 @@
+// Work partition of the flash-decode kernel, as plain integer functions usable from device code,
+// from the host launcher and from a C++ unit test compiled without CUDA.
+//
+// Vocabulary: a TILE is kTile consecutive cached tokens of one KV head; a COLUMN is the same tile
+// for the HG neighbouring KV heads of one head group; a UNIT is one (sequence, KV head) pair, i.e.
+// all tiles whose partial results must be merged.  Columns are numbered sequence-major, then head
+// group, then tile, and the numbered list is cut into `ctas` contiguous ranges whose sizes differ
+// by at most one.  (The reference cuts every sequence into fixed 64-token steps, one CTA each:
+// custom_kernels/custom_kernels.cu:243,251,256-259.)
+#pragma once
+
+#if defined(__CUDACC__)
+#define L3CI_HD __host__ __device__ __forceinline__
+#else
+#define L3CI_HD inline
+#endif
+
+namespace l3ci {
+
+// Tokens per tile: one stage holds a K and a V tile of 4 KiB each.
+L3CI_HD constexpr int fd_tile_tokens(int head_size) { return head_size == 128 ? 16 : 32; }
+
+// Warps per CTA = KV heads walked side by side = gcd(Hkv, 8).
+L3CI_HD constexpr int fd_head_group(int kv_heads) {
+  int a = kv_heads, b = 8;
+  while (b) {
+    const int t = a % b;
+    a = b;
+    b = t;
+  }
+  return a;
+}
+
+// Largest useful persistent grid: 8 warps' worth of pipelines fit in one SM's shared memory.
+L3CI_HD constexpr int fd_max_ctas(int sms, int head_group) { return sms * (8 / head_group); }
+
+// Tiles of a sequence; an empty sequence still owns one (fully masked) tile so that its output
+// rows get written.
+L3CI_HD constexpr int fd_tiles(int len, int tile) { return len <= 0 ? 1 : (len + tile - 1) / tile; }
+
+// CTAs that take part when `total` columns meet a grid of `grid` CTAs: never more CTAs than columns,
+// so that every participating CTA owns at least one column.
+L3CI_HD constexpr int fd_active_ctas(int grid, int total) { return grid < total ? grid : total; }
+
+// First column of CTA `cta` when `total` columns are dealt to `ctas` CTAs.
+L3CI_HD constexpr int fd_range_begin(int cta, int total, int ctas) {
+  return (int)(((long long)cta * total) / ctas);
+}
+
+// The CTA whose range holds column `col`: the largest c with fd_range_begin(c) <= col.
+L3CI_HD constexpr int fd_cta_of(int col, int total, int ctas) {
+  return (int)((((long long)col + 1) * ctas - 1) / total);
+}
+
+// Scratch record written by warp `warp` of CTA `cta` for a unit whose first column lies in CTA
+// `first_cta`.  A CTA leaves at most two records per warp: slot 0 for a unit that began in an
+// earlier CTA, slot 1 for a unit that begins here and runs on into the next CTA.
+L3CI_HD constexpr int fd_record_index(int cta, int first_cta, int head_group, int warp) {
+  return (cta * 2 + (cta == first_cta ? 1 : 0)) * head_group + warp;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Walk over the columns of a CTA's range: (sequence b, head group g, tile j).
+// ---------------------------------------------------------------------------------------------
+struct FdCursor {
+  int col;   // global column index
+  int b, g, j;
+  int tc;    // tiles of sequence b
+  int len;   // valid tokens of sequence b
+};
+
+struct FdWalker {
+  const int* pref;  // pref[b] = columns before sequence b, pref[B] = total; null when every sequence
+                    // has n_seq tokens
+  const int* lens;  // clamped lengths; null together with pref
+  int B, n_groups, n_seq, tile;
+
+  L3CI_HD int len_of(int b) const { return lens ? lens[b] : n_seq; }
+  L3CI_HD int pref_of(int b) const { return pref ? pref[b] : b * n_groups * fd_tiles(n_seq, tile); }
+  L3CI_HD int total() const { return pref_of(B); }
+
+  L3CI_HD FdCursor seek(int col) const {
+    FdCursor c;
+    c.col = col;
+    if (pref) {
+      int lo = 0, hi = B;  // largest b in [0, B) with pref[b] <= col
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (pref[mid] <= col) lo = mid; else hi = mid;
+      }
+      c.b = lo;
+    } else {
+      c.b = col / (n_groups * fd_tiles(n_seq, tile));
+    }
+    c.len = len_of(c.b);
+    c.tc = fd_tiles(c.len, tile);
+    const int local = col - pref_of(c.b);
+    c.g = local / c.tc;
+    c.j = local - c.g * c.tc;
+    return c;
+  }
+
+  L3CI_HD void advance(FdCursor& c) const {
+    ++c.col;
+    if (++c.j == c.tc) {
+      c.j = 0;
+      if (++c.g == n_groups) {
+        c.g = 0;
+        if (++c.b < B) {
+          c.len = len_of(c.b);
+          c.tc = fd_tiles(c.len, tile);
+        }
+      }
+    }
+  }
+
+  // First column of the unit the cursor is in, and the CTAs that unit spans.
+  L3CI_HD int unit_begin(const FdCursor& c) const { return pref_of(c.b) + c.g * c.tc; }
+};
+
+// True when the cursor stands on the last column its CTA sees of the current unit.
+L3CI_HD bool fd_unit_ends(const FdCursor& c, int range_end) { return c.j == c.tc - 1 || c.col == range_end - 1; }
+
+}  // namespace l3ci

@@ -1,0 +1,41 @@
+// Host-side helpers shared by the launchers: thread-local error text, launch checks,
+// cached device properties.  Unlike the reference, whose cudaCheck is never called
+// (custom_kernels/custom_kernels.cu:224-231), every launcher checks its arguments and the
+// launch result and reports through the status code it returns.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/l3ci_b200.h"
+
+namespace l3ci {
+
+// Stores a printf-formatted message for l3ci_last_error() and returns `status`.
+int fail(int status, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+// Largest opt-in dynamic shared memory per block of the current device (cached).
+int max_smem_optin();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define L3CI_CUDA_TRY(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return ::l3ci::fail(L3CI_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+// After a <<<>>> launch: picks up configuration errors without synchronising.
+#define L3CI_CHECK_LAUNCH(name)                                                            \
+  do {                                                                                     \
+    cudaError_t e_ = cudaGetLastError();                                                   \
+    if (e_ != cudaSuccess)                                                                 \
+      return ::l3ci::fail(L3CI_ERR_CUDA, "launch of %s failed: %s", name,                  \
+                          cudaGetErrorString(e_));                                         \
+  } while (0)
+
+}  // namespace l3ci

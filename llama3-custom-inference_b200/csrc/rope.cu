@@ -1,0 +1,185 @@
+// Rotary embedding (interleaved pairs) for sm_100a, alone and fused with the KV-cache write.
+//
+// Replaces custom_rot_embed_kernel / rot_embed (custom_kernels/custom_kernels.cu:391-442),
+// which launches one 32/64-thread CTA per (batch, token, head) and moves 4 bytes per thread.
+// Here one thread owns 8 consecutive bf16 (four rotation pairs, one 16-byte load and store)
+// and the two fp32 table vectors that go with them; the grid is flat over all vectors.
+// The fused variant walks the projection output q|k|v once and writes rotated q to a dense
+// buffer, rotated k and untouched v straight into the cache rows of this step, which is what
+// CausalSelfAttention.forward does with two kernel calls and two copies (model.py:100-108).
+//
+// Arithmetic: (x*c - y*s, x*s + y*c) in fp32 with each product and the sum rounded
+// separately (no fused multiply-add), then one rounding to bf16, so results are
+// bit-identical to the same formula evaluated with unfused fp32 operations on a CPU.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "bf16x8.cuh"
+#include "host_common.h"
+
+namespace l3ci {
+namespace {
+
+constexpr int kRopeBlock = 256;
+
+__device__ __forceinline__ void rotate_pair(float x, float y, float c, float s, float& xo, float& yo) {
+  xo = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
+  yo = __fadd_rn(__fmul_rn(x, s), __fmul_rn(y, c));
+}
+
+// Rotates the 8 bf16 of `v` with the table entries freq8[0..7] = (c0,s0,c1,s1,c2,s2,c3,s3).
+__device__ __forceinline__ uint4 rotate8(const uint4& v, const float* __restrict__ freq8) {
+  const float4 f0 = __ldg(reinterpret_cast<const float4*>(freq8));
+  const float4 f1 = __ldg(reinterpret_cast<const float4*>(freq8) + 1);
+  float a[8], r[8];
+  unpack8(v, a);
+  rotate_pair(a[0], a[1], f0.x, f0.y, r[0], r[1]);
+  rotate_pair(a[2], a[3], f0.z, f0.w, r[2], r[3]);
+  rotate_pair(a[4], a[5], f1.x, f1.y, r[4], r[5]);
+  rotate_pair(a[6], a[7], f1.z, f1.w, r[6], r[7]);
+  return pack8(r);
+}
+
+// x [B,S,H,D] strided, out dense.  One thread per 16-byte vector.
+__global__ void __launch_bounds__(kRopeBlock)
+rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freq,
+                      __nv_bfloat16* __restrict__ out, long long total, int S, int H, int vec_per_head,
+                      long long sb, long long ss, long long sh) {
+  const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int vec = (int)(idx % vec_per_head);
+  long long rest = idx / vec_per_head;
+  const int h = (int)(rest % H);
+  rest /= H;
+  const int s = (int)(rest % S);
+  const long long b = rest / S;
+  const int D = vec_per_head * kVecElems;
+  const uint4 v = ld_stream16(x + b * sb + s * ss + h * sh + vec * kVecElems);
+  const uint4 r = rotate8(v, freq + (long long)s * D + vec * kVecElems);
+  st_stream16(out + idx * kVecElems, r);
+}
+
+// Fallback for rows that only start on 4 bytes: one thread per rotation pair.
+__global__ void __launch_bounds__(kRopeBlock)
+rot_embed_pair_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freq,
+                      __nv_bfloat16* __restrict__ out, long long total, int S, int H, int pairs_per_head,
+                      long long sb, long long ss, long long sh) {
+  const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int p = (int)(idx % pairs_per_head);
+  long long rest = idx / pairs_per_head;
+  const int h = (int)(rest % H);
+  rest /= H;
+  const int s = (int)(rest % S);
+  const long long b = rest / S;
+  const int D = pairs_per_head * 2;
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(x + b * sb + s * ss + h * sh + 2 * p);
+  const float2 cs = __ldg(reinterpret_cast<const float2*>(freq + (long long)s * D) + p);
+  float xo, yo;
+  rotate_pair(bf16lo_to_f32(w), bf16hi_to_f32(w), cs.x, cs.y, xo, yo);
+  *reinterpret_cast<uint32_t*>(out + idx * 2) = pack_bf16x2(xo, yo);
+}
+
+// qkv [B,T,(Hq+2Hkv)*D] -> q_out dense [B,T,Hq,D], cache_k/v[b, start_pos+t, h, :].
+__global__ void __launch_bounds__(kRopeBlock)
+rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ freq,
+                          __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ cache_k,
+                          __nv_bfloat16* __restrict__ cache_v, long long total, int T, int Hq, int Hkv,
+                          int vec_per_head, long long qkv_sb, long long qkv_st, long long cache_sb,
+                          long long cache_st, long long start_pos) {
+  const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
+  if (idx >= total) return;
+  const int heads = Hq + 2 * Hkv;
+  const int vec = (int)(idx % vec_per_head);
+  long long rest = idx / vec_per_head;
+  const int hh = (int)(rest % heads);
+  rest /= heads;
+  const int t = (int)(rest % T);
+  const long long b = rest / T;
+  const int D = vec_per_head * kVecElems;
+  const uint4 v = ld_stream16(qkv + b * qkv_sb + t * qkv_st + (long long)hh * D + vec * kVecElems);
+  const float* f = freq + (long long)t * D + vec * kVecElems;
+  if (hh < Hq) {
+    st_stream16(q_out + ((b * T + t) * Hq + hh) * (long long)D + vec * kVecElems, rotate8(v, f));
+  } else if (hh < Hq + Hkv) {
+    // Cache rows are read again by the attention kernel of the same step: plain store.
+    *reinterpret_cast<uint4*>(cache_k + b * cache_sb + (start_pos + t) * cache_st +
+                              (long long)(hh - Hq) * D + vec * kVecElems) = rotate8(v, f);
+  } else {
+    *reinterpret_cast<uint4*>(cache_v + b * cache_sb + (start_pos + t) * cache_st +
+                              (long long)(hh - Hq - Hkv) * D + vec * kVecElems) = v;
+  }
+}
+
+int grid_for(long long total, unsigned* grid) {
+  const long long ctas = (total + kRopeBlock - 1) / kRopeBlock;
+  if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rot_embed: tensor too large");
+  *grid = (unsigned)ctas;
+  return L3CI_OK;
+}
+
+}  // namespace
+}  // namespace l3ci
+
+extern "C" int l3ci_rot_embed(const void* x, const float* freq, void* out, int64_t B, int64_t S,
+                              int64_t H, int64_t D, int64_t sb, int64_t ss, int64_t sh,
+                              l3ci_stream_t stream_) {
+  using namespace l3ci;
+  clear_error();
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (B < 0 || S < 0 || H < 0 || D <= 0) return fail(L3CI_ERR_INVALID, "rot_embed: negative size");
+  if (B == 0 || S == 0 || H == 0) return L3CI_OK;
+  if (!x || !freq || !out) return fail(L3CI_ERR_INVALID, "rot_embed: null pointer");
+  if (D % 2) return fail(L3CI_ERR_UNSUPPORTED, "rot_embed: head size %lld is odd", (long long)D);
+  if (S > 0x7fffffff || H > 0x7fffffff || D > 0x7fffffff) return fail(L3CI_ERR_INVALID, "rot_embed: size overflow");
+  const auto xp = static_cast<const __nv_bfloat16*>(x);
+  const auto op = static_cast<__nv_bfloat16*>(out);
+  const bool vec8 = D % kVecElems == 0 && aligned16(x) && aligned16(out) && aligned16(freq) &&
+                    sb % kVecElems == 0 && ss % kVecElems == 0 && sh % kVecElems == 0;
+  unsigned grid = 0;
+  if (vec8) {
+    const long long total = B * S * H * (D / kVecElems);
+    if (int st = grid_for(total, &grid)) return st;
+    rot_embed_vec8_kernel<<<grid, kRopeBlock, 0, stream>>>(xp, freq, op, total, (int)S, (int)H,
+                                                           (int)(D / kVecElems), sb, ss, sh);
+    L3CI_CHECK_LAUNCH("rot_embed_vec8_kernel");
+    return L3CI_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(out) & 3) ||
+      (reinterpret_cast<uintptr_t>(freq) & 7) || (sb & 1) || (ss & 1) || (sh & 1))
+    return fail(L3CI_ERR_ALIGNMENT, "rot_embed: rotation pairs must start on 4 bytes");
+  const long long total = B * S * H * (D / 2);
+  if (int st = grid_for(total, &grid)) return st;
+  rot_embed_pair_kernel<<<grid, kRopeBlock, 0, stream>>>(xp, freq, op, total, (int)S, (int)H,
+                                                         (int)(D / 2), sb, ss, sh);
+  L3CI_CHECK_LAUNCH("rot_embed_pair_kernel");
+  return L3CI_OK;
+}
+
+extern "C" int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void* q_out, void* cache_k,
+                                       void* cache_v, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                                       int64_t D, int64_t qkv_sb, int64_t qkv_st, int64_t cache_sb,
+                                       int64_t cache_st, int64_t start_pos, l3ci_stream_t stream_) {
+  using namespace l3ci;
+  clear_error();
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (B < 0 || T < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || start_pos < 0)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache: bad size");
+  if (B == 0 || T == 0) return L3CI_OK;
+  if (!qkv || !freq || !q_out || !cache_k || !cache_v)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache: null pointer");
+  if (D % kVecElems) return fail(L3CI_ERR_UNSUPPORTED, "rot_embed_kv_cache: head size %lld not a multiple of 8", (long long)D);
+  if (!aligned16(qkv) || !aligned16(freq) || !aligned16(q_out) || !aligned16(cache_k) ||
+      !aligned16(cache_v) || qkv_sb % kVecElems || qkv_st % kVecElems || cache_sb % kVecElems ||
+      cache_st % kVecElems)
+    return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache: rows must start on 16 bytes");
+  const long long total = B * T * (Hq + 2 * Hkv) * (D / kVecElems);
+  unsigned grid = 0;
+  if (int st = grid_for(total, &grid)) return st;
+  rot_embed_kv_cache_kernel<<<grid, kRopeBlock, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(qkv), freq, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), total, (int)T,
+      (int)Hq, (int)Hkv, (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, start_pos);
+  L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
+  return L3CI_OK;
+}

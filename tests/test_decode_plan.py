@@ -1,0 +1,80 @@
+"""The flash-decode work partition (csrc/flash_decode_plan.h) replayed on the CPU: every tile is visited
+once, every (sequence, kv head) unit is finished exactly once, merge records never collide."""
+import ctypes as C
+import random
+import subprocess
+from pathlib import Path
+
+import pytest
+
+REPO = Path(__file__).resolve().parents[1]
+CSRC = REPO / "llama3-custom-inference_b200" / "csrc"
+
+
+@pytest.fixture(scope="module")
+def plan(tmp_path_factory):
+    so = tmp_path_factory.mktemp("plan") / "plan_harness.so"
+    subprocess.run(["g++", "-O1", "-std=c++17", "-shared", "-fPIC", "-I", str(CSRC),
+                    str(REPO / "tests" / "plan_harness.cpp"), "-o", str(so)], check=True)
+    lib = C.CDLL(str(so))
+    lib.plan_simulate.argtypes = [C.c_int] * 4 + [C.POINTER(C.c_int)] + [C.c_int] * 2 + [C.POINTER(C.c_int), C.POINTER(C.c_longlong)]
+    return lib
+
+
+def simulate(plan, B, Hkv, D, n_seq, lens, G, stages=3):
+    info = (C.c_int * 4)()
+    stats = (C.c_longlong * 6)()
+    arr = (C.c_int * B)(*lens) if lens is not None else None
+    rc = plan.plan_simulate(B, Hkv, D, n_seq, arr, G, stages, info, stats)
+    assert rc == 0, f"invariant {rc} broken: info={list(info)} B={B} Hkv={Hkv} D={D} n_seq={n_seq} lens={lens} G={G}"
+    return list(stats)
+
+
+def test_constants(plan):
+    assert plan.plan_tile_tokens(128) == 16 and plan.plan_tile_tokens(64) == 32
+    assert [plan.plan_head_group(h) for h in (1, 2, 3, 4, 6, 8, 12, 32)] == [1, 2, 1, 4, 2, 8, 4, 8]
+    assert plan.plan_max_ctas(148, 8) == 148 and plan.plan_max_ctas(148, 1) == 1184
+
+
+def test_ranges_are_balanced_and_invertible(plan):
+    for total, G in [(1, 1), (3, 8), (300, 148), (148, 148), (149, 148), (65536, 148), (12288, 148), (7, 1184)]:
+        sizes = [plan.plan_range_begin(c + 1, total, G) - plan.plan_range_begin(c, total, G) for c in range(G)]
+        assert sum(sizes) == total and max(sizes) - min(sizes) <= 1
+        for col in range(0, total, max(1, total // 97)):
+            c = plan.plan_cta_of(col, total, G)
+            assert plan.plan_range_begin(c, total, G) <= col < plan.plan_range_begin(c + 1, total, G)
+
+
+@pytest.mark.parametrize("B,Hkv,D,n_seq,G", [
+    (1, 8, 64, 256, 8),          # config 1
+    (1, 8, 128, 131072, 148),    # config 3
+    (64, 8, 64, 2176, 148),      # end-to-end decode batch
+    (1, 8, 128, 1, 1), (1, 8, 128, 17, 2), (2, 1, 64, 100, 1184), (3, 2, 128, 777, 592),
+    (5, 32, 128, 333, 148), (4, 6, 64, 65, 592), (2, 3, 128, 4096, 1184), (7, 4, 64, 31, 296),
+])
+def test_uniform_lengths(plan, B, Hkv, D, n_seq, G):
+    stats = simulate(plan, B, Hkv, D, n_seq, None, G)
+    assert stats[0] + stats[1] == B * Hkv
+    assert stats[3] - stats[4] <= 1
+
+
+def test_config2_ragged_batch(plan):
+    rng = random.Random(42)
+    lens = [rng.randint(1024, 2048) for _ in range(16)]
+    stats = simulate(plan, 16, 8, 128, 2048, lens, 148)
+    assert stats[0] + stats[1] == 16 * 8 and stats[3] - stats[4] <= 1
+    assert stats[5] == sum((l + 15) // 16 for l in lens)
+
+
+def test_random_ragged_batches(plan):
+    rng = random.Random(7)
+    for _ in range(300):
+        B = rng.randint(1, 40)
+        Hkv = rng.choice([1, 2, 3, 4, 6, 8, 16])
+        D = rng.choice([64, 128])
+        n_seq = rng.choice([1, 15, 16, 17, 63, 64, 65, 200, 1000])
+        lens = [rng.choice([0, 1, n_seq, rng.randint(0, n_seq), rng.randint(-3, n_seq + 5)]) for _ in range(B)]
+        hg = plan.plan_head_group(Hkv)
+        G = rng.choice([1, 2, 3, 7, 148, plan.plan_max_ctas(148, hg)])
+        stats = simulate(plan, B, Hkv, D, n_seq, lens, G, stages=rng.choice([1, 2, 3, 4]))
+        assert stats[0] + stats[1] == B * Hkv
