@@ -1,0 +1,474 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|rmsnorm|rope] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of synthetic input: for the default workload (C2) one
+`flash_attention_decode` call over a ragged batch of 16 sequences (32 q / 8 kv heads, head size 128, lengths
+uniform in [1024, 2048], cache padded to 2048, bf16).  The metric is the reference's own
+(benchmark_kernel.py:48-49): bytes of K and V that belong to valid tokens, 2*2*Hkv*D*sum(len), per second,
+in decimal GB/s.
+
+Printed JSON line (rank 0):
+  value          GB/s over all GPUs with inputs resident in HBM; K steps timed as one region with CUDA events
+                 on the launching stream, barrier + synchronize on both sides, max over ranks
+  e2e            the same metric through the extension module with HOST inputs: every step copies q, k, v
+                 (and seq_lens) from pinned host memory, runs the kernel and reads the output back
+  roofline       achieved algorithmic GB/s of the flash-decode kernel against the measured HBM copy bandwidth
+  cpu_baseline   the reference's PyTorch attention path (scaled_dot_product_attention, bf16, on the CPU tensors)
+                 timed on this box's host cores over a bounded number of passes
+  clocks         SM clock and throttle reasons sampled through NVML while the GPU was busy
+
+L2 hygiene: every step reads a different one of 8 KV caches (1.07 GB in total, L2 is 126 MB), so a cache is
+cold again when its turn comes.  With --impl reference the CPU baseline alone is run and reported.
+Multi-GPU (launched by torch.distributed.run, one rank per GPU): C2 is weak-scaled, every rank owns a batch
+of 16 sequences and no data crosses GPUs; C3 (--workload c3) shards the KV sequence across ranks and merges
+the per-rank (o, lse) pairs after one all-gather.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+from __graft_entry__ import load_package  # noqa: E402
+
+N_ROTATE = 8
+FALLBACK_PEAK_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_kernel launch on the C2 workload, from the
+# ncu capture summarised in profiles/ (None until a capture of the current kernel exists).
+C2_TRAFFIC_BYTES = None
+
+
+def hbm_peak():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML every ~5 ms in a thread."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+        0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._marks = {}
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and all(v.strip().isdigit() for v in vis.split(",")) else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.nv = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report that, never fail the bench
+            self.nv = None
+            self.err = repr(e)
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, rs))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def mark(self, name):
+        self._marks[name] = time.perf_counter()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.nv:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable: " + self.err}
+        t0, t1 = self._marks.get("t0"), self._marks.get("t1")
+        timed = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1]
+        window = "timed region"
+        if len(timed) < 3:  # region shorter than the sampling period: use every sample taken under load
+            w0 = self._marks.get("w0", 0)
+            timed = [s for s in self.samples if s[0] >= w0]
+            window = "warm-up + timed region"
+        if not timed:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "no samples"}
+        mhz = sorted(s[1] for s in timed)
+        bits = 0
+        for s in timed:
+            bits |= s[2]
+        reasons = [n for b, n in self.REASONS.items() if bits & b]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(timed), "window": window}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def make_decode_workload(name: str, rank: int, world: int):
+    """Returns (case on CPU, description).  Values are seeded N(0,1) in bf16 (synthetic data)."""
+    from oracle import inputs
+
+    if name == "c2":
+        case = inputs.config2(seed=42 + rank)
+        desc = "C2 batched decode attention: B=16/GPU, Hq=32, Hkv=8, D=128, len~U[1024,2048], cache padded to 2048, bf16"
+    elif name == "c1":
+        case = inputs.config1(seed=42 + rank)
+        desc = "C1 single decode step: B=1, Hq=32, Hkv=8, D=64, S=256, bf16"
+    elif name == "c3":
+        case = inputs.config3(seed=42)
+        desc = "C3 long-context decode: B=1, Hq=32, Hkv=8, D=128, S=131072, bf16, KV sequence sharded over the GPUs"
+    else:
+        raise ValueError(name)
+    return case, desc
+
+
+def kv_bytes(case) -> int:
+    """2 (K,V) * 2 bytes * Hkv * D * sum(len): benchmark_kernel.py:48."""
+    B, Hkv, S, D = case.k.shape
+    tokens = int(case.seq_lens.clamp(0, S).sum()) if case.seq_lens is not None else B * S
+    return 2 * 2 * Hkv * D * tokens
+
+
+def cpu_attention_pass(case):
+    from oracle import attention
+
+    return attention.sdpa_reference(case.q, case.k, case.v, case.seq_lens, dtype=torch.bfloat16)
+
+
+def time_cpu_baseline(case, budget_s: float = 12.0, max_passes: int = 20):
+    """Times the reference's CPU attention call on a bounded number of passes over the same batch."""
+    cpu_attention_pass(case)  # warm-up (thread pool, allocator)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < max_passes and (time.perf_counter() < t_end or len(times) < 2):
+        t = time.perf_counter()
+        cpu_attention_pass(case)
+        times.append(time.perf_counter() - t)
+    best = sorted(times)[len(times) // 2]
+    return kv_bytes(case) / best / 1e9, len(times), best
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference_arm(args, rank, world):
+    """The reference's own CPU implementation of the path, timed on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    case, desc = make_decode_workload(args.workload if args.workload in ("c1", "c2", "c3") else "c2", 0, 1)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_attention_pass(case)
+    steps = max(1, min(args.steps, 10))
+    t = time.perf_counter()
+    for _ in range(steps):
+        cpu_attention_pass(case)
+    dt = (time.perf_counter() - t) / steps
+    val = kv_bytes(case) / dt / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "flash-decode HBM GB/s", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc.replace("/GPU", ""), "note": "F.scaled_dot_product_attention(enable_gqa=True) with a "
+                   "length mask on the bf16 CPU tensors: the reference's PyTorch attention path (model.py:115-116)"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "reference",
+                         "sample": f"{steps} full passes over one batch, median-free mean; os.cpu_count()={os.cpu_count()}"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "rmsnorm", "rope"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--max-ctas", type=int, default=0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = load_package()
+    ext = pkg.extension()  # no fallback: raises if the CUDA extension is not built
+
+    if args.workload in ("rmsnorm", "rope"):
+        line = bench_pre_attention(args, ext, pkg, dev, rank, world)
+    else:
+        line = bench_decode(args, ext, pkg, dev, rank, world)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def sync_all(world):
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int, dev) -> float:
+    import torch.distributed as dist
+
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int, dev) -> float:
+    import torch.distributed as dist
+
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def bench_decode(args, ext, pkg, dev, rank, world):
+    case, desc = make_decode_workload(args.workload, rank, world)
+    sharded_seq = args.workload == "c3" and world > 1
+    if sharded_seq:
+        lo, hi = pkg.sharding.kv_shard_bounds(case.k.shape[2], world)[rank]
+        from oracle.inputs import DecodeCase
+
+        full_bytes = kv_bytes(case)
+        case = DecodeCase(case.q, case.k[:, :, lo:hi], case.v[:, :, lo:hi], None)
+    my_bytes = kv_bytes(case)
+
+    # ---- device-resident inputs: N_ROTATE distinct KV caches so that each step finds L2 cold ----
+    q = case.q.to(dev)
+    lens = case.seq_lens.to(dev) if case.seq_lens is not None else None
+    n_rot = N_ROTATE if args.workload != "c3" else 2
+    ks, vs = [], []
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    for i in range(n_rot):
+        if i == 0:
+            ks.append(case.k.to(dev))
+            vs.append(case.v.to(dev))
+        else:  # same shape, strides and distribution, different values
+            B, Hkv, S, D = case.k.shape
+            ks.append(torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.float32).bfloat16().transpose(1, 2))
+            vs.append(torch.randn(B, S, Hkv, D, generator=g, device=dev, dtype=torch.float32).bfloat16().transpose(1, 2))
+    rot_bytes = sum(k.numel() * 2 * 2 for k in ks)
+    out = torch.empty_like(q)
+
+    def step(i):
+        j = i % n_rot
+        if sharded_seq:
+            return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
+        return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sampler.mark("w0")
+    for i in range(args.warmup):
+        step(i)
+    sync_all(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark("t0")
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    end.record()
+    torch.cuda.synchronize()
+    sampler.mark("t1")
+    sync_all(world)
+    sampler.stop()
+    ms_total = start.elapsed_time(end)
+    ms_max = max_over_ranks(ms_total, world, dev)
+    status = ext.flash_decode_status(q)
+    if status != 0:
+        raise RuntimeError(f"device-side wait ran out (status {status})")
+    total_bytes = full_bytes if sharded_seq else sum_over_ranks(float(my_bytes), world, dev)
+    value = total_bytes * args.steps / (ms_max * 1e-3) / 1e9
+    ms_per_step = ms_max / args.steps
+
+    # ---- roofline of the flash-decode kernel: algorithmic bytes of one launch / its average duration ----
+    peak, peak_kind = hbm_peak()
+    launch_ms = ms_total / args.steps
+    achieved = my_bytes / (launch_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": C2_TRAFFIC_BYTES if args.workload == "c2" else None, "peak_kind": peak_kind,
+                "kernel": "flash_decode_kernel", "algorithmic_bytes_per_launch": my_bytes,
+                "frac_of_8TBs_nominal": achieved / 8000.0}
+    if sharded_seq:
+        roofline["note"] = "per-rank shard; the step also holds one all_gather and the lse_merge kernel"
+
+    # ---- end to end through the extension with host buffers (pinned), copies inside the timed region ----
+    hq, hk, hv = case.q.contiguous().pin_memory(), case.k.pin_memory(), case.v.pin_memory()
+    hl = case.seq_lens.pin_memory() if case.seq_lens is not None else None
+    hout = torch.empty_like(case.q).pin_memory()
+    h2d = hq.numel() * 2 + hk.numel() * 2 + hv.numel() * 2 + (hl.numel() * 4 if hl is not None else 0)
+    d2h = hout.numel() * 2
+
+    def e2e_step():
+        dq = hq.to(dev, non_blocking=True)
+        dk = hk.to(dev, non_blocking=True)
+        dv = hv.to(dev, non_blocking=True)
+        dl = hl.to(dev, non_blocking=True) if hl is not None else None
+        if sharded_seq:
+            o = pkg.sharding.decode_kv_sharded(ext, dq, dk, dv, None)
+        else:
+            o = ext.flash_attention_decode(dq, dk, dv, seq_lens=dl)
+        hout.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    sync_all(world)
+    e_steps = max(1, args.e2e_steps)
+    start.record()
+    for _ in range(e_steps):
+        e2e_step()
+    end.record()
+    torch.cuda.synchronize()
+    sync_all(world)
+    e_ms = max_over_ranks(start.elapsed_time(end), world, dev)
+    e2e_val = total_bytes * e_steps / (e_ms * 1e-3) / 1e9
+    e2e = {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "steps": e_steps, "ms_per_step": e_ms / e_steps}
+
+    # ---- CPU baseline on this box's host cores (rank 0, N=1 only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, passes, sec = time_cpu_baseline(case)
+        cpu = {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "reference",
+               "sample": f"median of {passes} full passes of F.scaled_dot_product_attention (bf16, enable_gqa, length "
+                         f"mask) over the same batch, {sec * 1e3:.1f} ms each; os.cpu_count()={os.cpu_count()}"}
+
+    B, Hkv, S, D = case.k.shape
+    line = {
+        "metric": "flash-decode HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if sharded_seq else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
+                   "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
+                   "parallelism": ("kv-sequence sharded x%d + lse merge" % world) if sharded_seq else
+                                  ("data-parallel x%d, no collective" % world),
+                   "pct_of_8TBs_nominal_per_gpu": 100.0 * achieved / 8000.0},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * (2 if sharded_seq else 1),
+        "clocks": sampler.summary(),
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    return line
+
+
+def bench_pre_attention(args, ext, pkg, dev, rank, world):
+    """C4: RMSNorm over [4096, 2048] tokens, or fused RoPE + KV-cache write of q (32x64) and k, v (8x64)."""
+    from oracle import inputs
+
+    x, w, eps, qkv = inputs.config4(seed=42 + rank)
+    Hq, Hkv, D, B, S = 32, 8, 64, 2, 2048
+    freq = pkg.rope_table.precompute_freqs_cis(D, S, **{k: v for k, v in inputs.ROPE_CONFIG4.items()}).to(dev)
+    n_rot = 12  # 12 x (33.5 | 50 MB) > 126 MB L2
+    if args.workload == "rmsnorm":
+        xs = [x.to(dev) if i == 0 else torch.randn_like(x.float(), device=dev).bfloat16() for i in range(n_rot)]
+        dw = w.to(dev)
+        nbytes = 2 * x.numel() * 2 + w.numel() * 2
+        step = lambda i: ext.rms_norm(xs[i % n_rot], dw, eps)
+        kernel = "rms_norm_kernel"
+        desc = "C4 RMSNorm: tokens 4096 x hidden 2048 bf16, eps 1e-5"
+    else:
+        qs = [qkv.to(dev) if i == 0 else torch.randn_like(qkv.float(), device=dev).bfloat16() for i in range(n_rot)]
+        ck = torch.zeros(B, S, Hkv, D, dtype=torch.bfloat16, device=dev)
+        cv = torch.zeros_like(ck)
+        nbytes = 2 * qkv.numel() * 2 + freq.numel() * 4
+        step = lambda i: ext.rot_embed_kv_cache(qs[i % n_rot], freq, ck, cv, 0, Hq, Hkv)
+        kernel = "rot_embed_kv_cache_kernel"
+        desc = "C4 fused RoPE + KV-cache write: tokens 4096, q 32x64, k/v 8x64 bf16, Llama-3 scaling factor 32"
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    sampler.mark("w0")
+    for i in range(args.warmup):
+        step(i)
+    sync_all(world)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark("t0")
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    end.record()
+    torch.cuda.synchronize()
+    sampler.mark("t1")
+    sync_all(world)
+    sampler.stop()
+    ms_total = start.elapsed_time(end)
+    ms_max = max_over_ranks(ms_total, world, dev)
+    value = nbytes * world * args.steps / (ms_max * 1e-3) / 1e9
+    peak, peak_kind = hbm_peak()
+    achieved = nbytes / (ms_total / args.steps * 1e-3) / 1e9
+    return {
+        "metric": "pre-attention HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "l2": f"{n_rot} rotating inputs > 126 MB L2", "bytes_per_step": nbytes,
+                   "note": "includes the output allocation of the reference-shaped call (torch caching allocator)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": kernel},
+        "gpu_launches": args.steps, "clocks": sampler.summary(),
+    }
+
+
+if __name__ == "__main__":
+    main()

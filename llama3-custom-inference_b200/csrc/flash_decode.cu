@@ -69,7 +69,7 @@ struct FdParams {
   int B, Hq, Hkv, R, n_seq, n_groups;
   long long q_sb, q_sh, o_sb, o_sh;
   float scale_log2e;
-  int rec_floats;       // floats per record = R * (D + 2)
+  int rec_floats;       // floats per record: R * (D + 2), padded to a multiple of 32
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -611,6 +611,10 @@ int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, i
   return L3CI_OK;
 }
 
+// Floats of one (m, l, o) record: R rows of D outputs, then R maxima and R sums, padded to 128 bytes so
+// that every record (and its 16-byte vector reads) stays aligned.
+int record_floats(int R, int D) { return (R * (D + 2) + 31) & ~31; }
+
 size_t counters_bytes(int B, int Hkv) { return (((size_t)B * Hkv * sizeof(int)) + 255) & ~(size_t)255; }
 
 size_t smem_bytes(int HG, int B, bool ragged) {
@@ -646,7 +650,7 @@ extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t
   if (sms <= 0) return 0;
   // Records: 2 per CTA per warp; CTAs * warps is 8 per SM whatever the head grouping is.
   const size_t records = (size_t)fd_max_ctas(sms, fd_head_group(Hkv)) * fd_head_group(Hkv) * 2;
-  return kHeaderBytes + counters_bytes(B, Hkv) + records * (size_t)R * (D + 2) * sizeof(float);
+  return kHeaderBytes + counters_bytes(B, Hkv) + records * (size_t)record_floats(R, D) * sizeof(float);
 }
 
 extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) {
@@ -722,7 +726,7 @@ extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) {
   p.q_sb = a->q_sb; p.q_sh = a->q_sh; p.o_sb = a->o_sb; p.o_sh = a->o_sh;
   const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)D);
   p.scale_log2e = scale * 1.4426950408889634f;
-  p.rec_floats = R * (D + 2);
+  p.rec_floats = record_floats(R, D);
 
   if (D == 64) {
     return R > 8 ? launch_fd<64, true>(kmap, vmap, p, grid, HG, smem, stream)

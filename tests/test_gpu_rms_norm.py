@@ -1,0 +1,65 @@
+"""RMSNorm kernel through the C ABI against the fp32 oracle: at most 1 bf16 ulp."""
+import pytest
+import torch
+
+from oracle import compare, inputs
+from oracle.rms_norm import rms_norm_reference
+
+pytestmark = pytest.mark.gpu
+MAX_ULP = 1  # stated tolerance for RMSNorm
+
+
+def _check(capi, x, w, eps):
+    got = capi.rms_norm(x, w, eps)
+    torch.cuda.synchronize()
+    want = rms_norm_reference(x, w, eps)
+    assert got.shape == x.shape and got.dtype == torch.bfloat16
+    ulp = compare.bf16_ulp_distance(got.cpu(), want)
+    assert int(ulp.max()) <= MAX_ULP, f"max ulp {int(ulp.max())}, {(ulp > MAX_ULP).float().mean().item():.2%} beyond tolerance"
+    return float((ulp > 0).float().mean())
+
+
+def test_config4_token_batch(capi, device):
+    x, w, eps, _ = inputs.config4()
+    frac = _check(capi, x.to(device), w.to(device), eps)
+    assert frac < 0.05  # almost every element is the identical bf16 value
+
+
+@pytest.mark.parametrize("rows,embed", [(1, 2048), (64, 2048), (7, 8), (5, 64), (3, 256), (33, 1000), (9, 4096),
+                                        (4, 8192), (3, 16384), (2, 5120), (130, 2056), (2, 65536)])
+def test_shapes(capi, device, rows, embed):
+    g = torch.Generator().manual_seed(rows * 131 + embed)
+    x = (torch.randn(rows, 1, embed, generator=g) * 3).bfloat16().to(device)
+    w = (1 + 0.1 * torch.randn(embed, generator=g)).bfloat16().to(device)
+    _check(capi, x, w, 1e-5)
+
+
+def test_zero_row_and_large_values(capi, device):
+    x = torch.zeros(4, 1, 2048, dtype=torch.bfloat16, device=device)
+    x[1] = 1e4
+    x[2, 0, ::2] = -3e-3
+    w = torch.ones(2048, dtype=torch.bfloat16, device=device)
+    _check(capi, x, w, 1e-5)
+    _check(capi, x, w, 1e-6)
+
+
+def test_strided_rows_and_untouched_padding(capi, device):
+    rows, embed, pitch = 10, 512, 640
+    g = torch.Generator().manual_seed(1)
+    xbuf = torch.randn(rows, pitch, generator=g).bfloat16().to(device)
+    w = torch.randn(embed, generator=g).bfloat16().to(device)
+    obuf = torch.full((rows, pitch), 7.0, dtype=torch.bfloat16, device=device)
+    st = capi.load().l3ci_rms_norm(xbuf.data_ptr(), w.data_ptr(), obuf.data_ptr(), rows, embed, pitch, pitch, 1e-5,
+                                   torch.cuda.current_stream().cuda_stream)
+    assert st == capi.OK
+    torch.cuda.synchronize()
+    want = rms_norm_reference(xbuf[:, :embed], w, 1e-5)
+    assert compare.max_bf16_ulp(obuf[:, :embed].contiguous(), want) <= MAX_ULP
+    assert (obuf[:, embed:] == 7.0).all()
+
+
+def test_errors(capi, device):
+    lib = capi.load()
+    x = torch.zeros(2, 16, dtype=torch.bfloat16, device=device)
+    assert lib.l3ci_rms_norm(x.data_ptr() + 2, x.data_ptr(), x.data_ptr(), 1, 8, 8, 8, 1e-5, None) == capi.ERR_ALIGNMENT
+    assert lib.l3ci_rms_norm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 12, 12, 12, 1e-5, None) == capi.ERR_UNSUPPORTED
