@@ -319,7 +319,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
             return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
         return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(dev.index or 0)
     sampler.start()
     sampler.mark("w0")
     for i in range(args.warmup):

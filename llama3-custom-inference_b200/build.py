@@ -98,7 +98,10 @@ def build_extension(force: bool = False) -> Path:
     src = PKG / "custom_kernels" / "main.cpp"
     if not force and _newer(EXT, [src, LIB] + _headers()):
         return EXT
-    cxx = os.environ.get("CXX", "g++")
+    # The system g++ on PATH, not $CXX: a toolchain wrapper that links libstdc++ statically puts a second copy
+    # of the iostream locale facets into the module, and formatting an integer into an error message
+    # then crashes inside a process that already has the shared libstdc++ (torch) loaded.
+    cxx = os.environ.get("L3CI_CXX") or shutil.which("g++") or "g++"
     torch_lib = Path(torch.__file__).parent / "lib"
     includes = cpp_extension.include_paths(device_type="cuda")
     includes += [sysconfig.get_paths()["include"], str(INCLUDE)]
@@ -112,6 +115,9 @@ def build_extension(force: bool = False) -> Path:
             "-L", str(torch_lib), "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
             "-Wl,-rpath," + str(torch_lib)]
     _run(cmd)
+    syms = subprocess.run(["nm", "-D", "--defined-only", str(EXT)], stdout=subprocess.PIPE, text=True).stdout
+    if "_ZNSt6locale" in syms or "_txnal_" in syms:
+        raise RuntimeError(f"{EXT} contains a static copy of libstdc++ (built with {cxx}); use the system g++")
     return EXT
 
 

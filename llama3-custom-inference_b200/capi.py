@@ -233,3 +233,4 @@ def lse_merge(o_parts, lse_parts):
         _check(load().l3ci_lse_merge(o_parts.data_ptr(), lse_parts.data_ptr(), out.data_ptr(), P, B, Hq, D,
                                      out.stride(0), out.stride(1), _stream(o_parts)), "l3ci_lse_merge")
     return out
+

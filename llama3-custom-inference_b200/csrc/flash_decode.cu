@@ -18,10 +18,15 @@
 //    group padded to the 16-row A tile), which leaves the issue slots to the memory pipeline.
 //    Online softmax statistics live in registers; row reductions are 4-lane shuffles.
 //  * A (sequence, head) unit that is cut by a range boundary leaves an fp32 (m, l, o) record per
-//    CTA; the warp that arrives last (one atomic counter per unit) merges the records and writes
-//    the result.  The counter is reset by that warp, so scratch stays ready for the next call.
-//  * Every wait on an mbarrier is bounded; if it runs out the warp records L3CI_ERR_DEVICE_WAIT in
-//    the scratch header and leaves.
+//    CTA and a count on the unit's arrival counter.  When a warp has streamed its whole range it
+//    comes back to the (at most two) shared units it took part in, waits until all their records
+//    are there and merges ITS SLICE of the output columns, lanes spread over the records, so the
+//    merge costs one or two memory round trips however many CTAs share the unit.  The grid is
+//    launched cooperatively (never more CTAs than fit on the device at once), which is what makes
+//    waiting on other CTAs legitimate.  The last warp to leave resets the counter, so scratch stays
+//    ready for the next call.
+//  * Every wait (on an mbarrier, on an arrival counter) is bounded; if it runs out the warp records
+//    L3CI_ERR_DEVICE_WAIT in the scratch header and moves on.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -56,6 +61,18 @@ struct FdCfg {
   static constexpr int NT_O = D / 8;       // 8-column output tiles
   static constexpr int KS_PV = kTile / 16; // k-steps of P.V
 };
+
+// Build with -DL3CI_FD_TRACE to record, per warp, %globaltimer at five points of the kernel into a
+// buffer registered with l3ci_debug_set_trace (development aid; absent from normal builds).
+#ifdef L3CI_FD_TRACE
+__device__ unsigned long long* g_fd_trace = nullptr;
+#define FD_TRACE(slot)                                                                       \
+  do {                                                                                       \
+    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 8 + (slot)] = global_ns(); \
+  } while (0)
+#else
+#define FD_TRACE(slot) do { } while (0)
+#endif
 
 struct FdParams {
   const __nv_bfloat16* q;
@@ -162,6 +179,128 @@ __device__ __forceinline__ uint32_t ld_global_u32(const __nv_bfloat16* p) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Folding of partial attention states.  A state is (m, l, o): running maximum of the scaled scores
+// (log2 domain), sum of exp2(score - m), and the unnormalised output.  Two states fold as
+//   m' = max(m1, m2),  l' = l1*2^(m1-m') + l2*2^(m2-m'),  o' likewise.
+// ---------------------------------------------------------------------------------------------
+struct Chunk4 {
+  float m, l, o[4];
+  __device__ __forceinline__ void clear() { m = -INFINITY; l = 0.f; o[0] = o[1] = o[2] = o[3] = 0.f; }
+  __device__ __forceinline__ void fold(float m2, float l2, float x, float y, float z, float w) {
+    const float mn = fmaxf(m, m2);
+    const float mu = mn == -INFINITY ? 0.f : mn;
+    const float a = fast_exp2(m - mu), b = fast_exp2(m2 - mu);
+    m = mn;
+    l = fmaf(l, a, l2 * b);
+    o[0] = fmaf(o[0], a, x * b); o[1] = fmaf(o[1], a, y * b);
+    o[2] = fmaf(o[2], a, z * b); o[3] = fmaf(o[3], a, w * b);
+  }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Merge of a unit shared by the n CTAs first_cta .. first_cta + n - 1, as done by participant `me`
+// (0-based) for head-warp `warp`.  The unit's R x D outputs are cut into 4-column chunks and the
+// chunks are dealt evenly to the n participants.  A participant spreads its lanes over its chunks,
+// lpc lanes per chunk (a power of two, as many as 32 lanes allow); the lanes of a chunk take every
+// lpc-th record, fold them in registers (up to 8 records' loads in flight per lane) and meet in a
+// shuffle butterfly.  So a unit shared by many CTAs costs each of them a handful of loads, and a
+// unit shared by two or three costs one round of loads.  Returns false if the wait ran out.
+template <int D>
+__device__ __noinline__ bool merge_slice(const FdParams& p, int b, int head, int first_cta, int n, int me, int HG,
+                                         int warp, int lane) {
+  constexpr int C4 = D / 4;  // chunks per output row (a power of two)
+  constexpr int kBatch = 8;
+  const int R = p.R;
+  const int* counter = p.counters + b * p.Hkv + head;
+
+  // ---- wait (bounded) until every participant has published its record ----
+  // Every lane reads the counter with acquire semantics (one request per warp), so the record loads
+  // below need no further fence.
+  {
+    bool there = ld_acquire_gpu(counter) >= n;
+    if (!__all_sync(kFullMask, there)) {
+      const unsigned long long t0 = global_ns();
+      for (uint32_t it = 0;; ++it) {
+        __nanosleep(32);
+        there = ld_acquire_gpu(counter) >= n;
+        if (__all_sync(kFullMask, there)) break;
+        if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > kWaitLimitNs)) {
+          if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+          return false;
+        }
+      }
+    }
+  }
+
+  const int Q = R * C4;
+  const int q0 = (int)(((long long)me * Q) / n), q1 = (int)(((long long)(me + 1) * Q) / n);
+  const int chunks = q1 - q0;
+  int lg = 5;  // log2(lanes per chunk)
+  while (lg > 0 && (chunks << lg) > kWarp) --lg;
+  const int lpc = 1 << lg;
+  const int per_pass = kWarp >> lg;  // chunks per pass of the warp
+  const int sub = lane & (lpc - 1);
+  const long long hq0 = (long long)head * R;
+  const float* rec0 = p.records + (long long)fd_record_index(first_cta, first_cta, HG, warp) * p.rec_floats;
+  // records of CTAs after the first sit at position 0 of their CTA: a constant stride apart
+  const long long rec_stride = 2LL * HG * p.rec_floats;
+  const float* rec1 = p.records + (long long)fd_record_index(first_cta + 1, first_cta, HG, warp) * p.rec_floats;
+
+  for (int base = 0; base < chunks; base += per_pass) {
+    const int q = q0 + base + (lane >> lg);
+    const bool mine = q < q1;
+    const int r = q / C4, d = (q & (C4 - 1)) * 4;
+    Chunk4 acc;
+    acc.clear();
+    for (int k0 = 0; k0 < n; k0 += kBatch * lpc) {
+      float m[kBatch], l[kBatch];
+      float4 v[kBatch];
+      bool act[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int rec = k0 + sub + j * lpc;
+        act[j] = mine && rec < n;
+        if (act[j]) {
+          const float* rc = rec == 0 ? rec0 : rec1 + (rec - 1) * rec_stride;
+          m[j] = __ldcg(rc + R * D + r);
+          l[j] = __ldcg(rc + R * D + R + r);
+          v[j] = __ldcg(reinterpret_cast<const float4*>(rc + r * D + d));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        if (act[j]) acc.fold(m[j], l[j], v[j].x, v[j].y, v[j].z, v[j].w);
+    }
+    for (int off = lpc >> 1; off >= 1; off >>= 1) {
+      const float m2 = __shfl_xor_sync(kFullMask, acc.m, off), l2 = __shfl_xor_sync(kFullMask, acc.l, off);
+      const float x = __shfl_xor_sync(kFullMask, acc.o[0], off), y = __shfl_xor_sync(kFullMask, acc.o[1], off);
+      const float z = __shfl_xor_sync(kFullMask, acc.o[2], off), w = __shfl_xor_sync(kFullMask, acc.o[3], off);
+      acc.fold(m2, l2, x, y, z, w);
+    }
+    if (mine && sub == 0) {
+      const float inv = acc.l > 0.f ? 1.f / acc.l : 0.f;
+      if (p.out) {
+        __nv_bfloat16* ob = p.out + (long long)b * p.o_sb + (hq0 + r) * p.o_sh + d;
+        *reinterpret_cast<uint32_t*>(ob) = pack_bf16x2(acc.o[0] * inv, acc.o[1] * inv);
+        *reinterpret_cast<uint32_t*>(ob + 2) = pack_bf16x2(acc.o[2] * inv, acc.o[3] * inv);
+      }
+      if (p.o_partial) {
+        float* ob = p.o_partial + ((long long)b * p.Hq + hq0 + r) * D + d;
+        *reinterpret_cast<float4*>(ob) = make_float4(acc.o[0] * inv, acc.o[1] * inv, acc.o[2] * inv, acc.o[3] * inv);
+        if (d == 0)
+          p.lse[(long long)b * p.Hq + hq0 + r] = acc.l > 0.f ? (acc.m + log2f(acc.l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------
 // The kernel.  blockDim.x = 32 * HG; dynamic shared memory (1024-byte aligned by hand):
 //   [HG][kStages][kStageBytes] tiles | [HG][kStages] mbarriers | prefix[B+1] | len[B]
 // ---------------------------------------------------------------------------------------------
@@ -176,6 +315,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   const int HG = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  FD_TRACE(0);
   const int gid = lane >> 2;  // MMA row within the 8-row half
   const int tig = lane & 3;   // MMA column pair
 
@@ -199,7 +339,27 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   wk.B = p.B; wk.n_groups = p.n_groups; wk.n_seq = p.n_seq; wk.tile = C::kTile;
   wk.pref = nullptr; wk.lens = nullptr;
   int total;
-  if (p.seq_lens) {
+  if (p.seq_lens && p.B <= kWarp) {
+    // Up to 32 sequences: every warp scans the lengths by itself (all warps write the same values to the
+    // shared arrays), which saves the two CTA-wide barriers of the general path.
+    const int len = lane < p.B ? min(max(__ldg(p.seq_lens + lane), 0), p.n_seq) : 0;
+    const int cols = lane < p.B ? p.n_groups * fd_tiles(len, C::kTile) : 0;
+    int incl = cols;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int n = __shfl_up_sync(kFullMask, incl, d);
+      if (lane >= d) incl += n;
+    }
+    if (lane < p.B) {
+      s_len[lane] = len;
+      s_pref[lane + 1] = incl;
+    }
+    if (lane == 0) s_pref[0] = 0;
+    __syncwarp();
+    wk.pref = s_pref;
+    wk.lens = s_len;
+    total = __shfl_sync(kFullMask, incl, p.B - 1);
+  } else if (p.seq_lens) {
     for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
       const int len = min(max(__ldg(p.seq_lens + b), 0), p.n_seq);
       s_len[b] = len;
@@ -258,6 +418,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       tma_load_4d(dst + C::kKBytes + h * C::kBoxBytes, &vmap, bar, h * 64, tok, head, cu.b, policy);
   };
 
+  FD_TRACE(1);
   FdCursor prod = wk.seek(c0);
   FdCursor cons = prod;
   int issued = 0;
@@ -287,6 +448,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   int k_iter = 0;
   const int R = p.R;
   bool ok = true;
+  int def_b[2], def_head[2], def_first[2], def_n[2] = {0, 0};  // shared units to merge at the end
 
   while (cons.col < c1) {
     const int head = cons.g * HG + warp;
@@ -312,6 +474,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     const int stage = k_iter % kStages;
     const uint32_t parity = (k_iter / kStages) & 1;
     if (!mbar_wait_bounded(bar0 + stage * 8, parity)) { ok = false; break; }
+    if (k_iter == 0) FD_TRACE(2);
     const uint32_t kb = stage0 + stage * kStageBytes;
     const uint32_t vb = kb + C::kKBytes;
 
@@ -469,7 +632,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
           }
         }
       } else {
-        // Leave an unnormalised record; the last warp to arrive for this unit merges them all.
+        // Shared with other CTAs: leave an unnormalised record and a count on the unit's arrival counter.
         float* rec = p.records + (long long)fd_record_index(cta, cfirst, HG, warp) * p.rec_floats;
 #pragma unroll
         for (int nt = 0; nt < C::NT_O; ++nt) {
@@ -491,59 +654,13 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
             }
           }
         }
-        __threadfence();
-        __syncwarp();
-        int* counter = p.counters + cons.b * p.Hkv + head;
-        int last = 0;
-        if (lane == 0) {
-          const int n = clast - cfirst + 1;
-          last = atomicAdd(counter, 1) == n - 1;
-          if (last) *counter = 0;  // ready for the next launch
-        }
-        last = __shfl_sync(kFullMask, last, 0);
-        if (last) {
-          __threadfence();
-          constexpr int EPL = D / 32;  // output elements per lane
-          for (int r = 0; r < R; ++r) {
-            float M = -INFINITY;
-            for (int c = cfirst; c <= clast; ++c) {
-              const float* rc = p.records + (long long)fd_record_index(c, cfirst, HG, warp) * p.rec_floats;
-              M = fmaxf(M, __ldcg(rc + R * D + r));
-            }
-            const float Mu = M == -INFINITY ? 0.f : M;
-            float acc[EPL];
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
-            float L = 0.f;
-            for (int c = cfirst; c <= clast; ++c) {
-              const float* rc = p.records + (long long)fd_record_index(c, cfirst, HG, warp) * p.rec_floats;
-              const float w = fast_exp2(__ldcg(rc + R * D + r) - Mu);
-              L = fmaf(__ldcg(rc + R * D + R + r), w, L);
-              if constexpr (EPL == 4) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(rc + r * D) + lane);
-                acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
-                acc[2] = fmaf(v.z, w, acc[2]); acc[3] = fmaf(v.w, w, acc[3]);
-              } else {
-                const float2 v = __ldcg(reinterpret_cast<const float2*>(rc + r * D) + lane);
-                acc[0] = fmaf(v.x, w, acc[0]); acc[1] = fmaf(v.y, w, acc[1]);
-              }
-            }
-            const float inv = L > 0.f ? 1.f / L : 0.f;
-            if (p.out) {
-              __nv_bfloat16* ob = p.out + (long long)cons.b * p.o_sb + (hq0 + r) * p.o_sh + lane * EPL;
-#pragma unroll
-              for (int e = 0; e < EPL; e += 2)
-                *reinterpret_cast<uint32_t*>(ob + e) = pack_bf16x2(acc[e] * inv, acc[e + 1] * inv);
-            }
-            if (p.o_partial) {
-              float* ob = p.o_partial + ((long long)cons.b * p.Hq + hq0 + r) * D + lane * EPL;
-#pragma unroll
-              for (int e = 0; e < EPL; ++e) ob[e] = acc[e] * inv;
-              if (lane == 0)
-                p.lse[(long long)cons.b * p.Hq + hq0 + r] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
-            }
-          }
-        }
+        // The record is announced (and the unit merged) after the whole range has been streamed.  A warp
+        // has at most two such units: one that began in an earlier CTA, one that continues in the next.
+        const int which = cta == cfirst ? 1 : 0;
+        def_b[which] = cons.b;
+        def_head[which] = head;
+        def_first[which] = cfirst;
+        def_n[which] = clast - cfirst + 1;
       }
     }
     wk.advance(cons);
@@ -551,11 +668,43 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 
   if (!ok) {
     // A bulk copy never signalled.  Record it, then give the other copies of this warp a bounded
-    // chance to land before the shared memory goes away.
+    // chance to land before the shared memory goes away.  Shared units are left unmerged.
     if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
     for (int k = k_iter + 1; k < issued; ++k)
       (void)mbar_wait_bounded(bar0 + (k % kStages) * 8, (k / kStages) & 1);
+    return;
   }
+  FD_TRACE(3);
+  // ---- shared units ----
+  // Announce this warp's records (one fence for both), merge this CTA's slice of each unit once every
+  // participant has announced, then leave: the last participant to leave zeroes the counter.
+  if (def_n[0] > 1 || def_n[1] > 1) {
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+        if (def_n[w] > 1) atomicAdd(p.counters + def_b[w] * p.Hkv + def_head[w], 1);
+    }
+    FD_TRACE(5);
+    bool merged[2] = {false, false};
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+      if (def_n[w] > 1)
+        merged[w] = merge_slice<D>(p, def_b[w], def_head[w], def_first[w], def_n[w], cta - def_first[w], HG, warp, lane);
+    FD_TRACE(6);
+    __syncwarp();
+    if (lane == 0) {
+      int left[2] = {0, 0};
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+        if (merged[w]) left[w] = atomicAdd(p.counters + def_b[w] * p.Hkv + def_head[w], 1);
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+        if (merged[w] && left[w] == 2 * def_n[w] - 1) p.counters[def_b[w] * p.Hkv + def_head[w]] = 0;
+    }
+  }
+  FD_TRACE(4);
 }
 
 // Writes zeros for a call without any cached token.
@@ -623,24 +772,52 @@ size_t smem_bytes(int HG, int B, bool ragged) {
   return s;
 }
 
+// Launches the kernel cooperatively: the runtime refuses a grid that cannot be resident all at once,
+// which the kernel relies on when a warp waits for the records of other CTAs.  The grid is clamped to
+// what fits (blocks per SM from the occupancy calculator, cached per device and launch shape).
 template <int D, bool RHI>
 int launch_fd(const CUtensorMap& kmap, const CUtensorMap& vmap, const FdParams& p, int grid, int HG,
               size_t smem, cudaStream_t stream) {
-  static size_t configured[64] = {0};
+  struct Cached { size_t configured = 0; int block = 0; size_t smem = 0; int per_sm = 0; };
+  static Cached cache[64];
+  static std::mutex mu;
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 64 || configured[dev] < smem) {
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_kernel<D, RHI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
-    if (dev < 64) configured[dev] = smem;
+  const int block = HG * 32;
+  int per_sm = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    Cached local;
+    Cached& c = dev < 64 ? cache[dev] : local;
+    if (c.configured < smem) {
+      L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_kernel<D, RHI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+      c.configured = smem;
+    }
+    if (c.block != block || c.smem != smem) {
+      L3CI_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&c.per_sm, flash_decode_kernel<D, RHI>, block, smem));
+      c.block = block;
+      c.smem = smem;
+    }
+    per_sm = c.per_sm;
   }
-  flash_decode_kernel<D, RHI><<<grid, HG * 32, smem, stream>>>(kmap, vmap, p);
-  L3CI_CHECK_LAUNCH("flash_decode_kernel");
+  if (per_sm <= 0) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: kernel does not fit on an SM with %zu bytes of shared memory", smem);
+  const int resident = per_sm * sm_count();
+  if (grid > resident) grid = resident;
+  void* args[] = {const_cast<CUtensorMap*>(&kmap), const_cast<CUtensorMap*>(&vmap), const_cast<FdParams*>(&p)};
+  L3CI_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(&flash_decode_kernel<D, RHI>), dim3(grid),
+                                            dim3(block), args, smem, stream));
   return L3CI_OK;
 }
 
 }  // namespace
 }  // namespace l3ci
+
+#ifdef L3CI_FD_TRACE
+extern "C" __attribute__((visibility("default"))) int l3ci_debug_set_trace(unsigned long long* buf) {
+  return (int)cudaMemcpyToSymbol(l3ci::g_fd_trace, &buf, sizeof(buf));
+}
+#endif
 
 extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D) {
   using namespace l3ci;
