@@ -43,9 +43,10 @@ from __graft_entry__ import load_package  # noqa: E402
 
 N_ROTATE = 8
 FALLBACK_PEAK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_kernel launch on the C2 workload, from the
-# ncu capture summarised in profiles/ (None until a capture of the current kernel exists).
-C2_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_kernel launch on the C2 workload (seed 42),
+# from the ncu capture summarised in profiles/flash_decode_c2_full.md: 102.63 MB read + 5.49 MB written.
+C2_TRAFFIC_BYTES = 108_120_000
+C3_TRAFFIC_BYTES = 543_830_000  # profiles/flash_decode_c3_full.md: 537.00 MB read + 6.83 MB written
 
 
 def hbm_peak():
@@ -206,7 +207,7 @@ def run_reference_arm(args, rank, world):
         "config": {"workload": desc.replace("/GPU", ""), "note": "F.scaled_dot_product_attention(enable_gqa=True) with a "
                    "length mask on the bf16 CPU tensors: the reference's PyTorch attention path (model.py:115-116)"},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "reference",
-                         "sample": f"{steps} full passes over one batch, median-free mean; os.cpu_count()={os.cpu_count()}"},
+                         "sample": f"mean of {steps} full passes over one batch; os.cpu_count()={os.cpu_count()}"},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -349,7 +350,8 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     launch_ms = ms_total / args.steps
     achieved = my_bytes / (launch_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": C2_TRAFFIC_BYTES if args.workload == "c2" else None, "peak_kind": peak_kind,
+                "traffic": (C2_TRAFFIC_BYTES if args.workload == "c2" and world == 1 else
+                            C3_TRAFFIC_BYTES if args.workload == "c3" and world == 1 else None), "peak_kind": peak_kind,
                 "kernel": "flash_decode_kernel", "algorithmic_bytes_per_launch": my_bytes,
                 "frac_of_8TBs_nominal": achieved / 8000.0}
     if sharded_seq:

@@ -91,6 +91,20 @@ L3CI_API int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void* q
                                      int64_t cache_sb, int64_t cache_st,
                                      int64_t start_pos, l3ci_stream_t stream);
 
+/* The same pass with the position of every sequence read from device memory: token t of sequence b
+ * sits at position positions[b] + t, takes row positions[b] + t of the WHOLE rotary table
+ * `freq_table` (fp32 [freq_rows, D]) and is written to that row of the caches.  A position outside
+ * the table or beyond cache_len is skipped.  This is the form a decode loop needs when it is captured
+ * in a CUDA graph (no host-side start_pos) or when sequences of a batch are at different positions;
+ * it extends model.py:100-108 / :209, which have one start_pos for the batch. */
+L3CI_API int l3ci_rot_embed_kv_cache_at(const void* qkv, const float* freq_table, int64_t freq_rows,
+                                        void* q_out, void* cache_k, void* cache_v,
+                                        const int32_t* positions,
+                                        int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                                        int64_t qkv_sb, int64_t qkv_st,
+                                        int64_t cache_sb, int64_t cache_st, int64_t cache_len,
+                                        l3ci_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Split-KV flash-decode attention for one query token per sequence over a GQA KV cache.
  * Replaces `flash_attention_decode(query, keys, values)` with its split-KV and combine
@@ -111,7 +125,9 @@ typedef struct l3ci_flash_decode_args {
                             [0, n_seq]); NULL = every sequence has n_seq tokens               */
   void* scratch;         /* >= l3ci_flash_decode_scratch_bytes(...) bytes, 256-byte aligned,
                             zero-filled ONCE before its first use; the kernel leaves it ready
-                            for the next call on the same stream                              */
+                            for the next call on the same stream, of any shape with
+                            B * Hkv <= 65536 (beyond that: zero it again when the shape changes).
+                            Two calls that overlap on the GPU must not share it                */
   size_t scratch_bytes;
   int32_t B, Hq, Hkv, D, n_seq;
   int64_t q_sb, q_sh;

@@ -19,7 +19,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 # Every symbol include/l3ci_b200.h declares.
 EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
-    "l3ci_rms_norm", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache",
+    "l3ci_rms_norm", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_poll",
     "l3ci_lse_merge",
 )
@@ -72,6 +72,8 @@ def load() -> C.CDLL:
     lib.l3ci_rot_embed.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp]
     lib.l3ci_rot_embed_kv_cache.restype = C.c_int
     lib.l3ci_rot_embed_kv_cache.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp]
+    lib.l3ci_rot_embed_kv_cache_at.restype = C.c_int
+    lib.l3ci_rot_embed_kv_cache_at.argtypes = [vp, vp, i64, vp, vp, vp, vp] + [i64] * 10 + [vp]
     lib.l3ci_flash_decode_scratch_bytes.restype = C.c_size_t
     lib.l3ci_flash_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
     lib.l3ci_flash_decode.restype = C.c_int
@@ -144,6 +146,22 @@ def rot_embed_kv_cache(qkv, freq, cache_k, cache_v, start_pos: int, n_head: int,
                                               cache_v.data_ptr(), B, T, n_head, n_kv_head, D, qkv.stride(0),
                                               qkv.stride(1), cache_k.stride(0), cache_k.stride(1), start_pos,
                                               _stream(qkv)), "l3ci_rot_embed_kv_cache")
+    return q_out
+
+
+def rot_embed_kv_cache_at(qkv, freq_table, cache_k, cache_v, positions, n_head: int, n_kv_head: int):
+    """Like `rot_embed_kv_cache`, with per-sequence positions (int32 [B] on the device) and the whole table."""
+    import torch
+
+    B, T, W = qkv.shape
+    D = W // (n_head + 2 * n_kv_head)
+    q_out = torch.empty((B, T, n_head, D), dtype=qkv.dtype, device=qkv.device)
+    with _on(qkv):
+        _check(load().l3ci_rot_embed_kv_cache_at(qkv.data_ptr(), freq_table.data_ptr(), freq_table.shape[0],
+                                                 q_out.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(),
+                                                 positions.data_ptr(), B, T, n_head, n_kv_head, D, qkv.stride(0),
+                                                 qkv.stride(1), cache_k.stride(0), cache_k.stride(1), cache_k.shape[1],
+                                                 _stream(qkv)), "l3ci_rot_embed_kv_cache_at")
     return q_out
 
 

@@ -764,7 +764,16 @@ int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, i
 // that every record (and its 16-byte vector reads) stays aligned.
 int record_floats(int R, int D) { return (R * (D + 2) + 31) & ~31; }
 
-size_t counters_bytes(int B, int Hkv) { return (((size_t)B * Hkv * sizeof(int)) + 255) & ~(size_t)255; }
+// Scratch layout: header | arrival counters | records.  The counter area has the same place and size
+// for every call with up to kFixedCounters (sequence, kv head) units, so a scratch buffer that was zeroed
+// once can serve calls of any shape: counters are left at zero by the kernel, records are written before
+// they are read.  Larger batches get a counter area of their own size (then a change of shape needs the
+// buffer zeroed again).
+constexpr size_t kFixedCounters = 65536;
+size_t counters_bytes(int B, int Hkv) {
+  const size_t units = (size_t)B * Hkv;
+  return ((units > kFixedCounters ? units : kFixedCounters) * sizeof(int) + 255) & ~(size_t)255;
+}
 
 size_t smem_bytes(int HG, int B, bool ragged) {
   size_t s = 1024 + (size_t)HG * kStages * kStageBytes + (size_t)HG * kStages * 8;

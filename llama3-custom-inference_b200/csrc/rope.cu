@@ -86,7 +86,8 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ cache_k,
                           __nv_bfloat16* __restrict__ cache_v, long long total, int T, int Hq, int Hkv,
                           int vec_per_head, long long qkv_sb, long long qkv_st, long long cache_sb,
-                          long long cache_st, long long start_pos) {
+                          long long cache_st, long long start_pos, const int* __restrict__ positions,
+                          long long freq_rows, long long cache_len) {
   const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
   if (idx >= total) return;
   const int heads = Hq + 2 * Hkv;
@@ -97,16 +98,24 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
   const int t = (int)(rest % T);
   const long long b = rest / T;
   const int D = vec_per_head * kVecElems;
+  // Position of this token: start_pos + t for the whole batch, or positions[b] + t per sequence (then
+  // `freq` is the whole table and a position outside the table or the cache is skipped, not written).
+  long long pos = start_pos + t, frow = t;
+  if (positions) {
+    pos = (long long)__ldg(positions + b) + t;
+    frow = pos;
+    if (pos < 0 || pos >= freq_rows || pos >= cache_len) return;
+  }
   const uint4 v = ld_stream16(qkv + b * qkv_sb + t * qkv_st + (long long)hh * D + vec * kVecElems);
-  const float* f = freq + (long long)t * D + vec * kVecElems;
+  const float* f = freq + frow * D + vec * kVecElems;
   if (hh < Hq) {
     st_stream16(q_out + ((b * T + t) * Hq + hh) * (long long)D + vec * kVecElems, rotate8(v, f));
   } else if (hh < Hq + Hkv) {
     // Cache rows are read again by the attention kernel of the same step: plain store.
-    *reinterpret_cast<uint4*>(cache_k + b * cache_sb + (start_pos + t) * cache_st +
+    *reinterpret_cast<uint4*>(cache_k + b * cache_sb + pos * cache_st +
                               (long long)(hh - Hq) * D + vec * kVecElems) = rotate8(v, f);
   } else {
-    *reinterpret_cast<uint4*>(cache_v + b * cache_sb + (start_pos + t) * cache_st +
+    *reinterpret_cast<uint4*>(cache_v + b * cache_sb + pos * cache_st +
                               (long long)(hh - Hq - Hkv) * D + vec * kVecElems) = v;
   }
 }
@@ -179,7 +188,36 @@ extern "C" int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void*
   rot_embed_kv_cache_kernel<<<grid, kRopeBlock, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), freq, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), total, (int)T,
-      (int)Hq, (int)Hkv, (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, start_pos);
+      (int)Hq, (int)Hkv, (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, start_pos, nullptr, 0, 0);
+  L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
+  return L3CI_OK;
+}
+
+extern "C" int l3ci_rot_embed_kv_cache_at(const void* qkv, const float* freq_table, int64_t freq_rows, void* q_out,
+                                          void* cache_k, void* cache_v, const int32_t* positions, int64_t B,
+                                          int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t qkv_sb,
+                                          int64_t qkv_st, int64_t cache_sb, int64_t cache_st, int64_t cache_len,
+                                          l3ci_stream_t stream_) {
+  using namespace l3ci;
+  clear_error();
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (B < 0 || T < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || freq_rows < 0 || cache_len < 0)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache_at: bad size");
+  if (B == 0 || T == 0) return L3CI_OK;
+  if (!qkv || !freq_table || !q_out || !cache_k || !cache_v || !positions)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache_at: null pointer");
+  if (D % kVecElems) return fail(L3CI_ERR_UNSUPPORTED, "rot_embed_kv_cache_at: head size %lld not a multiple of 8", (long long)D);
+  if (!aligned16(qkv) || !aligned16(freq_table) || !aligned16(q_out) || !aligned16(cache_k) || !aligned16(cache_v) ||
+      (reinterpret_cast<uintptr_t>(positions) & 3) || qkv_sb % kVecElems || qkv_st % kVecElems ||
+      cache_sb % kVecElems || cache_st % kVecElems)
+    return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache_at: rows must start on 16 bytes");
+  const long long total = B * T * (Hq + 2 * Hkv) * (D / kVecElems);
+  unsigned grid = 0;
+  if (int st = grid_for(total, &grid)) return st;
+  rot_embed_kv_cache_kernel<<<grid, kRopeBlock, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(qkv), freq_table, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), total, (int)T, (int)Hq, (int)Hkv,
+      (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, 0, positions, freq_rows, cache_len);
   L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
   return L3CI_OK;
 }

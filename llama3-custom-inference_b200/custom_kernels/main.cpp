@@ -208,8 +208,12 @@ Tensor rot_embed(Tensor input, Tensor freq) {
 // Rotary embedding of q and k plus the cache write of k and v in one pass (model.py:100-108).
 // qkv: [B, T, (n_head + 2*n_kv_head) * D]; caches: [maxB, maxLen, n_kv_head, D].  Returns rotated
 // q as [B, T, n_head, D]; cache_k / cache_v are updated in place at [:, start_pos : start_pos + T].
+//
+// With `positions` (int32 [B] on the device) every sequence has its own position: token t of sequence b
+// is at positions[b] + t, `freq` is then the WHOLE table and `start_pos` is ignored.  Nothing on the host
+// depends on the positions, so a decode step written this way can be captured in a CUDA graph.
 Tensor rot_embed_kv_cache(Tensor qkv, Tensor freq, Tensor cache_k, Tensor cache_v, int64_t start_pos,
-                          int64_t n_head, int64_t n_kv_head) {
+                          int64_t n_head, int64_t n_kv_head, std::optional<Tensor> positions) {
   check_bf16_cuda(qkv, "qkv");
   check_bf16_cuda(cache_k, "cache_k");
   check_bf16_cuda(cache_v, "cache_v");
@@ -220,14 +224,30 @@ Tensor rot_embed_kv_cache(Tensor qkv, Tensor freq, Tensor cache_k, Tensor cache_
               "cache_k and cache_v must be [maxB, maxLen, n_kv_head, D] with equal layout");
   TORCH_CHECK(cache_k.size(2) == n_kv_head && cache_k.size(3) == D && cache_k.stride(3) == 1 && cache_k.stride(2) == D,
               "cache rows must be [n_kv_head, D] contiguous");
-  TORCH_CHECK(B <= cache_k.size(0) && start_pos >= 0 && start_pos + T <= cache_k.size(1), "step does not fit the cache");
+  TORCH_CHECK(B <= cache_k.size(0), "batch does not fit the cache");
   TORCH_CHECK(freq.is_cuda() && freq.scalar_type() == torch::kFloat32 && freq.numel() >= T * D, "freq must be float32 [T, D]");
+  if (positions) {
+    TORCH_CHECK(positions->is_cuda() && positions->scalar_type() == torch::kInt32 && positions->dim() == 1 &&
+                    positions->size(0) == B && positions->is_contiguous() && positions->get_device() == qkv.get_device(),
+                "positions must be a contiguous int32 CUDA tensor of shape [B]");
+    TORCH_CHECK(freq.dim() == 2 && freq.size(1) == D, "with positions, freq must be the whole [rows, D] table");
+  } else {
+    TORCH_CHECK(start_pos >= 0 && start_pos + T <= cache_k.size(1), "step does not fit the cache");
+  }
   TORCH_CHECK(cache_k.get_device() == qkv.get_device() && cache_v.get_device() == qkv.get_device() &&
                   freq.get_device() == qkv.get_device(),
               "tensors on different devices");
   const c10::cuda::CUDAGuard guard(qkv.device());
   Tensor f = freq.is_contiguous() ? freq : freq.contiguous();
   Tensor q_out = torch::empty({B, T, n_head, D}, qkv.options());
+  if (positions) {
+    check_status(l3ci_rot_embed_kv_cache_at(qkv.data_ptr(), f.data_ptr<float>(), f.size(0), q_out.data_ptr(),
+                                            cache_k.data_ptr(), cache_v.data_ptr(), positions->data_ptr<int32_t>(), B, T,
+                                            n_head, n_kv_head, D, qkv.stride(0), qkv.stride(1), cache_k.stride(0),
+                                            cache_k.stride(1), cache_k.size(1), current_stream()),
+                 "rot_embed_kv_cache");
+    return q_out;
+  }
   check_status(l3ci_rot_embed_kv_cache(qkv.data_ptr(), f.data_ptr<float>(), q_out.data_ptr(), cache_k.data_ptr(),
                                        cache_v.data_ptr(), B, T, n_head, n_kv_head, D, qkv.stride(0), qkv.stride(1),
                                        cache_k.stride(0), cache_k.stride(1), start_pos, current_stream()),
@@ -264,7 +284,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rot_embed", torch::wrap_pybind_function(rot_embed), "rot_embed", py::arg("input"), py::arg("freq"));
   m.def("rot_embed_kv_cache", torch::wrap_pybind_function(rot_embed_kv_cache), "rot_embed_kv_cache",
         py::arg("qkv"), py::arg("freq"), py::arg("cache_k"), py::arg("cache_v"), py::arg("start_pos"),
-        py::arg("n_head"), py::arg("n_kv_head"));
+        py::arg("n_head"), py::arg("n_kv_head"), py::kw_only(), py::arg("positions") = py::none());
   m.def("flash_attention_decode_partial", torch::wrap_pybind_function(flash_attention_decode_partial),
         "flash_attention_decode_partial", py::arg("query"), py::arg("keys"), py::arg("values"), py::kw_only(),
         py::arg("seq_lens") = py::none(), py::arg("scale") = 0.0, py::arg("max_ctas") = 0);

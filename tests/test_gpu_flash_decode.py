@@ -115,13 +115,16 @@ def test_any_grid_size_gives_the_same_result(capi, device, max_ctas):
 
 
 def test_scratch_is_reusable_without_clearing(capi, device):
-    scratch = capi.DecodeScratch(4, 32, 8, 128, device)
-    for i in range(4):
-        # alternate between calls that merge records (few sequences, many CTAs per unit) and ones that do not
-        case = inputs.decode_case(4 if i % 2 else 1, 32, 8, 128, 3000 if i % 2 == 0 else 40, seed=30 + i)
-        _check(capi, case, device, scratch=scratch)
+    # one scratch buffer, zeroed once, serves calls of different batch sizes, head counts and head sizes
+    scratch = capi.DecodeScratch(4, 16, 2, 128, device)   # ratio 8 at D=128: the largest records used below
+    shapes = [(1, 32, 8, 128, 3000), (4, 32, 8, 128, 40), (3, 16, 2, 128, 2000), (2, 8, 8, 64, 5000),
+              (4, 32, 8, 64, 700), (1, 32, 8, 128, 3000)]
+    for i, (B, Hq, Hkv, D, S) in enumerate(shapes):
+        assert capi.load().l3ci_flash_decode_scratch_bytes(B, Hq, Hkv, D) <= scratch.bytes
+        _check(capi, inputs.decode_case(B, Hq, Hkv, D, S, seed=30 + i, ragged=i % 2 == 1, min_len=S // 2), device,
+               scratch=scratch)
     assert scratch.poll() == capi.OK
-    counters = scratch.buf[256:256 + 4 * 8 * 4].view(torch.int32)
+    counters = scratch.buf[256:256 + 65536 * 4].view(torch.int32)
     assert int(counters.abs().sum()) == 0  # arrival counters are left at zero
 
 

@@ -78,6 +78,31 @@ def test_fused_rope_kv_cache_write(capi, device, B, T, start):
     assert (ck == 3.0).all() and (cv == 5.0).all()
 
 
+def test_fused_write_with_per_sequence_positions(capi, device):
+    # every sequence at its own position; one is past the end of the cache and must be skipped untouched
+    B, T, Hq, Hkv, D, max_len = 5, 1, 32, 8, 64, 50
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(B, T, (Hq + 2 * Hkv) * D, generator=g).bfloat16()
+    table = _table(D, 64)
+    pos = torch.tensor([0, 7, 49, 50, 31], dtype=torch.int32)
+    cache_k = torch.full((B, max_len, Hkv, D), 3.0, dtype=torch.bfloat16, device=device)
+    cache_v = torch.full((B, max_len, Hkv, D), 5.0, dtype=torch.bfloat16, device=device)
+    q_rot = capi.rot_embed_kv_cache_at(qkv.to(device), table.to(device), cache_k, cache_v, pos.to(device), Hq, Hkv)
+    torch.cuda.synchronize()
+    q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    want_k = torch.full((B, max_len, Hkv, D), 3.0, dtype=torch.bfloat16)
+    want_v = torch.full((B, max_len, Hkv, D), 5.0, dtype=torch.bfloat16)
+    for b in range(B):
+        p = int(pos[b])
+        if p >= max_len:
+            continue
+        f = table[p:p + 1]
+        assert torch.equal(q_rot[b:b + 1].cpu(), rot_embed_reference(q[b:b + 1].reshape(1, T, Hq, D), f))
+        want_k[b, p] = rot_embed_reference(k[b:b + 1].reshape(1, T, Hkv, D), f)[0, 0]
+        want_v[b, p] = v[b].reshape(T, Hkv, D)[0]
+    assert torch.equal(cache_k.cpu(), want_k) and torch.equal(cache_v.cpu(), want_v)
+
+
 def test_errors(capi, device):
     lib = capi.load()
     x = torch.zeros(64, dtype=torch.bfloat16, device=device)
