@@ -144,6 +144,39 @@ L3CI_API size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t H
 
 L3CI_API int l3ci_flash_decode(const l3ci_flash_decode_args* args);
 
+/* ------------------------------------------------------------------------------------------
+ * l3ci_flash_decode without any scratch from the caller.  (No counterpart in the reference, which
+ * allocates three scratch tensors inside every call: custom_kernels/custom_kernels.cu:269-271.)
+ *
+ * Who needs it: a host that cannot create device memory at the moment it wants attention computed.
+ * Typical cases are a serving process that handed the whole GPU to its own arena at start-up (the KV
+ * cache is sized to fill the card, so a later cudaMalloc has nothing to take from and may not be
+ * permitted by the embedding runtime at all), and code on a path where an allocation call would stall
+ * or is forbidden by policy (a latency-critical decode loop that must not enter the driver's
+ * allocator).  Such a caller still owns q, k, v and the output; only the merge scratch is missing.
+ *
+ * This entry point takes the same argument struct; its `scratch` and `scratch_bytes` fields are ignored.
+ * The scratch is an L3CI_STATIC_SCRATCH_BYTES array that is part of the library's device code, so
+ * every GPU on which the library is used carries it until the process ends.  The call makes no
+ * cudaMalloc/cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *  - the shape must fit: l3ci_flash_decode_scratch_bytes(B, Hq, Hkv, D) <= L3CI_STATIC_SCRATCH_BYTES
+ *    and B * Hkv <= 65536; otherwise L3CI_ERR_SCRATCH with a message that states both sizes
+ *    (12 MiB covers head ratios up to 8 at head size 128 on a 148-SM part);
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture;
+ *  - all calls on a device share the one array and find in it what the previous call left: the entry
+ *    point clears the part that has to start at zero itself (one small cudaMemsetAsync on `stream`),
+ *    but two calls that overlap on the GPU (different streams, or different host threads without
+ *    ordering) race on it.  Use one stream per device for this entry point, or l3ci_flash_decode with
+ *    one scratch buffer per stream;
+ *  - the device-side status word is not readable afterwards (l3ci_flash_decode_poll needs a caller
+ *    buffer).
+ * ------------------------------------------------------------------------------------------ */
+#define L3CI_STATIC_SCRATCH_BYTES (12u << 20)
+L3CI_API int l3ci_flash_decode_static(const l3ci_flash_decode_args* args);
+
 /* Reads back (synchronising `stream`) the device-side status word kept in `scratch`:
  * L3CI_OK, or L3CI_ERR_DEVICE_WAIT if a bounded wait on a bulk copy ran out in an earlier
  * call.  Clears the word and the arrival counters so the scratch can be used again. */

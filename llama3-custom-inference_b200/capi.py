@@ -20,7 +20,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
     "l3ci_rms_norm", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
-    "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_poll",
+    "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_lse_merge",
 )
 
@@ -78,6 +78,8 @@ def load() -> C.CDLL:
     lib.l3ci_flash_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
     lib.l3ci_flash_decode.restype = C.c_int
     lib.l3ci_flash_decode.argtypes = [C.POINTER(FlashDecodeArgs)]
+    lib.l3ci_flash_decode_static.restype = C.c_int
+    lib.l3ci_flash_decode_static.argtypes = [C.POINTER(FlashDecodeArgs)]
     lib.l3ci_flash_decode_poll.restype = C.c_int
     lib.l3ci_flash_decode_poll.argtypes = [vp, C.c_size_t, vp]
     lib.l3ci_lse_merge.restype = C.c_int
@@ -252,3 +254,19 @@ def lse_merge(o_parts, lse_parts):
                                      out.stride(0), out.stride(1), _stream(o_parts)), "l3ci_lse_merge")
     return out
 
+
+STATIC_SCRATCH_BYTES = 12 << 20  # L3CI_STATIC_SCRATCH_BYTES
+
+
+def flash_attention_decode_static(q, k, v, seq_lens=None, scale: float = 0.0):
+    """`flash_attention_decode` for callers that cannot allocate device memory: the merge scratch is the
+    library's built-in array (one per GPU, shared by every call on it; do not overlap calls).  The output
+    tensor is still created here because this helper mirrors the reference call form; a caller that owns
+    its output buffer fills `FlashDecodeArgs.out` itself and calls `l3ci_flash_decode_static` directly."""
+    import torch
+
+    out = torch.empty_like(q)
+    a = flash_decode_args(q, k, v, out=out, seq_lens=seq_lens, scale=scale)
+    with _on(q):
+        _check(load().l3ci_flash_decode_static(C.byref(a)), "l3ci_flash_decode_static")
+    return out

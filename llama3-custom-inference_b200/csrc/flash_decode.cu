@@ -839,8 +839,10 @@ extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t
   return kHeaderBytes + counters_bytes(B, Hkv) + records * (size_t)record_floats(R, D) * sizeof(float);
 }
 
-extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) {
-  using namespace l3ci;
+namespace l3ci {
+namespace {
+// Validates the arguments and launches; `a->scratch` must already be what the call may use.
+int flash_decode_launch(const l3ci_flash_decode_args* a) {
   clear_error();
   if (!a) return fail(L3CI_ERR_INVALID, "flash_decode: null args");
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
@@ -920,6 +922,64 @@ extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) {
   }
   return R > 8 ? launch_fd<128, true>(kmap, vmap, p, grid, HG, smem, stream)
                : launch_fd<128, false>(kmap, vmap, p, grid, HG, smem, stream);
+}
+}  // namespace
+}  // namespace l3ci
+
+extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) { return l3ci::flash_decode_launch(a); }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in this library's own device image.
+// ---------------------------------------------------------------------------------------------
+// Every GPU that loads the library holds these bytes until the process exits.  In host code the name
+// below is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_fd_static_scratch[L3CI_STATIC_SCRATCH_BYTES];
+
+namespace l3ci {
+namespace {
+// Device address of g_fd_static_scratch on the current device, looked up once per device (with that
+// device current) and remembered.
+int static_scratch_address(void** out) {
+  static void* address[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  L3CI_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode_static: device index %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_fd_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(L3CI_ERR_CUDA, "flash_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    address[dev] = ptr;
+  }
+  *out = address[dev];
+  return L3CI_OK;
+}
+}  // namespace
+}  // namespace l3ci
+
+extern "C" int l3ci_flash_decode_static(const l3ci_flash_decode_args* a) {
+  using namespace l3ci;
+  clear_error();
+  if (!a) return fail(L3CI_ERR_INVALID, "flash_decode_static: null args");
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv) return flash_decode_launch(a);  // reports the bad size
+  const size_t need = l3ci_flash_decode_scratch_bytes(a->B, a->Hq, a->Hkv, a->D);
+  if (need == 0 || need > (size_t)L3CI_STATIC_SCRATCH_BYTES || (size_t)a->B * a->Hkv > kFixedCounters)
+    return fail(L3CI_ERR_SCRATCH,
+                "flash_decode_static: this shape needs %zu bytes of scratch (B*Hkv = %lld units), the built-in area holds "
+                "%zu bytes and %zu units; use l3ci_flash_decode with caller-provided scratch",
+                need, (long long)a->B * a->Hkv, (size_t)L3CI_STATIC_SCRATCH_BYTES, kFixedCounters);
+  void* area = nullptr;
+  if (int st = static_scratch_address(&area)) return st;
+  // The area keeps whatever the previous call (of any shape) left.  Records are written before they are read;
+  // the status word and the arrival counters of this call's units must start at zero.
+  const size_t clear = kHeaderBytes + (((size_t)a->B * a->Hkv * sizeof(int) + 255) & ~(size_t)255);
+  L3CI_CUDA_TRY(cudaMemsetAsync(area, 0, clear, reinterpret_cast<cudaStream_t>(a->stream)));
+  l3ci_flash_decode_args b = *a;
+  b.scratch = area;
+  b.scratch_bytes = (size_t)L3CI_STATIC_SCRATCH_BYTES;
+  return flash_decode_launch(&b);
 }
 
 extern "C" int l3ci_flash_decode_poll(void* scratch, size_t scratch_bytes, l3ci_stream_t stream_) {
