@@ -13,6 +13,7 @@ Contents:
   capi.py         ctypes binding of the C ABI (include/l3ci_b200.h) over torch device tensors
   rope_table.py   rotary table with the Llama-3 frequency scaling as parameters (model.py:27-60)
   sharding.py     partition of a decode batch / a long KV sequence over the GPUs of one box
+  decode_loop.py  random-init Llama-3 decode loop around the kernels (end-to-end tokens/s harness)
   custom_kernels/ the torch extension module; put this package directory on sys.path and the
                   reference's `from custom_kernels import custom_kernels_extension` (model.py:23)
                   resolves to it unchanged
@@ -47,4 +48,4 @@ def extension():
     return importlib.import_module("custom_kernels.custom_kernels_extension")
 
 
-from . import capi, rope_table, sharding  # noqa: E402,F401
+from . import capi, decode_loop, rope_table, sharding  # noqa: E402,F401

@@ -339,26 +339,34 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   wk.B = p.B; wk.n_groups = p.n_groups; wk.n_seq = p.n_seq; wk.tile = C::kTile;
   wk.pref = nullptr; wk.lens = nullptr;
   int total;
-  if (p.seq_lens && p.B <= kWarp) {
-    // Up to 32 sequences: every warp scans the lengths by itself (all warps write the same values to the
+  if (p.seq_lens && p.B <= 8 * kWarp) {
+    // Up to 256 sequences: every warp scans the lengths by itself (all warps write the same values to the
     // shared arrays), which saves the two CTA-wide barriers of the general path.
-    const int len = lane < p.B ? min(max(__ldg(p.seq_lens + lane), 0), p.n_seq) : 0;
-    const int cols = lane < p.B ? p.n_groups * fd_tiles(len, C::kTile) : 0;
-    int incl = cols;
+    const int chunk = (p.B + kWarp - 1) / kWarp;  // <= 8 consecutive sequences per lane
+    const int beg = min(lane * chunk, p.B), end = min(beg + chunk, p.B);
+    int sum = 0;
+    for (int b = beg; b < end; ++b) {
+      const int len = min(max(__ldg(p.seq_lens + b), 0), p.n_seq);
+      s_len[b] = len;
+      sum += p.n_groups * fd_tiles(len, C::kTile);
+    }
+    int incl = sum;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int n = __shfl_up_sync(kFullMask, incl, d);
       if (lane >= d) incl += n;
     }
-    if (lane < p.B) {
-      s_len[lane] = len;
-      s_pref[lane + 1] = incl;
+    // Every value is written whole (never read-modify-written), so warps writing the same entry agree.
+    int run = incl - sum;
+    for (int b = beg; b < end; ++b) {
+      run += p.n_groups * fd_tiles(min(max(__ldg(p.seq_lens + b), 0), p.n_seq), C::kTile);
+      s_pref[b + 1] = run;
     }
     if (lane == 0) s_pref[0] = 0;
     __syncwarp();
     wk.pref = s_pref;
     wk.lens = s_len;
-    total = __shfl_sync(kFullMask, incl, p.B - 1);
+    total = __shfl_sync(kFullMask, incl, kWarp - 1);
   } else if (p.seq_lens) {
     for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
       const int len = min(max(__ldg(p.seq_lens + b), 0), p.n_seq);
@@ -394,11 +402,24 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 
   // The host sizes the grid from the padded length; with shorter sequences there may be fewer
   // columns than CTAs.  Only the first G CTAs work, so that every working CTA owns >= 1 column.
-  const int G = fd_active_ctas((int)gridDim.x, total);
+  // Short sequences: whole units per CTA, no cross-CTA merge.  Otherwise: equal contiguous ranges.
+  const int units = p.B * p.n_groups;
+  const bool whole = fd_whole_units(total, units, (int)gridDim.x);
+  const int G = whole ? min((int)gridDim.x, units) : fd_active_ctas((int)gridDim.x, total);
   const int cta = blockIdx.x;
   if (cta >= G) return;
-  const int c0 = fd_range_begin(cta, total, G);
-  const int c1 = fd_range_begin(cta + 1, total, G);
+  int c0, c1;
+  if (whole) {
+    auto unit_col = [&](int u) {
+      const int b = u / p.n_groups, g = u - b * p.n_groups;
+      return b >= p.B ? total : wk.pref_of(b) + g * fd_tiles(wk.len_of(b), C::kTile);
+    };
+    c0 = unit_col(fd_range_begin(cta, units, G));
+    c1 = unit_col(fd_range_begin(cta + 1, units, G));
+  } else {
+    c0 = fd_range_begin(cta, total, G);
+    c1 = fd_range_begin(cta + 1, total, G);
+  }
 
   const uint64_t policy = l2_evict_first_policy();
   const uint32_t stage0 = smem_u32(stages);
@@ -590,8 +611,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       l_lo = group_sum<4>(l_lo);
       if constexpr (RHI) l_hi = group_sum<4>(l_hi);
       const int u0 = wk.unit_begin(cons);
-      const int cfirst = fd_cta_of(u0, total, G);
-      const int clast = fd_cta_of(u0 + cons.tc - 1, total, G);
+      const int cfirst = whole ? cta : fd_cta_of(u0, total, G);
+      const int clast = whole ? cta : fd_cta_of(u0 + cons.tc - 1, total, G);
       const long long hq0 = (long long)head * R;
 
       if (cfirst == clast) {

@@ -3,7 +3,7 @@
 // Replaces custom_rot_embed_kernel / rot_embed (custom_kernels/custom_kernels.cu:391-442),
 // which launches one 32/64-thread CTA per (batch, token, head) and moves 4 bytes per thread.
 // Here one thread owns 8 consecutive bf16 (four rotation pairs, one 16-byte load and store)
-// and the two fp32 table vectors that go with them; the grid is flat over all vectors.
+// and the two fp32 table vectors that go with them; one CTA walks one token's heads.
 // The fused variant walks the projection output q|k|v once and writes rotated q to a dense
 // buffer, rotated k and untouched v straight into the cache rows of this step, which is what
 // CausalSelfAttention.forward does with two kernel calls and two copies (model.py:100-108).
@@ -20,7 +20,9 @@
 namespace l3ci {
 namespace {
 
-constexpr int kRopeBlock = 256;
+constexpr int kRopeBlock = 256;   // pair kernel: one thread per rotation pair
+constexpr int kTokenBlock = 128;  // token kernels: threads stride over one token's vectors
+constexpr int kTokenBatch = 4;    // 16-byte loads a thread has in flight
 
 __device__ __forceinline__ void rotate_pair(float x, float y, float c, float s, float& xo, float& yo) {
   xo = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
@@ -40,23 +42,36 @@ __device__ __forceinline__ uint4 rotate8(const uint4& v, const float* __restrict
   return pack8(r);
 }
 
-// x [B,S,H,D] strided, out dense.  One thread per 16-byte vector.
-__global__ void __launch_bounds__(kRopeBlock)
+// x [B,S,H,D] strided, out dense.  One CTA per token: (batch, position) is decoded once per CTA and the
+// threads stride over the token's H * D/8 vectors, so no thread does 64-bit index arithmetic.
+__global__ void __launch_bounds__(kTokenBlock)
 rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freq,
-                      __nv_bfloat16* __restrict__ out, long long total, int S, int H, int vec_per_head,
-                      long long sb, long long ss, long long sh) {
-  const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
-  if (idx >= total) return;
-  const int vec = (int)(idx % vec_per_head);
-  long long rest = idx / vec_per_head;
-  const int h = (int)(rest % H);
-  rest /= H;
-  const int s = (int)(rest % S);
-  const long long b = rest / S;
+                      __nv_bfloat16* __restrict__ out, int S, int H, int vec_per_head, long long sb, long long ss,
+                      long long sh) {
+  const long long token = blockIdx.x;
+  const int s = (int)(token % S);
+  const long long b = token / S;
   const int D = vec_per_head * kVecElems;
-  const uint4 v = ld_stream16(x + b * sb + s * ss + h * sh + vec * kVecElems);
-  const uint4 r = rotate8(v, freq + (long long)s * D + vec * kVecElems);
-  st_stream16(out + idx * kVecElems, r);
+  const int row_vecs = H * vec_per_head;
+  const __nv_bfloat16* xin = x + b * sb + s * ss;
+  __nv_bfloat16* xout = out + token * (long long)row_vecs * kVecElems;
+  const float* f = freq + (long long)s * D;
+  for (int i0 = threadIdx.x; i0 < row_vecs; i0 += kTokenBlock * kTokenBatch) {
+    uint4 v[kTokenBatch];
+#pragma unroll
+    for (int u = 0; u < kTokenBatch; ++u) {
+      const int i = i0 + u * kTokenBlock;
+      if (i < row_vecs) {
+        const int h = i / vec_per_head, vec = i - h * vec_per_head;
+        v[u] = ld_stream16(xin + h * sh + vec * kVecElems);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kTokenBatch; ++u) {
+      const int i = i0 + u * kTokenBlock;
+      if (i < row_vecs) st_stream16(xout + i * kVecElems, rotate8(v[u], f + (i % vec_per_head) * kVecElems));
+    }
+  }
 }
 
 // Fallback for rows that only start on 4 bytes: one thread per rotation pair.
@@ -80,23 +95,17 @@ rot_embed_pair_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
   *reinterpret_cast<uint32_t*>(out + idx * 2) = pack_bf16x2(xo, yo);
 }
 
-// qkv [B,T,(Hq+2Hkv)*D] -> q_out dense [B,T,Hq,D], cache_k/v[b, start_pos+t, h, :].
-__global__ void __launch_bounds__(kRopeBlock)
+// qkv [B,T,(Hq+2Hkv)*D] -> q_out dense [B,T,Hq,D], cache_k/v[b, pos, h, :].  One CTA per token.
+__global__ void __launch_bounds__(kTokenBlock)
 rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ freq,
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ cache_k,
-                          __nv_bfloat16* __restrict__ cache_v, long long total, int T, int Hq, int Hkv,
-                          int vec_per_head, long long qkv_sb, long long qkv_st, long long cache_sb,
-                          long long cache_st, long long start_pos, const int* __restrict__ positions,
-                          long long freq_rows, long long cache_len) {
-  const long long idx = (long long)blockIdx.x * kRopeBlock + threadIdx.x;
-  if (idx >= total) return;
-  const int heads = Hq + 2 * Hkv;
-  const int vec = (int)(idx % vec_per_head);
-  long long rest = idx / vec_per_head;
-  const int hh = (int)(rest % heads);
-  rest /= heads;
-  const int t = (int)(rest % T);
-  const long long b = rest / T;
+                          __nv_bfloat16* __restrict__ cache_v, int T, int Hq, int Hkv, int vec_per_head,
+                          long long qkv_sb, long long qkv_st, long long cache_sb, long long cache_st,
+                          long long start_pos, const int* __restrict__ positions, long long freq_rows,
+                          long long cache_len) {
+  const long long token = blockIdx.x;
+  const int t = (int)(token % T);
+  const long long b = token / T;
   const int D = vec_per_head * kVecElems;
   // Position of this token: start_pos + t for the whole batch, or positions[b] + t per sequence (then
   // `freq` is the whole table and a position outside the table or the cache is skipped, not written).
@@ -106,17 +115,34 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
     frow = pos;
     if (pos < 0 || pos >= freq_rows || pos >= cache_len) return;
   }
-  const uint4 v = ld_stream16(qkv + b * qkv_sb + t * qkv_st + (long long)hh * D + vec * kVecElems);
-  const float* f = freq + frow * D + vec * kVecElems;
-  if (hh < Hq) {
-    st_stream16(q_out + ((b * T + t) * Hq + hh) * (long long)D + vec * kVecElems, rotate8(v, f));
-  } else if (hh < Hq + Hkv) {
-    // Cache rows are read again by the attention kernel of the same step: plain store.
-    *reinterpret_cast<uint4*>(cache_k + b * cache_sb + pos * cache_st +
-                              (long long)(hh - Hq) * D + vec * kVecElems) = rotate8(v, f);
-  } else {
-    *reinterpret_cast<uint4*>(cache_v + b * cache_sb + pos * cache_st +
-                              (long long)(hh - Hq - Hkv) * D + vec * kVecElems) = v;
+  const __nv_bfloat16* in = qkv + b * qkv_sb + t * qkv_st;
+  const float* f = freq + frow * D;
+  __nv_bfloat16* qo = q_out + token * (long long)Hq * D;
+  __nv_bfloat16* ko = cache_k + b * cache_sb + pos * cache_st;
+  __nv_bfloat16* vo = cache_v + b * cache_sb + pos * cache_st;
+  const int q_vecs = Hq * vec_per_head, k_vecs = Hkv * vec_per_head;
+  const int row_vecs = q_vecs + 2 * k_vecs;
+  for (int i0 = threadIdx.x; i0 < row_vecs; i0 += kTokenBlock * kTokenBatch) {
+    uint4 v[kTokenBatch];
+#pragma unroll
+    for (int u = 0; u < kTokenBatch; ++u) {
+      const int i = i0 + u * kTokenBlock;
+      if (i < row_vecs) v[u] = ld_stream16(in + i * kVecElems);
+    }
+#pragma unroll
+    for (int u = 0; u < kTokenBatch; ++u) {
+      const int i = i0 + u * kTokenBlock;
+      if (i >= row_vecs) continue;
+      const int vec = i % vec_per_head;
+      if (i < q_vecs) {
+        st_stream16(qo + i * kVecElems, rotate8(v[u], f + vec * kVecElems));
+      } else if (i < q_vecs + k_vecs) {
+        // Cache rows are read again by the attention kernel of the same step: plain store.
+        *reinterpret_cast<uint4*>(ko + (i - q_vecs) * kVecElems) = rotate8(v[u], f + vec * kVecElems);
+      } else {
+        *reinterpret_cast<uint4*>(vo + (i - q_vecs - k_vecs) * kVecElems) = v[u];
+      }
+    }
   }
 }
 
@@ -147,10 +173,9 @@ extern "C" int l3ci_rot_embed(const void* x, const float* freq, void* out, int64
                     sb % kVecElems == 0 && ss % kVecElems == 0 && sh % kVecElems == 0;
   unsigned grid = 0;
   if (vec8) {
-    const long long total = B * S * H * (D / kVecElems);
-    if (int st = grid_for(total, &grid)) return st;
-    rot_embed_vec8_kernel<<<grid, kRopeBlock, 0, stream>>>(xp, freq, op, total, (int)S, (int)H,
-                                                           (int)(D / kVecElems), sb, ss, sh);
+    if (B * S > 0x7fffffffLL || H * (D / kVecElems) > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rot_embed: tensor too large");
+    grid = (unsigned)(B * S);
+    rot_embed_vec8_kernel<<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, (int)(D / kVecElems), sb, ss, sh);
     L3CI_CHECK_LAUNCH("rot_embed_vec8_kernel");
     return L3CI_OK;
   }
@@ -182,12 +207,11 @@ extern "C" int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void*
       !aligned16(cache_v) || qkv_sb % kVecElems || qkv_st % kVecElems || cache_sb % kVecElems ||
       cache_st % kVecElems)
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache: rows must start on 16 bytes");
-  const long long total = B * T * (Hq + 2 * Hkv) * (D / kVecElems);
-  unsigned grid = 0;
-  if (int st = grid_for(total, &grid)) return st;
-  rot_embed_kv_cache_kernel<<<grid, kRopeBlock, 0, stream>>>(
+  if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache: tensor too large");
+  rot_embed_kv_cache_kernel<<<(unsigned)(B * T), kTokenBlock, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), freq, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), total, (int)T,
+      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T,
       (int)Hq, (int)Hkv, (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, start_pos, nullptr, 0, 0);
   L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
   return L3CI_OK;
@@ -211,12 +235,11 @@ extern "C" int l3ci_rot_embed_kv_cache_at(const void* qkv, const float* freq_tab
       (reinterpret_cast<uintptr_t>(positions) & 3) || qkv_sb % kVecElems || qkv_st % kVecElems ||
       cache_sb % kVecElems || cache_st % kVecElems)
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache_at: rows must start on 16 bytes");
-  const long long total = B * T * (Hq + 2 * Hkv) * (D / kVecElems);
-  unsigned grid = 0;
-  if (int st = grid_for(total, &grid)) return st;
-  rot_embed_kv_cache_kernel<<<grid, kRopeBlock, 0, stream>>>(
+  if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
+    return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache_at: tensor too large");
+  rot_embed_kv_cache_kernel<<<(unsigned)(B * T), kTokenBlock, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), freq_table, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), total, (int)T, (int)Hq, (int)Hkv,
+      static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T, (int)Hq, (int)Hkv,
       (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, 0, positions, freq_rows, cache_len);
   L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
   return L3CI_OK;

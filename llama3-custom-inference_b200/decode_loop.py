@@ -1,0 +1,171 @@
+"""A Llama-3 decode loop around the extension kernels, for end-to-end tokens/s on random weights.
+
+Host-side mirror of what the reference's model does around its three extension calls — `Block` /
+`CausalSelfAttention` / `MLP` / `LLaMA3.forward` (model.py:92-149, 203-232) and the greedy branch of
+`LLaMA3.generate` (model.py:363-381) — restricted to what the end-to-end benchmark needs: random-init
+weights of the Llama-3.2-1B architecture (or any `DecoderConfig`), a batch of equal-length prompts, greedy
+decoding with `ignore_eos`.  It is a harness, not a model library: no checkpoint loading, no sampling, no
+tokenizer.
+
+What differs from the reference's loop, all on the caller's side of the kernels:
+  * rotary embedding, the K/V cache write and the split of q|k|v are one call (`rot_embed_kv_cache` with
+    per-sequence device positions) instead of two `rot_embed` calls and two cache copies (model.py:100-108);
+  * decode attention reads the cache in place with device-side lengths (`seq_lens=`), so no tensor shape or
+    host scalar changes from step to step;
+  * which lets one decode step be captured in a CUDA graph and replayed: no per-step Python dispatch, no
+    per-step mask construction (model.py:211) and no `all(eos_reached)` host sync (model.py:380).
+GEMMs, embedding lookup, SiLU and argmax are plain torch ops (cuBLAS); prefill attention is torch SDPA, as in
+the reference (model.py:114-116).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import rope_table
+
+
+@dataclass
+class DecoderConfig:
+    """Architecture numbers of model.py:153-165 (defaults: Llama-3.2-1B) plus the rotary scaling factor."""
+    vocab_size: int = 128256
+    n_layer: int = 16
+    n_head: int = 32
+    n_kv_head: int = 8
+    n_embd: int = 2048
+    hidden_dim: int = 8192
+    norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    rope_scale_factor: float = 32.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.n_embd // self.n_head
+
+
+class Llama3Decoder:
+    """Random-init decoder-only transformer with a static KV cache on one GPU."""
+
+    def __init__(self, ext, cfg: DecoderConfig, device, max_batch: int, max_len: int, seed: int = 42,
+                 weights: Optional[dict] = None):
+        self.ext, self.cfg, self.device = ext, cfg, torch.device(device)
+        self.max_batch, self.max_len = max_batch, max_len
+        E, F_, D = cfg.n_embd, cfg.hidden_dim, cfg.head_dim
+        qkv_rows = (cfg.n_head + 2 * cfg.n_kv_head) * D
+        if weights is None:
+            weights = init_weights(cfg, seed)
+        self.w = {k: v.to(self.device) for k, v in weights.items()}
+        bf16 = dict(dtype=torch.bfloat16, device=self.device)
+        self.cache_k = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
+        self.cache_v = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
+        self.freqs = rope_table.precompute_freqs_cis(D, max_len, cfg.rope_theta, True,
+                                                     scale_factor=cfg.rope_scale_factor).to(self.device)
+        assert self.w["h0.attn"].shape == (qkv_rows, E) and self.w["h0.fc"].shape == (F_, E)
+        self._graph = None
+
+    # ---- one forward pass over T new tokens per sequence ------------------------------------------------
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor) -> torch.Tensor:
+        """tokens [B, T] int64; positions int32 [B] = tokens already cached per sequence; seq_lens int32 [B] =
+        positions + T.  Returns the greedy next token per sequence, int64 [B]."""
+        cfg, ext, w = self.cfg, self.ext, self.w
+        B, T = tokens.shape
+        E, D, Hq, Hkv = cfg.n_embd, cfg.head_dim, cfg.n_head, cfg.n_kv_head
+        x = F.embedding(tokens, w["wte"])                                            # model.py:208
+        for l in range(cfg.n_layer):
+            p = f"h{l}."
+            h = ext.rms_norm(x, w[p + "ln_1"], cfg.norm_eps)                           # model.py:147, 71
+            qkv = F.linear(h, w[p + "attn"])                                           # model.py:95
+            q = ext.rot_embed_kv_cache(qkv, self.freqs, self.cache_k[l], self.cache_v[l], 0, Hq, Hkv,
+                                       positions=positions)                            # model.py:96-108
+            if T > 1:
+                # prefill: all sequences start at position 0 with T tokens (model.py:114-116)
+                k = self.cache_k[l][:B, :T].transpose(1, 2)
+                v = self.cache_v[l][:B, :T].transpose(1, 2)
+                y = F.scaled_dot_product_attention(q.transpose(1, 2), k, v, is_causal=True, enable_gqa=True)
+            else:
+                y = ext.flash_attention_decode(q.transpose(1, 2), self.cache_k[l][:B].transpose(1, 2),
+                                               self.cache_v[l][:B].transpose(1, 2), seq_lens=seq_lens)  # model.py:118
+            y = y.transpose(1, 2).reshape(B, T, E)                                     # model.py:120
+            x = x + F.linear(y, w[p + "proj"])                                         # model.py:121, 147
+            h = ext.rms_norm(x, w[p + "ln_2"], cfg.norm_eps)                           # model.py:148
+            x = x + F.linear(F.silu(F.linear(h, w[p + "fc2"])) * F.linear(h, w[p + "fc"]), w[p + "mlp_proj"])  # :134
+        x = ext.rms_norm(x[:, -1:, :].contiguous(), w["ln_f"], cfg.norm_eps)           # model.py:217
+        logits = F.linear(x, w["wte"]).float()                                         # model.py:225 (tied head)
+        return logits[:, -1].argmax(dim=-1)                                            # model.py:371
+
+    # ---- greedy generation --------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def generate(self, prompts: torch.Tensor, max_gen_len: int, use_graph: bool = True) -> torch.Tensor:
+        """prompts int64 [B, P] (equal lengths, on the device).  Returns the generated tokens int64
+        [B, max_gen_len].  With `use_graph` one decode step is captured in a CUDA graph and replayed."""
+        B, P = prompts.shape
+        assert B <= self.max_batch and P + max_gen_len <= self.max_len
+        dev = self.device
+        out = torch.empty(B, max_gen_len, dtype=torch.int64, device=dev)
+        positions = torch.zeros(B, dtype=torch.int32, device=dev)
+        seq_lens = torch.full((B,), P, dtype=torch.int32, device=dev)
+        tok = self.forward(prompts, positions, seq_lens)                               # prefill
+        out[:, 0] = tok
+        # static state of the decode step: everything the step reads or writes lives in these tensors
+        cur = tok.view(B, 1).clone()
+        positions.fill_(P)
+        seq_lens.fill_(P + 1)
+        step_idx = torch.ones(1, dtype=torch.int64, device=dev)
+
+        def step():
+            nxt = self.forward(cur, positions, seq_lens)
+            out.scatter_(1, step_idx.view(1, 1).expand(B, 1), nxt.view(B, 1))
+            cur.copy_(nxt.view(B, 1))
+            positions.add_(1)
+            seq_lens.add_(1)
+            step_idx.add_(1)
+
+        n_steps = max_gen_len - 1
+        if n_steps <= 0:
+            return out
+        if not use_graph:
+            for _ in range(n_steps):
+                step()
+            return out
+        # Capture needs every lazy allocation (decode workspace, cuBLAS handles) to have happened: run the step
+        # once eagerly on a side stream, then capture the same step.
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+            n_steps -= 1
+            graph = torch.cuda.CUDAGraph()
+            if n_steps > 0:
+                with torch.cuda.graph(graph, stream=side):
+                    step()
+                # the capture did not run the step: replay it for every remaining token
+                for _ in range(n_steps):
+                    graph.replay()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self._graph = graph
+        return out
+
+
+def init_weights(cfg: DecoderConfig, seed: int = 42) -> dict:
+    """bf16 weights ~ N(0, 0.02) from a CPU generator, norm weights 1 (the benchmark's random-init model).
+    Names follow the reference's module tree (model.py:83-84, 127-131, 140-143, 183-188)."""
+    g = torch.Generator().manual_seed(seed)
+    E, F_, D = cfg.n_embd, cfg.hidden_dim, cfg.head_dim
+
+    def mat(rows, cols):
+        return (torch.randn(rows, cols, generator=g) * 0.02).bfloat16()
+
+    w = {"wte": mat(cfg.vocab_size, E), "ln_f": torch.ones(E, dtype=torch.bfloat16)}
+    for l in range(cfg.n_layer):
+        p = f"h{l}."
+        w[p + "ln_1"] = torch.ones(E, dtype=torch.bfloat16)
+        w[p + "attn"] = mat((cfg.n_head + 2 * cfg.n_kv_head) * D, E)
+        w[p + "proj"] = mat(E, E)
+        w[p + "ln_2"] = torch.ones(E, dtype=torch.bfloat16)
+        w[p + "fc"] = mat(F_, E)
+        w[p + "fc2"] = mat(F_, E)
+        w[p + "mlp_proj"] = mat(E, F_)
+    return w

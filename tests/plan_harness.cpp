@@ -24,7 +24,8 @@ int plan_cta_of(int col, int total, int ctas) { return fd_cta_of(col, total, cta
 
 // Returns 0 if all invariants hold, else a positive code; info[0..3] receive details.
 // stats[0] = units finished directly, stats[1] = units merged, stats[2] = records written,
-// stats[3] = max columns of a CTA, stats[4] = min columns of a non-empty CTA, stats[5] = total columns.
+// stats[3] = max columns of a CTA, stats[4] = min columns of a non-empty CTA, stats[5] = total columns,
+// stats[6] = 1 if the whole-unit cut was chosen.
 int plan_simulate(int B, int Hkv, int D, int n_seq, const int* seq_lens, int G, int stages, int* info,
                   long long* stats) {
   const int tile = fd_tile_tokens(D);
@@ -47,7 +48,14 @@ int plan_simulate(int B, int Hkv, int D, int n_seq, const int* seq_lens, int G, 
   }
   const int total = wk.total();
   const int grid = G;
-  G = fd_active_ctas(grid, total);
+  const int units = B * n_groups;
+  const bool whole = fd_whole_units(total, units, grid);
+  G = whole ? (grid < units ? grid : units) : fd_active_ctas(grid, total);
+  auto unit_col = [&](int u) {
+    const int b = u / n_groups, g = u - b * n_groups;
+    return b >= B ? total : wk.pref_of(b) + g * fd_tiles(wk.len_of(b), tile);
+  };
+  stats[6] = whole;
   stats[5] = total;
   stats[3] = 0;
   stats[4] = total + 1;
@@ -59,11 +67,12 @@ int plan_simulate(int B, int Hkv, int D, int n_seq, const int* seq_lens, int G, 
   long long n_records = 0;
 
   for (int cta = 0; cta < G; ++cta) {
-    const int c0 = fd_range_begin(cta, total, G), c1 = fd_range_begin(cta + 1, total, G);
+    const int c0 = whole ? unit_col(fd_range_begin(cta, units, G)) : fd_range_begin(cta, total, G);
+    const int c1 = whole ? unit_col(fd_range_begin(cta + 1, units, G)) : fd_range_begin(cta + 1, total, G);
     if (c0 >= c1) { info[0] = cta; return 1; }  // every active CTA owns a column
     if (c1 - c0 > stats[3]) stats[3] = c1 - c0;
     if (c1 - c0 < stats[4]) stats[4] = c1 - c0;
-    for (int col = c0; col < c1; ++col)
+    for (int col = c0; col < c1 && !whole; ++col)
       if (fd_cta_of(col, total, G) != cta) { info[0] = cta; info[1] = col; info[2] = fd_cta_of(col, total, G); return 2; }
     for (int warp = 0; warp < HG; ++warp) {
       FdCursor prod = wk.seek(c0), cons = prod;
@@ -85,7 +94,8 @@ int plan_simulate(int B, int Hkv, int D, int n_seq, const int* seq_lens, int G, 
         if (prod.col < c1) { inflight.push_back(prod); wk.advance(prod); }
         if (fd_unit_ends(cons, c1)) {
           const int u0 = wk.unit_begin(cons);
-          const int cfirst = fd_cta_of(u0, total, G), clast = fd_cta_of(u0 + cons.tc - 1, total, G);
+          const int cfirst = whole ? cta : fd_cta_of(u0, total, G), clast = whole ? cta : fd_cta_of(u0 + cons.tc - 1, total, G);
+          if (whole && (u0 < c0 || u0 + cons.tc > c1)) { info[0] = cta; info[1] = u0; return 16; }  // unit not whole
           if (cta < cfirst || cta > clast) { info[0] = cta; info[1] = cfirst; info[2] = clast; return 7; }
           if (cfirst == clast) {
             direct[{cons.b, head}]++;

@@ -23,7 +23,7 @@ def plan(tmp_path_factory):
 
 def simulate(plan, B, Hkv, D, n_seq, lens, G, stages=3):
     info = (C.c_int * 4)()
-    stats = (C.c_longlong * 6)()
+    stats = (C.c_longlong * 7)()
     arr = (C.c_int * B)(*lens) if lens is not None else None
     rc = plan.plan_simulate(B, Hkv, D, n_seq, arr, G, stages, info, stats)
     assert rc == 0, f"invariant {rc} broken: info={list(info)} B={B} Hkv={Hkv} D={D} n_seq={n_seq} lens={lens} G={G}"
@@ -55,14 +55,17 @@ def test_ranges_are_balanced_and_invertible(plan):
 def test_uniform_lengths(plan, B, Hkv, D, n_seq, G):
     stats = simulate(plan, B, Hkv, D, n_seq, None, G)
     assert stats[0] + stats[1] == B * Hkv
-    assert stats[3] - stats[4] <= 1
+    if stats[6]:
+        assert stats[1] == 0      # whole units per CTA: nothing to merge
+    else:
+        assert stats[3] - stats[4] <= 1
 
 
 def test_config2_ragged_batch(plan):
     rng = random.Random(42)
     lens = [rng.randint(1024, 2048) for _ in range(16)]
     stats = simulate(plan, 16, 8, 128, 2048, lens, 148)
-    assert stats[0] + stats[1] == 16 * 8 and stats[3] - stats[4] <= 1
+    assert stats[6] == 0 and stats[0] + stats[1] == 16 * 8 and stats[3] - stats[4] <= 1
     assert stats[5] == sum((l + 15) // 16 for l in lens)
 
 
@@ -78,3 +81,16 @@ def test_random_ragged_batches(plan):
         G = rng.choice([1, 2, 3, 7, 148, plan.plan_max_ctas(148, hg)])
         stats = simulate(plan, B, Hkv, D, n_seq, lens, G, stages=rng.choice([1, 2, 3, 4]))
         assert stats[0] + stats[1] == B * Hkv
+
+
+def test_short_sequences_are_not_cut(plan):
+    # the start of an end-to-end decode: 64 sequences of ~150 tokens in a cache padded to 2176
+    rng = random.Random(11)
+    lens = [rng.randint(129, 180) for _ in range(64)]
+    stats = simulate(plan, 64, 8, 64, 2176, lens, 148)
+    assert stats[6] == 1 and stats[1] == 0 and stats[0] == 64 * 8
+    # late in the same decode the sequences are long and are cut again
+    stats = simulate(plan, 64, 8, 64, 2176, [2100] * 64, 148)
+    assert stats[6] == 0
+    # one long sequence is always cut
+    assert simulate(plan, 1, 8, 128, 131072, None, 148)[6] == 0

@@ -1,0 +1,69 @@
+"""Two ranks on two GPUs (NCCL): a KV sequence sharded across the ranks, shard results exchanged and merged,
+and a batch sharded by sequence with no exchange.  Skipped on a box with one GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import load_package
+from oracle import attention, compare, inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = load_package()
+        ext = pkg.extension()
+        # --- KV sequence sharded over the ranks, one all_gather, merge on every rank
+        case = inputs.decode_case(2, 32, 8, 128, 6000, seed=61, ragged=True, min_len=100)
+        lo, hi = pkg.sharding.kv_shard_bounds(6000, world)[rank]
+        dc = case.to(dev)
+        lens = pkg.sharding.local_seq_lens(dc.seq_lens, lo, hi)
+        out = pkg.sharding.decode_kv_sharded(ext, dc.q, dc.k[:, :, lo:hi], dc.v[:, :, lo:hi], lens)
+        torch.cuda.synchronize()
+        want = attention.sdpa_reference(case.q, case.k, case.v, case.seq_lens)
+        compare.assert_close_attention(out, want)
+        # --- batch sharded by sequence: every rank computes its own sequences, nothing is exchanged
+        batch = inputs.config2(seed=62)
+        mine = pkg.sharding.partition_batch(batch.seq_lens.tolist(), world)[rank]
+        idx = torch.tensor(mine)
+        sub = inputs.DecodeCase(batch.q[idx], batch.k[idx], batch.v[idx], batch.seq_lens[idx]).to(dev)
+        got = ext.flash_attention_decode(sub.q, sub.k, sub.v, seq_lens=sub.seq_lens)
+        torch.cuda.synchronize()
+        full = attention.sdpa_reference(batch.q, batch.k, batch.v, batch.seq_lens)
+        compare.assert_close_attention(got, full[idx])
+        assert ext.flash_decode_status(got) == 0
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of hanging the peer in a collective
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sequence_sharding_and_batch_sharding():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert results == {0: "ok", 1: "ok"}, results
