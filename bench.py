@@ -227,6 +227,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--nccl-merge", action="store_true", help="c3 on >1 GPU: all_gather + merge kernel instead of the fused exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -318,8 +319,15 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     rot_bytes = sum(k.numel() * 2 * 2 for k in ks)
     out = torch.empty_like(q)
 
+    xchg = None
+    if sharded_seq and not args.nccl_merge:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        xchg = pkg.sharding.KvShardExchange(ext, q.shape[0], q.shape[1], q.shape[3], dev)
+
     def step(i):
         j = i % n_rot
+        if sharded_seq and xchg is not None:
+            return pkg.sharding.decode_kv_sharded_fused(ext, q, ks[j], vs[j], xchg)
         if sharded_seq:
             return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
         return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
@@ -359,7 +367,9 @@ def bench_decode(args, ext, pkg, dev, rank, world):
                 "kernel": "flash_decode_kernel", "algorithmic_bytes_per_launch": my_bytes,
                 "frac_of_8TBs_nominal": achieved / 8000.0}
     if sharded_seq:
-        roofline["note"] = "per-rank shard; the step also holds one all_gather and the lse_merge kernel"
+        roofline["note"] = "per-rank shard; the step also holds the exchange of shard results and their merge"
+    if xchg is not None and xchg.check() != 0:
+        raise RuntimeError("exchange wait ran out")
 
     # ---- end to end through the extension with host buffers (pinned), copies inside the timed region ----
     hq, hk, hv = case.q.contiguous().pin_memory(), case.k.pin_memory(), case.v.pin_memory()
@@ -373,7 +383,9 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         dk = hk.to(dev, non_blocking=True)
         dv = hv.to(dev, non_blocking=True)
         dl = hl.to(dev, non_blocking=True) if hl is not None else None
-        if sharded_seq:
+        if sharded_seq and xchg is not None:
+            o = pkg.sharding.decode_kv_sharded_fused(ext, dq, dk, dv, xchg)
+        elif sharded_seq:
             o = pkg.sharding.decode_kv_sharded(ext, dq, dk, dv, None)
         else:
             o = ext.flash_attention_decode(dq, dk, dv, seq_lens=dl)
@@ -409,7 +421,8 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         "scaling": "strong" if sharded_seq else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
                    "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
-                   "parallelism": ("kv-sequence sharded x%d + lse merge" % world) if sharded_seq else
+                   "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
+                                                                  "fused NVLink exchange/merge kernel")) if sharded_seq else
                                   ("data-parallel x%d, no collective" % world),
                    "pct_of_8TBs_nominal_per_gpu": 100.0 * achieved / 8000.0},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * (2 if sharded_seq else 1),

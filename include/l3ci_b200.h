@@ -194,6 +194,28 @@ L3CI_API int l3ci_lse_merge(const float* o, const float* lse, void* out,
                             int32_t parts, int32_t B, int32_t Hq, int32_t D,
                             int64_t o_sb, int64_t o_sh, l3ci_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * The same merge with the exchange fused in: every rank pushes its shard result into its peers'
+ * memory over NVLink and merges what the peers pushed to it, in ONE kernel, with no collective
+ * library in between.  No counterpart in the reference (single GPU).
+ *
+ * Every rank owns a buffer of l3ci_lse_exchange_bytes(ranks, B, Hq, D) bytes, zero-filled once, that
+ * all ranks of the box can address (CUDA IPC / torch symmetric memory); `bufs` is a DEVICE array of
+ * `ranks` base pointers as seen from this process, bufs[rank] being the local one.  Layout (fp32):
+ *   data  [2][ranks][B*Hq*D outputs, then B*Hq lse padded to a multiple of 4 floats]
+ *   flags [2][ranks][B*Hq] (uint32, after the data)
+ * A call with epoch e (1, 2, 3, ... the same on all ranks) uses parity e & 1.  Before the call the
+ * rank's own shard result must be in ITS OWN slot [e & 1][rank] (l3ci_flash_decode with o_partial /
+ * lse pointing there).  The kernel waits at most one second for the peers' rows; if that runs out it
+ * writes L3CI_ERR_DEVICE_WAIT to *status (optional device word) and leaves `out` unwritten for
+ * those rows.  Every rank must call it, on its own GPU, once per epoch.
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API size_t l3ci_lse_exchange_bytes(int32_t ranks, int32_t B, int32_t Hq, int32_t D);
+L3CI_API int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t ranks, uint32_t epoch,
+                                     void* out, int32_t B, int32_t Hq, int32_t D,
+                                     int64_t o_sb, int64_t o_sh, int32_t* status,
+                                     l3ci_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,7 +21,7 @@ EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
     "l3ci_rms_norm", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
-    "l3ci_lse_merge",
+    "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge",
 )
 
 
@@ -84,6 +84,10 @@ def load() -> C.CDLL:
     lib.l3ci_flash_decode_poll.argtypes = [vp, C.c_size_t, vp]
     lib.l3ci_lse_merge.restype = C.c_int
     lib.l3ci_lse_merge.argtypes = [vp, vp, vp, i32, i32, i32, i32, i64, i64, vp]
+    lib.l3ci_lse_exchange_bytes.restype = C.c_size_t
+    lib.l3ci_lse_exchange_bytes.argtypes = [i32, i32, i32, i32]
+    lib.l3ci_lse_exchange_merge.restype = C.c_int
+    lib.l3ci_lse_exchange_merge.argtypes = [vp, i32, i32, C.c_uint32, vp, i32, i32, i32, i64, i64, vp, vp]
     _lib = lib
     return lib
 

@@ -209,95 +209,146 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 // lpc lanes per chunk (a power of two, as many as 32 lanes allow); the lanes of a chunk take every
 // lpc-th record, fold them in registers (up to 8 records' loads in flight per lane) and meet in a
 // shuffle butterfly.  So a unit shared by many CTAs costs each of them a handful of loads, and a
-// unit shared by two or three costs one round of loads.  Returns false if the wait ran out.
+// unit shared by two or three costs one round of loads.
 template <int D>
-__device__ __noinline__ bool merge_slice(const FdParams& p, int b, int head, int first_cta, int n, int me, int HG,
-                                         int warp, int lane) {
-  constexpr int C4 = D / 4;  // chunks per output row (a power of two)
-  constexpr int kBatch = 8;
-  const int R = p.R;
-  const int* counter = p.counters + b * p.Hkv + head;
+struct SliceJob {
+  static constexpr int C4 = D / 4;  // chunks per output row (a power of two)
+  static constexpr int kBatch = 8;  // (chunk, record) loads a lane has in flight
+  int b, head, n, R;
+  int q0, q1, lg, lpc, per_pass, sub;
+  const float* rec0;   // record of the first participant (position 1 of its CTA)
+  const float* rec1;   // record of the second participant (position 0); later ones follow at rec_stride
+  long long rec_stride;
+  struct Loads { float m[kBatch], l[kBatch]; float4 v[kBatch]; bool act[kBatch]; };
 
-  // ---- wait (bounded) until every participant has published its record ----
-  // Every lane reads the counter with acquire semantics (one request per warp), so the record loads
-  // below need no further fence.
-  {
-    bool there = ld_acquire_gpu(counter) >= n;
-    if (!__all_sync(kFullMask, there)) {
-      const unsigned long long t0 = global_ns();
-      for (uint32_t it = 0;; ++it) {
-        __nanosleep(32);
-        there = ld_acquire_gpu(counter) >= n;
-        if (__all_sync(kFullMask, there)) break;
-        if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > kWaitLimitNs)) {
-          if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
-          return false;
-        }
+  __device__ __forceinline__ void setup(const FdParams& p, int b_, int head_, int first_cta, int n_, int me, int HG,
+                                        int warp, int lane) {
+    b = b_; head = head_; n = n_; R = p.R;
+    const int Q = R * C4;
+    q0 = (int)(((long long)me * Q) / n);
+    q1 = (int)(((long long)(me + 1) * Q) / n);
+    lg = 5;
+    while (lg > 0 && ((q1 - q0) << lg) > kWarp) --lg;
+    lpc = 1 << lg;
+    per_pass = kWarp >> lg;
+    sub = lane & (lpc - 1);
+    rec0 = p.records + (long long)fd_record_index(first_cta, first_cta, HG, warp) * p.rec_floats;
+    rec1 = p.records + (long long)fd_record_index(first_cta + 1, first_cta, HG, warp) * p.rec_floats;
+    rec_stride = 2LL * HG * p.rec_floats;
+  }
+  // True when one round of loads covers the whole job.
+  __device__ __forceinline__ bool single_round() const { return q1 - q0 <= per_pass && n <= kBatch * lpc; }
+
+  __device__ __forceinline__ void load(Loads& ld, int base, int k0, int lane) const {
+    const int q = q0 + base + (lane >> lg);
+    const int r = q / C4, d = (q & (C4 - 1)) * 4;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int rec = k0 + sub + j * lpc;
+      ld.act[j] = q < q1 && rec < n;
+      if (ld.act[j]) {
+        const float* rc = rec == 0 ? rec0 : rec1 + (rec - 1) * rec_stride;
+        ld.m[j] = __ldcg(rc + R * D + r);
+        ld.l[j] = __ldcg(rc + R * D + R + r);
+        ld.v[j] = __ldcg(reinterpret_cast<const float4*>(rc + r * D + d));
       }
     }
   }
-
-  const int Q = R * C4;
-  const int q0 = (int)(((long long)me * Q) / n), q1 = (int)(((long long)(me + 1) * Q) / n);
-  const int chunks = q1 - q0;
-  int lg = 5;  // log2(lanes per chunk)
-  while (lg > 0 && (chunks << lg) > kWarp) --lg;
-  const int lpc = 1 << lg;
-  const int per_pass = kWarp >> lg;  // chunks per pass of the warp
-  const int sub = lane & (lpc - 1);
-  const long long hq0 = (long long)head * R;
-  const float* rec0 = p.records + (long long)fd_record_index(first_cta, first_cta, HG, warp) * p.rec_floats;
-  // records of CTAs after the first sit at position 0 of their CTA: a constant stride apart
-  const long long rec_stride = 2LL * HG * p.rec_floats;
-  const float* rec1 = p.records + (long long)fd_record_index(first_cta + 1, first_cta, HG, warp) * p.rec_floats;
-
-  for (int base = 0; base < chunks; base += per_pass) {
-    const int q = q0 + base + (lane >> lg);
-    const bool mine = q < q1;
-    const int r = q / C4, d = (q & (C4 - 1)) * 4;
-    Chunk4 acc;
-    acc.clear();
-    for (int k0 = 0; k0 < n; k0 += kBatch * lpc) {
-      float m[kBatch], l[kBatch];
-      float4 v[kBatch];
-      bool act[kBatch];
+  __device__ __forceinline__ void fold(Chunk4& acc, const Loads& ld) const {
 #pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const int rec = k0 + sub + j * lpc;
-        act[j] = mine && rec < n;
-        if (act[j]) {
-          const float* rc = rec == 0 ? rec0 : rec1 + (rec - 1) * rec_stride;
-          m[j] = __ldcg(rc + R * D + r);
-          l[j] = __ldcg(rc + R * D + R + r);
-          v[j] = __ldcg(reinterpret_cast<const float4*>(rc + r * D + d));
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j)
-        if (act[j]) acc.fold(m[j], l[j], v[j].x, v[j].y, v[j].z, v[j].w);
-    }
+    for (int j = 0; j < kBatch; ++j)
+      if (ld.act[j]) acc.fold(ld.m[j], ld.l[j], ld.v[j].x, ld.v[j].y, ld.v[j].z, ld.v[j].w);
+  }
+  // Butterfly over the lanes of a chunk, then the chunk's four outputs are normalised and written.
+  __device__ __forceinline__ void finish(Chunk4& acc, const FdParams& p, int base, int lane) const {
     for (int off = lpc >> 1; off >= 1; off >>= 1) {
       const float m2 = __shfl_xor_sync(kFullMask, acc.m, off), l2 = __shfl_xor_sync(kFullMask, acc.l, off);
       const float x = __shfl_xor_sync(kFullMask, acc.o[0], off), y = __shfl_xor_sync(kFullMask, acc.o[1], off);
       const float z = __shfl_xor_sync(kFullMask, acc.o[2], off), w = __shfl_xor_sync(kFullMask, acc.o[3], off);
       acc.fold(m2, l2, x, y, z, w);
     }
-    if (mine && sub == 0) {
+    const int q = q0 + base + (lane >> lg);
+    if (q < q1 && sub == 0) {
+      const int r = q / C4, d = (q & (C4 - 1)) * 4;
+      const long long hq = (long long)head * R + r;
       const float inv = acc.l > 0.f ? 1.f / acc.l : 0.f;
       if (p.out) {
-        __nv_bfloat16* ob = p.out + (long long)b * p.o_sb + (hq0 + r) * p.o_sh + d;
+        __nv_bfloat16* ob = p.out + (long long)b * p.o_sb + hq * p.o_sh + d;
         *reinterpret_cast<uint32_t*>(ob) = pack_bf16x2(acc.o[0] * inv, acc.o[1] * inv);
         *reinterpret_cast<uint32_t*>(ob + 2) = pack_bf16x2(acc.o[2] * inv, acc.o[3] * inv);
       }
       if (p.o_partial) {
-        float* ob = p.o_partial + ((long long)b * p.Hq + hq0 + r) * D + d;
+        float* ob = p.o_partial + ((long long)b * p.Hq + hq) * D + d;
         *reinterpret_cast<float4*>(ob) = make_float4(acc.o[0] * inv, acc.o[1] * inv, acc.o[2] * inv, acc.o[3] * inv);
         if (d == 0)
-          p.lse[(long long)b * p.Hq + hq0 + r] = acc.l > 0.f ? (acc.m + log2f(acc.l)) * 0.6931471805599453f : -INFINITY;
+          p.lse[(long long)b * p.Hq + hq] = acc.l > 0.f ? (acc.m + log2f(acc.l)) * 0.6931471805599453f : -INFINITY;
       }
     }
   }
-  return true;
+  // The general form: as many passes over chunks and rounds over records as the job needs.
+  __device__ __forceinline__ void run(const FdParams& p, int lane) const {
+    for (int base = 0; base < q1 - q0; base += per_pass) {
+      Chunk4 acc;
+      acc.clear();
+      for (int k0 = 0; k0 < n; k0 += kBatch * lpc) {
+        Loads ld;
+        load(ld, base, k0, lane);
+        fold(acc, ld);
+      }
+      finish(acc, p, base, lane);
+    }
+  }
+};
+
+// Waits (bounded) until all n participants of a unit have announced their records.  Every lane reads the
+// counter with acquire semantics (one request per warp), so the record loads that follow need no fence.
+__device__ __forceinline__ bool wait_for_records(const FdParams& p, const int* counter, int n, int lane) {
+  bool there = ld_acquire_gpu(counter) >= n;
+  if (__all_sync(kFullMask, there)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 0;; ++it) {
+    __nanosleep(32);
+    there = ld_acquire_gpu(counter) >= n;
+    if (__all_sync(kFullMask, there)) return true;
+    if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > kWaitLimitNs)) {
+      if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+      return false;
+    }
+  }
+}
+
+// Merges this warp's slices of its (at most two) shared units.  When both fit in one round of loads each, the
+// loads of the second unit are issued before the first is folded, so the two merges cost one memory round trip.
+// merged[w] tells whether unit w was merged (false: not shared, or the wait ran out).  Kept out of line so
+// that its registers do not weigh on the streaming loop.
+template <int D>
+__device__ __noinline__ void merge_shared_units(const FdParams& p, const int* def_b, const int* def_head,
+                                                const int* def_first, const int* def_n, int cta, int HG, int warp,
+                                                int lane, bool* merged) {
+  SliceJob<D> job[2];
+  bool on[2];
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    on[w] = def_n[w] > 1;
+    if (on[w]) on[w] = wait_for_records(p, p.counters + def_b[w] * p.Hkv + def_head[w], def_n[w], lane);
+    if (on[w]) job[w].setup(p, def_b[w], def_head[w], def_first[w], def_n[w], cta - def_first[w], HG, warp, lane);
+    merged[w] = on[w];
+  }
+  if (on[0] && on[1] && job[0].single_round() && job[1].single_round()) {
+    typename SliceJob<D>::Loads l0, l1;
+    job[0].load(l0, 0, 0, lane);
+    job[1].load(l1, 0, 0, lane);
+    Chunk4 a0, a1;
+    a0.clear();
+    a1.clear();
+    job[0].fold(a0, l0);
+    job[0].finish(a0, p, 0, lane);
+    job[1].fold(a1, l1);
+    job[1].finish(a1, p, 0, lane);
+  } else {
+    if (on[0]) job[0].run(p, lane);
+    if (on[1]) job[1].run(p, lane);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -709,10 +760,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     }
     FD_TRACE(5);
     bool merged[2] = {false, false};
-#pragma unroll
-    for (int w = 0; w < 2; ++w)
-      if (def_n[w] > 1)
-        merged[w] = merge_slice<D>(p, def_b[w], def_head[w], def_first[w], def_n[w], cta - def_first[w], HG, warp, lane);
+    merge_shared_units<D>(p, def_b, def_head, def_first, def_n, cta, HG, warp, lane, merged);
     FD_TRACE(6);
     __syncwarp();
     if (lane == 0) {

@@ -137,14 +137,26 @@ Tensor flash_attention_decode(Tensor query, Tensor keys, Tensor values, std::opt
 }
 
 // Attention over a slice of the cached sequence, returned as fp32 (o, lse) for lse_merge.
+// `out_o` / `out_lse` (contiguous fp32 [B,Hq,D] / [B,Hq]) let the caller choose where the result lands, e.g. in
+// its slot of an exchange buffer that peers can address.
 std::tuple<Tensor, Tensor> flash_attention_decode_partial(Tensor query, Tensor keys, Tensor values,
                                                           std::optional<Tensor> seq_lens, double scale,
-                                                          int64_t max_ctas) {
+                                                          int64_t max_ctas, std::optional<Tensor> out_o,
+                                                          std::optional<Tensor> out_lse) {
   const DecodeShapes s = check_decode_inputs(query, keys, values, seq_lens);
   const c10::cuda::CUDAGuard guard(query.device());
   auto f32 = torch::dtype(torch::kFloat32).device(query.device());
-  Tensor o = torch::empty({s.B, s.Hq, s.D}, f32);
-  Tensor lse = torch::empty({s.B, s.Hq}, f32);
+  TORCH_CHECK(out_o.has_value() == out_lse.has_value(), "out_o and out_lse go together");
+  if (out_o) {
+    TORCH_CHECK(out_o->is_cuda() && out_o->scalar_type() == torch::kFloat32 && out_o->is_contiguous() &&
+                    out_o->numel() == (int64_t)s.B * s.Hq * s.D && out_lse->is_cuda() &&
+                    out_lse->scalar_type() == torch::kFloat32 && out_lse->is_contiguous() &&
+                    out_lse->numel() == (int64_t)s.B * s.Hq && out_o->get_device() == query.get_device() &&
+                    out_lse->get_device() == query.get_device(),
+                "out_o / out_lse must be contiguous fp32 CUDA tensors of B*Hq*D / B*Hq elements");
+  }
+  Tensor o = out_o ? *out_o : torch::empty({s.B, s.Hq, s.D}, f32);
+  Tensor lse = out_lse ? *out_lse : torch::empty({s.B, s.Hq}, f32);
   if (s.B == 0) return {o, lse};
   run_decode(query, keys, values, seq_lens, nullptr, &o, &lse, scale, max_ctas, s);
   return {o, lse};
@@ -166,6 +178,27 @@ Tensor lse_merge(Tensor o_parts, Tensor lse_parts) {
   check_status(l3ci_lse_merge(o_parts.data_ptr<float>(), lse_parts.data_ptr<float>(), out.data_ptr(), parts, B, Hq,
                               D, out.stride(0), out.stride(1), current_stream()),
                "lse_merge");
+  return out;
+}
+
+// Exchange of shard results over peer memory fused with their merge (l3ci_lse_exchange_merge).  `bufs` is an
+// int64 CUDA tensor [ranks] holding the base addresses of every rank's exchange buffer as this process sees
+// them; this rank's own result must already be in its slot of parity epoch & 1.
+Tensor lse_exchange_merge(Tensor bufs, int64_t rank, int64_t epoch, int64_t B, int64_t Hq, int64_t D,
+                          std::optional<Tensor> status) {
+  TORCH_CHECK(bufs.is_cuda() && bufs.scalar_type() == torch::kInt64 && bufs.dim() == 1 && bufs.is_contiguous(),
+              "bufs must be a contiguous int64 CUDA tensor of buffer addresses");
+  if (status)
+    TORCH_CHECK(status->is_cuda() && status->scalar_type() == torch::kInt32 && status->numel() >= 1 &&
+                    status->get_device() == bufs.get_device(),
+                "status must be an int32 CUDA tensor");
+  const c10::cuda::CUDAGuard guard(bufs.device());
+  Tensor out = torch::empty({B, 1, Hq, D}, torch::dtype(torch::kBFloat16).device(bufs.device())).transpose(1, 2);
+  check_status(l3ci_lse_exchange_merge(reinterpret_cast<void* const*>(bufs.data_ptr<int64_t>()), (int32_t)rank,
+                                       (int32_t)bufs.size(0), (uint32_t)epoch, out.data_ptr(), (int32_t)B, (int32_t)Hq,
+                                       (int32_t)D, out.stride(0), out.stride(1),
+                                       status ? status->data_ptr<int32_t>() : nullptr, current_stream()),
+               "lse_exchange_merge");
   return out;
 }
 
@@ -287,7 +320,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("n_head"), py::arg("n_kv_head"), py::kw_only(), py::arg("positions") = py::none());
   m.def("flash_attention_decode_partial", torch::wrap_pybind_function(flash_attention_decode_partial),
         "flash_attention_decode_partial", py::arg("query"), py::arg("keys"), py::arg("values"), py::kw_only(),
-        py::arg("seq_lens") = py::none(), py::arg("scale") = 0.0, py::arg("max_ctas") = 0);
+        py::arg("seq_lens") = py::none(), py::arg("scale") = 0.0, py::arg("max_ctas") = 0,
+        py::arg("out_o") = py::none(), py::arg("out_lse") = py::none());
+  m.def("lse_exchange_merge", torch::wrap_pybind_function(lse_exchange_merge), "lse_exchange_merge", py::arg("bufs"),
+        py::arg("rank"), py::arg("epoch"), py::arg("B"), py::arg("Hq"), py::arg("D"), py::kw_only(),
+        py::arg("status") = py::none());
+  m.def("lse_exchange_bytes", [](int64_t ranks, int64_t B, int64_t Hq, int64_t D) {
+    return (int64_t)l3ci_lse_exchange_bytes((int32_t)ranks, (int32_t)B, (int32_t)Hq, (int32_t)D);
+  });
   m.def("lse_merge", torch::wrap_pybind_function(lse_merge), "lse_merge", py::arg("o_parts"), py::arg("lse_parts"));
   m.def("flash_decode_status", torch::wrap_pybind_function(flash_decode_status), "flash_decode_status",
         py::arg("like"));

@@ -10,7 +10,11 @@ attention shards:
   ((D + 1) * Hq * 4 bytes per sequence and rank) and merged by log-sum-exp on every rank
   (`kv_shard_bounds`, `local_seq_lens`, `exchange_partials`, `decode_kv_sharded`).
 
-Only `decode_kv_sharded` touches a GPU; the rest is integer arithmetic and `torch.distributed`
+`KvShardExchange` + `decode_kv_sharded_fused` replace the all-gather and the merge kernel by ONE kernel per rank
+that pushes the rank's (o, lse) into its peers' memory over NVLink and merges what the peers pushed
+(`lse_exchange_merge`); the buffers are torch symmetric memory.
+
+Only `decode_kv_sharded*` touch a GPU; the rest is integer arithmetic and `torch.distributed`
 plumbing that also runs over gloo on CPU.
 """
 from __future__ import annotations
@@ -82,3 +86,57 @@ def decode_kv_sharded(ext, q: torch.Tensor, k_local: torch.Tensor, v_local: torc
         return ext.lse_merge(o.unsqueeze(0), lse.unsqueeze(0))
     o_parts, lse_parts = exchange_partials(o, lse, group)
     return ext.lse_merge(o_parts, lse_parts)
+
+
+class KvShardExchange:
+    """Peer-addressable buffers for the fused exchange + merge of shard results on one box.
+
+    One instance per (process group, B, Hq, D).  Construction is collective (every rank of `group` must create
+    it in the same order): it allocates torch symmetric memory of `lse_exchange_bytes` bytes, zero-fills it and
+    exchanges the handles.  `slot()` gives the fp32 views this rank's decode kernel writes its shard result to;
+    `merge()` launches the fused kernel.  Calls are numbered by an epoch that advances identically on all
+    ranks, so every rank must make the same sequence of `slot()` / `merge()` calls."""
+
+    def __init__(self, ext, B: int, Hq: int, D: int, device, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.ext, self.B, self.Hq, self.D = ext, B, Hq, D
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        nbytes = ext.lse_exchange_bytes(self.world, B, Hq, D)
+        self.buf = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group.group_name)
+        self.bufs = torch.tensor(list(self.handle.buffer_ptrs), dtype=torch.int64, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.rows = B * Hq
+        self.slot_floats = self.rows * D + ((self.rows + 3) & ~3)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        self.handle.barrier()          # every rank's buffer is zeroed before anyone may push into it
+
+    def slot(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Starts the next exchange and returns (o [B,Hq,D], lse [B,Hq]) views of this rank's own slot."""
+        self.epoch += 1
+        base = ((self.epoch & 1) * self.world + self.rank) * self.slot_floats
+        o = self.buf[base: base + self.rows * self.D].view(self.B, self.Hq, self.D)
+        lse = self.buf[base + self.rows * self.D: base + self.rows * self.D + self.rows].view(self.B, self.Hq)
+        return o, lse
+
+    def merge(self) -> torch.Tensor:
+        """Pushes this rank's slot to the peers, waits for theirs, merges: bf16 [B,Hq,1,D] on every rank."""
+        return self.ext.lse_exchange_merge(self.bufs, self.rank, self.epoch, self.B, self.Hq, self.D,
+                                           status=self.status)
+
+    def check(self) -> int:
+        """Synchronises and returns the device status word (0 = every wait was satisfied)."""
+        return int(self.status.item())
+
+
+def decode_kv_sharded_fused(ext, q: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
+                            xchg: KvShardExchange, seq_lens_local: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`decode_kv_sharded` with the exchange and the merge in one kernel over peer memory: two launches per step
+    (shard attention into the exchange slot, then push + wait + merge) and no collective call."""
+    o, lse = xchg.slot()
+    ext.flash_attention_decode_partial(q, k_local, v_local, seq_lens=seq_lens_local, out_o=o, out_lse=lse)
+    return xchg.merge()

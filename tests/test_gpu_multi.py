@@ -21,7 +21,8 @@ def _free_port():
 
 
 def _rank_main(rank, world, port, q):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -37,6 +38,17 @@ def _rank_main(rank, world, port, q):
         torch.cuda.synchronize()
         want = attention.sdpa_reference(case.q, case.k, case.v, case.seq_lens)
         compare.assert_close_attention(out, want)
+        # --- the same with the exchange fused into the merge kernel (peer stores over NVLink), three steps in a
+        #     row so that both parities of the exchange buffer and their reuse are exercised
+        xchg = pkg.sharding.KvShardExchange(ext, 2, 32, 128, dev)
+        for step in range(3):
+            c = inputs.decode_case(2, 32, 8, 128, 6000, seed=70 + step, ragged=True, min_len=100)
+            d = c.to(dev)
+            ll = pkg.sharding.local_seq_lens(d.seq_lens, lo, hi)
+            got = pkg.sharding.decode_kv_sharded_fused(ext, d.q, d.k[:, :, lo:hi], d.v[:, :, lo:hi], xchg, ll)
+            torch.cuda.synchronize()
+            compare.assert_close_attention(got, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
+        assert xchg.check() == 0
         # --- batch sharded by sequence: every rank computes its own sequences, nothing is exchanged
         batch = inputs.config2(seed=62)
         mine = pkg.sharding.partition_batch(batch.seq_lens.tolist(), world)[rank]
