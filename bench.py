@@ -226,6 +226,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-comparator", action="store_true", help="c1-c3: skip the torch SDPA timing on the GPU")
+    ap.add_argument("--no-graph", action="store_true", help="c1-c3: launch every step through the extension call "
+                    "instead of replaying a captured launch")
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--nccl-merge", action="store_true", help="c3 on >1 GPU: all_gather + merge kernel instead of the fused exchange")
     args = ap.parse_args()
@@ -332,17 +335,24 @@ def bench_decode(args, ext, pkg, dev, rank, world):
             return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
         return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
 
+    # The launches of the rotating caches are captured back to back in one CUDA graph: the timed loop then
+    # costs the host one graph launch per n_rot steps instead of the extension's argument checks and
+    # tensor-map encoding per step, which take as long as a short kernel.  (The fused exchange numbers its
+    # calls on the host and stays eager.)
+    use_graph = not args.no_graph and not sharded_seq
+    run_steps = graph_runner(step, n_rot, dev) if use_graph else eager_runner(step)
+    run_steps.prepare(args.warmup)
+    run_steps.prepare(args.steps)
+
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     sampler.mark("w0")
-    for i in range(args.warmup):
-        step(i)
+    run_steps(args.warmup)
     sync_all(world)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.mark("t0")
     start.record()
-    for i in range(args.steps):
-        step(i)
+    run_steps(args.steps)
     end.record()
     torch.cuda.synchronize()
     sampler.mark("t1")
@@ -370,6 +380,34 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         roofline["note"] = "per-rank shard; the step also holds the exchange of shard results and their merge"
     if xchg is not None and xchg.check() != 0:
         raise RuntimeError("exchange wait ran out")
+
+    # ---- comparator on the same GPU: torch's own attention (the call the reference checks itself against,
+    # benchmark_kernel.py:27-28), same rotating caches, same timing; informational ----
+    comparators = None
+    if world == 1 and not args.no_comparator:
+        import torch.nn.functional as F
+
+        mask = None
+        if lens is not None:
+            mask = (torch.arange(case.k.shape[2], device=dev)[None, :] < lens[:, None])[:, None, None, :]
+        try:
+            sd_step = lambda i: F.scaled_dot_product_attention(q, ks[i % n_rot], vs[i % n_rot], attn_mask=mask,  # noqa: E731
+                                                               enable_gqa=True)
+            sd_run = graph_runner(sd_step, n_rot, dev) if use_graph else eager_runner(sd_step)
+            n_sd = max(n_rot, min(args.steps, 200))
+            sd_run.prepare(n_sd)
+            sd_run(n_rot)
+            torch.cuda.synchronize()
+            start.record()
+            sd_run(n_sd)
+            end.record()
+            torch.cuda.synchronize()
+            sd_ms = start.elapsed_time(end) / n_sd
+            comparators = {"torch_sdpa_gpu": {"ms_per_step": sd_ms, "GB/s": my_bytes / (sd_ms * 1e-3) / 1e9, "steps": n_sd,
+                                              "call": "F.scaled_dot_product_attention(q, k, v, enable_gqa=True" +
+                                                      (", attn_mask=lengths)" if mask is not None else ")")}}
+        except Exception as exc:  # the comparator is optional evidence, never a reason to lose the bench line
+            comparators = {"torch_sdpa_gpu": {"error": str(exc)[:200]}}
 
     # ---- end to end through the extension with host buffers (pinned), copies inside the timed region ----
     hq, hk, hv = case.q.contiguous().pin_memory(), case.k.pin_memory(), case.v.pin_memory()
@@ -421,6 +459,8 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         "scaling": "strong" if sharded_seq else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
                    "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
+                   "launch": f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back" if use_graph
+                             else "each step is an eager extension call",
                    "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
                                                                   "fused NVLink exchange/merge kernel")) if sharded_seq else
                                   ("data-parallel x%d, no collective" % world),
@@ -430,7 +470,57 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if comparators is not None:
+        line["comparators"] = comparators
     return line
+
+
+def graph_runner(step, n_rot, dev):
+    """Returns run_steps(K): K steps as replays of a CUDA graph that holds the n_rot launches step(0..n_rot-1)
+    back to back (plus one graph of K % n_rot launches), so that consecutive launches follow each other on the
+    device without waiting for the host."""
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        step(0)  # per-stream workspaces are allocated outside the capture
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graphs = {}
+    keep = []  # results of the captured calls stay alive, so every step of a graph writes its own buffer
+
+    def graph_of(n):
+        if n not in graphs:
+            side.wait_stream(torch.cuda.current_stream(dev))
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(gr, stream=side):
+                    for j in range(n):
+                        keep.append(step(j))
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graphs[n] = gr
+        return graphs[n]
+
+    def prepare(K):
+        graph_of(n_rot)
+        if K % n_rot:
+            graph_of(K % n_rot)
+
+    def run_steps(K):
+        for _ in range(K // n_rot):
+            graphs[n_rot].replay()
+        if K % n_rot:
+            graphs[K % n_rot].replay()
+
+    run_steps.prepare = prepare
+    return run_steps
+
+
+def eager_runner(step):
+    def run_steps(K):
+        for i in range(K):
+            step(i)
+
+    run_steps.prepare = lambda K: None
+    return run_steps
 
 
 def bench_pre_attention(args, ext, pkg, dev, rank, world):
@@ -450,23 +540,24 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world):
         desc = "C4 RMSNorm: tokens 4096 x hidden 2048 bf16, eps 1e-5"
     else:
         qs = [qkv.to(dev) if i == 0 else torch.randn_like(qkv.float(), device=dev).bfloat16() for i in range(n_rot)]
-        ck = torch.zeros(B, S, Hkv, D, dtype=torch.bfloat16, device=dev)
-        cv = torch.zeros_like(ck)
+        cks = [torch.zeros(B, S, Hkv, D, dtype=torch.bfloat16, device=dev) for _ in range(n_rot)]
+        cvs = [torch.zeros_like(cks[0]) for _ in range(n_rot)]
         nbytes = 2 * qkv.numel() * 2 + freq.numel() * 4
-        step = lambda i: ext.rot_embed_kv_cache(qs[i % n_rot], freq, ck, cv, 0, Hq, Hkv)
+        step = lambda i: ext.rot_embed_kv_cache(qs[i % n_rot], freq, cks[i % n_rot], cvs[i % n_rot], 0, Hq, Hkv)
         kernel = "rot_embed_kv_cache_kernel"
         desc = "C4 fused RoPE + KV-cache write: tokens 4096, q 32x64, k/v 8x64 bf16, Llama-3 scaling factor 32"
+    run_steps = eager_runner(step) if args.no_graph else graph_runner(step, n_rot, dev)
+    run_steps.prepare(args.warmup)
+    run_steps.prepare(args.steps)
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     sampler.start()
     sampler.mark("w0")
-    for i in range(args.warmup):
-        step(i)
+    run_steps(args.warmup)
     sync_all(world)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.mark("t0")
     start.record()
-    for i in range(args.steps):
-        step(i)
+    run_steps(args.steps)
     end.record()
     torch.cuda.synchronize()
     sampler.mark("t1")
@@ -481,8 +572,9 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world):
         "metric": "pre-attention HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": desc, "l2": f"{n_rot} rotating inputs > 126 MB L2", "bytes_per_step": nbytes,
-                   "note": "includes the output allocation of the reference-shaped call (torch caching allocator)"},
+        "config": {"workload": desc, "l2": f"{n_rot} rotating inputs and outputs > 126 MB L2", "bytes_per_step": nbytes,
+                   "launch": "each step is an eager extension call (with its output allocation)" if args.no_graph else
+                             f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "kernel": kernel},
         "gpu_launches": args.steps, "clocks": sampler.summary(),
@@ -543,12 +635,13 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
         "config": {"workload": f"C5 random-init Llama-3.2-1B architecture, batch {B}/GPU, prompt {P}, {G} greedy tokens",
                    "global_batch": B * world, "parallelism": "replicas x%d" % world,
                    "l2": "working set per decode step (2.5 GB weights + KV cache) >> 126 MB L2",
-                   "note": "GEMMs are cuBLAS via torch; RMSNorm, RoPE + cache write and decode attention are this "
+                   "note": "GEMMs are cuBLAS via torch; RMSNorm (+ residual add), SiLU*mul, RoPE + cache write and decode attention are this "
                            "repository's kernels; the decode step is replayed from a CUDA graph",
                    "reference_published_rtx4060_tokens_per_s": 2041.67},
         "e2e": e2e,
-        # per decode step: 33 RMSNorm + 16 fused RoPE/cache + 16 flash-decode launches of this library
-        "gpu_launches": decode_steps * 65 + steps * 49, "clocks": sampler.summary(),
+        # per decode step: 33 RMSNorm (32 with the residual add) + 16 SiLU*mul + 16 fused RoPE/cache + 16
+        # flash-decode launches of this library; the prefill pass has no flash-decode
+        "gpu_launches": decode_steps * 81 + steps * 65, "clocks": sampler.summary(),
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu

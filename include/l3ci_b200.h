@@ -58,6 +58,19 @@ L3CI_API int l3ci_rms_norm(const void* x, const void* weight, void* out,
                            int64_t x_row_stride, int64_t out_row_stride,
                            float eps, l3ci_stream_t stream);
 
+/* Residual add fused into RMSNorm:  s = bf16(x + residual) (written to sum_out), out = rmsnorm(s) * w.
+ * Does in one pass what Block.forward does with an elementwise add followed by ln_2 / the next block's
+ * ln_1 (model.py:147-148).  All tensors dense [rows, embed]. */
+L3CI_API int l3ci_add_rms_norm(const void* x, const void* residual, const void* weight,
+                               void* sum_out, void* out, int64_t rows, int64_t embed, float eps,
+                               l3ci_stream_t stream);
+
+/* SwiGLU gate:  out = bf16( bf16(silu(gate)) * up ) over [rows, cols] (cols a multiple of 8), out dense,
+ * gate and up with their own row strides in elements (so both may be halves of one [rows, 2*cols] GEMM
+ * result).  The `F.silu(self.c_fc2(x)) * self.c_fc(x)` of MLP.forward (model.py:134) as one kernel. */
+L3CI_API int l3ci_silu_mul(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                           int64_t gate_row_stride, int64_t up_row_stride, l3ci_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Rotary embedding, interleaved-pair (Meta) convention:
  *   (x', y') = (x*c - y*s, x*s + y*c) for (x, y) = in[.., 2i], in[.., 2i+1] and

@@ -19,7 +19,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 # Every symbol include/l3ci_b200.h declares.
 EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
-    "l3ci_rms_norm", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
+    "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge",
 )
@@ -68,6 +68,10 @@ def load() -> C.CDLL:
     lib.l3ci_version.argtypes = []
     lib.l3ci_rms_norm.restype = C.c_int
     lib.l3ci_rms_norm.argtypes = [vp, vp, vp, i64, i64, i64, i64, f32, vp]
+    lib.l3ci_add_rms_norm.restype = C.c_int
+    lib.l3ci_add_rms_norm.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, vp]
+    lib.l3ci_silu_mul.restype = C.c_int
+    lib.l3ci_silu_mul.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp]
     lib.l3ci_rot_embed.restype = C.c_int
     lib.l3ci_rot_embed.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp]
     lib.l3ci_rot_embed_kv_cache.restype = C.c_int
@@ -123,6 +127,31 @@ def rms_norm(x, weight, eps: float):
     with _on(x):
         _check(load().l3ci_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, E, E, E, eps, _stream(x)),
                "l3ci_rms_norm")
+    return out
+
+
+def add_rms_norm(x, residual, weight, eps: float):
+    """Returns (bf16(x + residual), rmsnorm of that sum * weight); dense [..., E] tensors."""
+    import torch
+
+    assert x.is_contiguous() and residual.is_contiguous() and x.shape == residual.shape
+    s, out = torch.empty_like(x), torch.empty_like(x)
+    E = x.shape[-1]
+    with _on(x):
+        _check(load().l3ci_add_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), s.data_ptr(),
+                                        out.data_ptr(), x.numel() // E, E, eps, _stream(x)), "l3ci_add_rms_norm")
+    return s, out
+
+
+def silu_mul(gate, up):
+    """bf16(bf16(silu(gate)) * up) for 2-D tensors of equal shape whose rows are contiguous."""
+    import torch
+
+    assert gate.dim() == 2 and gate.shape == up.shape and gate.stride(1) == 1 and up.stride(1) == 1
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+    with _on(gate):
+        _check(load().l3ci_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.shape[0], gate.shape[1],
+                                    gate.stride(0), up.stride(0), _stream(gate)), "l3ci_silu_mul")
     return out
 
 

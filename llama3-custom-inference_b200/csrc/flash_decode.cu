@@ -68,10 +68,17 @@ struct FdCfg {
 __device__ unsigned long long* g_fd_trace = nullptr;
 #define FD_TRACE(slot)                                                                       \
   do {                                                                                       \
-    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 8 + (slot)] = global_ns(); \
+    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 16 + (slot)] = global_ns(); \
   } while (0)
+#define FD_TRACE_VAL(slot, v)                                                                 \
+  do {                                                                                       \
+    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 16 + (slot)] = (v); \
+  } while (0)
+#define FD_TRACE_ONLY(...) __VA_ARGS__
 #else
 #define FD_TRACE(slot) do { } while (0)
+#define FD_TRACE_VAL(slot, v) do { } while (0)
+#define FD_TRACE_ONLY(...)
 #endif
 
 struct FdParams {
@@ -300,16 +307,22 @@ struct SliceJob {
   }
 };
 
-// Waits (bounded) until all n participants of a unit have announced their records.  Every lane reads the
-// counter with acquire semantics (one request per warp), so the record loads that follow need no fence.
-__device__ __forceinline__ bool wait_for_records(const FdParams& p, const int* counter, int n, int lane) {
-  bool there = ld_acquire_gpu(counter) >= n;
-  if (__all_sync(kFullMask, there)) return true;
+// Waits (bounded) until the participants of this warp's (at most two) shared units have all announced their
+// records: counter c[w] must reach n[w] for every w with on[w].  Both counters are polled in the same round
+// trip.  Every lane reads with acquire semantics (one request per warp), so the record loads that follow need
+// no fence.
+__device__ __forceinline__ bool wait_for_records(const FdParams& p, const int* const* c, const int* n, const bool* on,
+                                                 int lane) {
+  auto poll = [&]() {
+    const int v0 = on[0] ? ld_acquire_gpu(c[0]) : 0;
+    const int v1 = on[1] ? ld_acquire_gpu(c[1]) : 0;
+    return (!on[0] || v0 >= n[0]) && (!on[1] || v1 >= n[1]);
+  };
+  if (__all_sync(kFullMask, poll())) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t it = 0;; ++it) {
     __nanosleep(32);
-    there = ld_acquire_gpu(counter) >= n;
-    if (__all_sync(kFullMask, there)) return true;
+    if (__all_sync(kFullMask, poll())) return true;
     if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > kWaitLimitNs)) {
       if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
       return false;
@@ -317,23 +330,30 @@ __device__ __forceinline__ bool wait_for_records(const FdParams& p, const int* c
   }
 }
 
-// Merges this warp's slices of its (at most two) shared units.  When both fit in one round of loads each, the
-// loads of the second unit are issued before the first is folded, so the two merges cost one memory round trip.
-// merged[w] tells whether unit w was merged (false: not shared, or the wait ran out).  Kept out of line so
-// that its registers do not weigh on the streaming loop.
+// Merges this warp's slices of its (at most two) shared units and counts the warp out of them: the counter of a
+// unit goes from n (all records announced) to 2n (all participants past their wait), and whoever brings it to 2n
+// zeroes it for the next launch.  The count-out is issued before the records are loaded, so its round trip
+// overlaps theirs.  When both merges fit in one round of loads each, the loads of the second unit are issued
+// before the first is folded, so the two merges cost one memory round trip.  If the wait runs out the units are
+// left unmerged and the counters as they are.  Kept out of line so that its registers do not weigh on the
+// streaming loop.
 template <int D>
 __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* def_b, const int* def_head,
                                                 const int* def_first, const int* def_n, int cta, int HG, int warp,
-                                                int lane, bool* merged) {
+                                                int lane) {
   SliceJob<D> job[2];
-  bool on[2];
+  const bool on[2] = {def_n[0] > 1, def_n[1] > 1};
+  int* const counter[2] = {p.counters + def_b[0] * p.Hkv + def_head[0], p.counters + def_b[1] * p.Hkv + def_head[1]};
+  if (!wait_for_records(p, counter, def_n, on, lane)) return;
+  int left[2] = {0, 0};
+  if (lane == 0) {
 #pragma unroll
-  for (int w = 0; w < 2; ++w) {
-    on[w] = def_n[w] > 1;
-    if (on[w]) on[w] = wait_for_records(p, p.counters + def_b[w] * p.Hkv + def_head[w], def_n[w], lane);
-    if (on[w]) job[w].setup(p, def_b[w], def_head[w], def_first[w], def_n[w], cta - def_first[w], HG, warp, lane);
-    merged[w] = on[w];
+    for (int w = 0; w < 2; ++w)
+      if (on[w]) left[w] = atomicAdd(counter[w], 1);
   }
+#pragma unroll
+  for (int w = 0; w < 2; ++w)
+    if (on[w]) job[w].setup(p, def_b[w], def_head[w], def_first[w], def_n[w], cta - def_first[w], HG, warp, lane);
   if (on[0] && on[1] && job[0].single_round() && job[1].single_round()) {
     typename SliceJob<D>::Loads l0, l1;
     job[0].load(l0, 0, 0, lane);
@@ -348,6 +368,11 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
   } else {
     if (on[0]) job[0].run(p, lane);
     if (on[1]) job[1].run(p, lane);
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int w = 0; w < 2; ++w)
+      if (on[w] && left[w] == 2 * def_n[w] - 1) *counter[w] = 0;
   }
 }
 
@@ -520,8 +545,47 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   int k_iter = 0;
   const int R = p.R;
   bool ok = true;
-  int def_b[2], def_head[2], def_first[2], def_n[2] = {0, 0};  // shared units to merge at the end
+  int def_b[2] = {0, 0}, def_head[2] = {0, 0}, def_first[2] = {0, 0}, def_n[2] = {0, 0};  // shared units to merge at the end
 
+  FD_TRACE_ONLY(long long trace_wait = 0, trace_c0 = 0, tr_qk = 0, tr_sm = 0, tr_pv = 0, tr_t = 0;)
+  // S = Q K^T for the kTile tokens of the stage at kb.  The k-steps are dealt to kChains accumulator sets that
+  // are added at the end, so that no tensor-core instruction waits on more than one predecessor.
+  auto qk_scores = [&](uint32_t kb, float (&sc)[C::NT_S][4]) {
+    constexpr int kChains = C::KS / 2;
+    float part[kChains][C::NT_S][4];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c)
+#pragma unroll
+      for (int nt = 0; nt < C::NT_S; ++nt) part[c][nt][0] = part[c][nt][1] = part[c][nt][2] = part[c][nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < C::KS; ++ks) {
+#pragma unroll
+      for (int ntp = 0; ntp < C::NT_S / 2; ++ntp) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = kb + (ks >> 2) * C::kBoxBytes + ntp * 2048 + k_row_off +
+                              (((2u * (ks & 3)) ^ k_x) << 4);
+        ldsm_x4(addr, b0, b1, b2, b3);
+        if constexpr (RHI) {
+          mma_bf16(part[ks % kChains][2 * ntp], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b0, b1);
+          mma_bf16(part[ks % kChains][2 * ntp + 1], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b2, b3);
+        } else {
+          mma_bf16(part[ks % kChains][2 * ntp], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+          mma_bf16(part[ks % kChains][2 * ntp + 1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < C::NT_S; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float a = part[0][nt][e];
+#pragma unroll
+        for (int c = 1; c < kChains; ++c) a += part[c][nt][e];
+        sc[nt][e] = a;
+      }
+  };
+  float s[C::NT_S][4];
+  bool have_s = false;
   while (cons.col < c1) {
     const int head = cons.g * HG + warp;
     if (seg_start) {
@@ -544,33 +608,30 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     }
 
     const int stage = k_iter % kStages;
-    const uint32_t parity = (k_iter / kStages) & 1;
-    if (!mbar_wait_bounded(bar0 + stage * 8, parity)) { ok = false; break; }
-    if (k_iter == 0) FD_TRACE(2);
     const uint32_t kb = stage0 + stage * kStageBytes;
     const uint32_t vb = kb + C::kKBytes;
-
-    // ---- S = Q K^T for kTile tokens ----
-    float s[C::NT_S][4];
-#pragma unroll
-    for (int nt = 0; nt < C::NT_S; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < C::KS; ++ks) {
-#pragma unroll
-      for (int ntp = 0; ntp < C::NT_S / 2; ++ntp) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t addr = kb + (ks >> 2) * C::kBoxBytes + ntp * 2048 + k_row_off +
-                              (((2u * (ks & 3)) ^ k_x) << 4);
-        ldsm_x4(addr, b0, b1, b2, b3);
-        if constexpr (RHI) {
-          mma_bf16(s[2 * ntp], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b0, b1);
-          mma_bf16(s[2 * ntp + 1], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b2, b3);
-        } else {
-          mma_bf16(s[2 * ntp], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-          mma_bf16(s[2 * ntp + 1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
-        }
-      }
+    if (!have_s) {
+      FD_TRACE_ONLY(const long long tw0 = clock64();)
+      if (!mbar_wait_bounded(bar0 + stage * 8, (k_iter / kStages) & 1)) { ok = false; break; }
+      FD_TRACE_ONLY(trace_wait += clock64() - tw0; if (k_iter == 0) trace_c0 = clock64();)
+      if (k_iter == 0) FD_TRACE(2);
+      qk_scores(kb, s);
     }
+    // Scores of the next tile, when it continues this unit: its K is normally in shared memory already, and its
+    // chain of tensor-core instructions has nothing to do with the softmax and the P.V of the current tile, so
+    // the two overlap in the instruction stream.
+    const bool more = !fd_unit_ends(cons, c1);
+    float s_next[C::NT_S][4];
+    if (more) {
+      const int st2 = (k_iter + 1) % kStages;
+      FD_TRACE_ONLY(const long long tw0 = clock64();)
+      if (!mbar_wait_bounded(bar0 + st2 * 8, ((k_iter + 1) / kStages) & 1)) { ok = false; break; }
+      FD_TRACE_ONLY(trace_wait += clock64() - tw0;)
+      FD_TRACE_ONLY(tr_t = clock64();)
+      qk_scores(stage0 + st2 * kStageBytes, s_next);
+      FD_TRACE_ONLY(tr_qk += clock64() - tr_t;)
+    }
+    FD_TRACE_ONLY(tr_t = clock64();)
 
     // ---- mask the tail of the sequence, online softmax (log2 domain) ----
     const int tok0 = cons.j * C::kTile;
@@ -633,6 +694,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       }
     }
 
+    FD_TRACE_ONLY(tr_sm += clock64() - tr_t; tr_t = clock64();)
     // ---- O += P V ----
 #pragma unroll
     for (int kk = 0; kk < C::KS_PV; ++kk) {
@@ -647,6 +709,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       }
     }
 
+    FD_TRACE_ONLY(tr_pv += clock64() - tr_t;)
     // ---- release the stage and refill it ----
     __syncwarp();
     if (prod.col < c1) {
@@ -655,6 +718,13 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       ++issued;
     }
     ++k_iter;
+    have_s = more;
+    if (more) {
+#pragma unroll
+      for (int nt = 0; nt < C::NT_S; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = s_next[nt][e];
+    }
 
     // ---- end of this (sequence, head) unit inside the CTA's range? ----
     if (fd_unit_ends(cons, c1)) {
@@ -747,9 +817,15 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     return;
   }
   FD_TRACE(3);
+  FD_TRACE_VAL(8, (unsigned long long)trace_wait);
+  FD_TRACE_VAL(9, (unsigned long long)(clock64() - trace_c0));
+  FD_TRACE_VAL(10, (unsigned long long)k_iter);
+  FD_TRACE_VAL(11, (unsigned long long)tr_qk);
+  FD_TRACE_VAL(12, (unsigned long long)tr_sm);
+  FD_TRACE_VAL(13, (unsigned long long)tr_pv);
   // ---- shared units ----
-  // Announce this warp's records (one fence for both), merge this CTA's slice of each unit once every
-  // participant has announced, then leave: the last participant to leave zeroes the counter.
+  // Announce this warp's records (one fence for both), then merge this CTA's slice of each unit once every
+  // participant has announced.
   if (def_n[0] > 1 || def_n[1] > 1) {
     __threadfence();
     __syncwarp();
@@ -759,19 +835,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
         if (def_n[w] > 1) atomicAdd(p.counters + def_b[w] * p.Hkv + def_head[w], 1);
     }
     FD_TRACE(5);
-    bool merged[2] = {false, false};
-    merge_shared_units<D>(p, def_b, def_head, def_first, def_n, cta, HG, warp, lane, merged);
+    merge_shared_units<D>(p, def_b, def_head, def_first, def_n, cta, HG, warp, lane);
     FD_TRACE(6);
-    __syncwarp();
-    if (lane == 0) {
-      int left[2] = {0, 0};
-#pragma unroll
-      for (int w = 0; w < 2; ++w)
-        if (merged[w]) left[w] = atomicAdd(p.counters + def_b[w] * p.Hkv + def_head[w], 1);
-#pragma unroll
-      for (int w = 0; w < 2; ++w)
-        if (merged[w] && left[w] == 2 * def_n[w] - 1) p.counters[def_b[w] * p.Hkv + def_head[w]] = 0;
-    }
   }
   FD_TRACE(4);
 }

@@ -6,8 +6,9 @@
 // arithmetic here is fp32 with one final rounding:
 //     out = bf16( (float(x) * rsqrt(sum(x^2)/E + eps)) * float(w) )
 //
-// Work split: a row of up to 2048 elements belongs to one warp (8 vectors per lane, no
-// shared memory, no barrier); longer rows get one CTA of 64..1024 threads.
+// Work split: a row of up to 512 elements belongs to one warp (no shared memory, no barrier);
+// longer rows get one CTA of 64..1024 threads with two vectors per thread (up to eight beyond
+// 16384 elements).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -24,11 +25,15 @@ struct RmsCfg {
   static constexpr int kRowsPerCta = kBlock / TPR;
 };
 
+// With `res` the row that is normalised is s = bf16(x + res) (what a bf16 tensor add produces); s is also
+// written to `sum_out`, which is the residual stream of the next layer (model.py:147-148 do the add and the
+// norm as separate kernels).
 template <int TPR, int VPT>
 __global__ void __launch_bounds__(RmsCfg<TPR>::kBlock)
 rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                 __nv_bfloat16* __restrict__ out, long long rows, int nvec, long long x_stride,
-                long long out_stride, float embed_f, float eps) {
+                long long out_stride, float embed_f, float eps, const __nv_bfloat16* __restrict__ res,
+                __nv_bfloat16* __restrict__ sum_out) {
   constexpr int kRows = RmsCfg<TPR>::kRowsPerCta;
   __shared__ float red[32];
   const int t = threadIdx.x % TPR;
@@ -43,8 +48,31 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     const int idx = t + i * TPR;
     if (row_ok && idx < nvec) {
       v[i] = ld_stream16(xr + (long long)idx * kVecElems);
+      if (res) {
+        // rows of res and sum_out are dense (stride = row length)
+        const long long off = row * ((long long)nvec * kVecElems) + (long long)idx * kVecElems;
+        const uint4 rv = ld_stream16(res + off);
+        float a[8], b[8];
+        unpack8(v[i], a);
+        unpack8(rv, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = __fadd_rn(a[j], b[j]);
+        v[i] = pack8(a);
+        *reinterpret_cast<uint4*>(sum_out + off) = v[i];
+      }
     } else {
       v[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  // the weight does not depend on the reduction: fetch it while the row is in flight
+  // (unless row + weight would not fit the registers a thread of this CTA size can have)
+  constexpr bool kEarlyW = VPT * RmsCfg<TPR>::kBlock <= 2048;
+  uint4 wv[VPT];
+  if constexpr (kEarlyW) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = t + i * TPR;
+      wv[i] = idx < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + idx) : make_uint4(0, 0, 0, 0);
     }
   }
 #pragma unroll
@@ -66,10 +94,10 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   for (int i = 0; i < VPT; ++i) {
     const int idx = t + i * TPR;
     if (idx < nvec) {
-      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w) + idx);
+      if constexpr (!kEarlyW) wv[i] = __ldg(reinterpret_cast<const uint4*>(w) + idx);
       float f[8], g[8];
       unpack8(v[i], f);
-      unpack8(wv, g);
+      unpack8(wv[i], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) f[j] = __fmul_rn(__fmul_rn(f[j], inv), g[j]);
       st_stream16(orow + (long long)idx * kVecElems, pack8(f));
@@ -79,24 +107,74 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 
 template <int TPR, int VPT>
 int launch(const void* x, const void* w, void* out, long long rows, int nvec, long long xs,
-           long long os, float eps, cudaStream_t stream) {
+           long long os, float eps, cudaStream_t stream, const void* res, void* sum_out) {
   constexpr int kRows = RmsCfg<TPR>::kRowsPerCta;
   const long long ctas = (rows + kRows - 1) / kRows;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rms_norm: too many rows (%lld)", rows);
   rms_norm_kernel<TPR, VPT><<<(unsigned)ctas, RmsCfg<TPR>::kBlock, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      static_cast<__nv_bfloat16*>(out), rows, nvec, xs, os, (float)(nvec * kVecElems), eps);
+      static_cast<__nv_bfloat16*>(out), rows, nvec, xs, os, (float)(nvec * kVecElems), eps,
+      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(sum_out));
   L3CI_CHECK_LAUNCH("rms_norm_kernel");
   return L3CI_OK;
 }
 
 template <int TPR>
 int launch_vpt(int vpt, const void* x, const void* w, void* out, long long rows, int nvec,
-               long long xs, long long os, float eps, cudaStream_t stream) {
-  if (vpt <= 1) return launch<TPR, 1>(x, w, out, rows, nvec, xs, os, eps, stream);
-  if (vpt <= 2) return launch<TPR, 2>(x, w, out, rows, nvec, xs, os, eps, stream);
-  if (vpt <= 4) return launch<TPR, 4>(x, w, out, rows, nvec, xs, os, eps, stream);
-  return launch<TPR, 8>(x, w, out, rows, nvec, xs, os, eps, stream);
+               long long xs, long long os, float eps, cudaStream_t stream, const void* res, void* sum_out) {
+  if (vpt <= 1) return launch<TPR, 1>(x, w, out, rows, nvec, xs, os, eps, stream, res, sum_out);
+  if (vpt <= 2) return launch<TPR, 2>(x, w, out, rows, nvec, xs, os, eps, stream, res, sum_out);
+  if (vpt <= 4) return launch<TPR, 4>(x, w, out, rows, nvec, xs, os, eps, stream, res, sum_out);
+  return launch<TPR, 8>(x, w, out, rows, nvec, xs, os, eps, stream, res, sum_out);
+}
+
+int rms_norm_dispatch(const void* x, const void* weight, void* out, int64_t rows, int64_t embed, int64_t x_row_stride,
+                      int64_t out_row_stride, float eps, cudaStream_t stream, const void* res, void* sum_out,
+                      const char* what) {
+  if (rows < 0 || embed <= 0) return fail(L3CI_ERR_INVALID, "%s: rows=%lld embed=%lld", what, (long long)rows, (long long)embed);
+  if (rows == 0) return L3CI_OK;
+  if (!x || !weight || !out) return fail(L3CI_ERR_INVALID, "%s: null pointer", what);
+  if (embed % kVecElems != 0 || embed > 65536)
+    return fail(L3CI_ERR_UNSUPPORTED, "%s: embed=%lld must be a multiple of 8 and <= 65536", what, (long long)embed);
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || x_row_stride % kVecElems ||
+      out_row_stride % kVecElems || (res && !aligned16(res)) || (sum_out && !aligned16(sum_out)))
+    return fail(L3CI_ERR_ALIGNMENT, "%s: rows must start on 16 bytes", what);
+  const int nvec = (int)(embed / kVecElems);
+  // Thread group per row: two vectors per thread where the row allows it (measured on B200 at 2048 columns:
+  // 128 threads x 2 vectors beat 32 x 8 by 1 us of 13 at 4096 rows and by 2 us of 8 at 64 rows: the loads of a
+  // row are one or two deep instead of eight), up to eight per thread for the longest rows.
+  int tpr = 32;
+  while (tpr < 1024 && tpr * 2 < nvec) tpr *= 2;
+  const int vpt = (nvec + tpr - 1) / tpr;
+  switch (tpr) {
+    case 32: return launch_vpt<32>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    case 64: return launch_vpt<64>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    case 128: return launch_vpt<128>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    case 256: return launch_vpt<256>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    case 512: return launch_vpt<512>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    default: return launch_vpt<1024>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+  }
+}
+
+// out = bf16( bf16(silu(gate)) * up ): the two roundings of F.silu(gate) * up on bf16 tensors (model.py:134).
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                __nv_bfloat16* __restrict__ out, long long nvec, int row_vecs, long long gate_stride,
+                long long up_stride) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= nvec) return;
+  const long long r = i / row_vecs, c = (i % row_vecs) * kVecElems;
+  const uint4 g = ld_stream16(gate + r * gate_stride + c), u = ld_stream16(up + r * up_stride + c);
+  float a[8], b[8];
+  unpack8(g, a);
+  unpack8(u, b);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = __fdiv_rn(a[j], __fadd_rn(1.0f, expf(-a[j])));
+  const uint4 s = pack8(a);  // first rounding: silu(gate) as a bf16 tensor
+  unpack8(s, a);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = __fmul_rn(a[j], b[j]);
+  st_stream16(out + i * kVecElems, pack8(a));
 }
 
 }  // namespace
@@ -105,28 +183,35 @@ int launch_vpt(int vpt, const void* x, const void* w, void* out, long long rows,
 extern "C" int l3ci_rms_norm(const void* x, const void* weight, void* out, int64_t rows,
                              int64_t embed, int64_t x_row_stride, int64_t out_row_stride,
                              float eps, l3ci_stream_t stream_) {
+  l3ci::clear_error();
+  return l3ci::rms_norm_dispatch(x, weight, out, rows, embed, x_row_stride, out_row_stride, eps,
+                                 reinterpret_cast<cudaStream_t>(stream_), nullptr, nullptr, "rms_norm");
+}
+
+extern "C" int l3ci_add_rms_norm(const void* x, const void* residual, const void* weight, void* sum_out, void* out,
+                                 int64_t rows, int64_t embed, float eps, l3ci_stream_t stream_) {
+  l3ci::clear_error();
+  if (!residual || !sum_out) return l3ci::fail(L3CI_ERR_INVALID, "add_rms_norm: null pointer");
+  return l3ci::rms_norm_dispatch(x, weight, out, rows, embed, embed, embed, eps, reinterpret_cast<cudaStream_t>(stream_),
+                                 residual, sum_out, "add_rms_norm");
+}
+
+extern "C" int l3ci_silu_mul(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                             int64_t gate_row_stride, int64_t up_row_stride, l3ci_stream_t stream_) {
   using namespace l3ci;
   clear_error();
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (rows < 0 || embed <= 0) return fail(L3CI_ERR_INVALID, "rms_norm: rows=%lld embed=%lld", (long long)rows, (long long)embed);
-  if (rows == 0) return L3CI_OK;
-  if (!x || !weight || !out) return fail(L3CI_ERR_INVALID, "rms_norm: null pointer");
-  if (embed % kVecElems != 0 || embed > 65536)
-    return fail(L3CI_ERR_UNSUPPORTED, "rms_norm: embed=%lld must be a multiple of 8 and <= 65536", (long long)embed);
-  if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || x_row_stride % kVecElems ||
-      out_row_stride % kVecElems)
-    return fail(L3CI_ERR_ALIGNMENT, "rms_norm: rows must start on 16 bytes");
-  const int nvec = (int)(embed / kVecElems);
-  // Smallest thread group whose lanes hold the row in <= 8 vectors each.
-  int tpr = 32;
-  while (tpr * 8 < nvec) tpr *= 2;
-  const int vpt = (nvec + tpr - 1) / tpr;
-  switch (tpr) {
-    case 32: return launch_vpt<32>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-    case 64: return launch_vpt<64>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-    case 128: return launch_vpt<128>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-    case 256: return launch_vpt<256>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-    case 512: return launch_vpt<512>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-    default: return launch_vpt<1024>(vpt, x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream);
-  }
+  if (rows < 0 || cols < 0) return fail(L3CI_ERR_INVALID, "silu_mul: negative size");
+  if (rows == 0 || cols == 0) return L3CI_OK;
+  if (!gate || !up || !out) return fail(L3CI_ERR_INVALID, "silu_mul: null pointer");
+  if (cols % kVecElems || cols / kVecElems > 0x7fffffffLL || gate_row_stride % kVecElems || up_row_stride % kVecElems ||
+      !aligned16(gate) || !aligned16(up) || !aligned16(out))
+    return fail(L3CI_ERR_ALIGNMENT, "silu_mul: rows must start on 16 bytes and cols be a multiple of 8");
+  const long long nvec = rows * (cols / kVecElems);
+  const long long ctas = (nvec + 255) / 256;
+  if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "silu_mul: tensor too large");
+  silu_mul_kernel<<<(unsigned)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), nvec,
+      (int)(cols / kVecElems), gate_row_stride, up_row_stride);
+  L3CI_CHECK_LAUNCH("silu_mul_kernel");
+  return L3CI_OK;
 }

@@ -220,6 +220,43 @@ Tensor rms_norm(Tensor input, Tensor weight, double eps) {
   return out;
 }
 
+// (x + residual) and its RMSNorm in one pass: returns (sum, normed).  model.py:147-148 as one kernel.
+std::tuple<Tensor, Tensor> add_rms_norm(Tensor x, Tensor residual, Tensor weight, double eps) {
+  check_bf16_cuda(x, "x");
+  check_bf16_cuda(residual, "residual");
+  check_bf16_cuda(weight, "weight");
+  TORCH_CHECK(x.sizes() == residual.sizes() && weight.dim() == 1 && weight.size(0) == x.size(-1), "shape mismatch");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor xc = x.contiguous(), rc = residual.contiguous(), w = weight.contiguous();
+  Tensor sum = torch::empty_like(xc), out = torch::empty_like(xc);
+  const int64_t E = xc.size(-1);
+  check_status(l3ci_add_rms_norm(xc.data_ptr(), rc.data_ptr(), w.data_ptr(), sum.data_ptr(), out.data_ptr(),
+                                 E ? xc.numel() / E : 0, E, (float)eps, current_stream()),
+               "add_rms_norm");
+  return {sum, out};
+}
+
+// silu(gate) * up with the roundings of the two bf16 tensor ops it replaces (model.py:134).
+Tensor silu_mul(Tensor gate, Tensor up) {
+  check_bf16_cuda(gate, "gate");
+  check_bf16_cuda(up, "up");
+  TORCH_CHECK(gate.sizes() == up.sizes(), "gate and up must have the same shape");
+  TORCH_CHECK(gate.dim() >= 1, "gate must have at least one dimension");
+  const c10::cuda::CUDAGuard guard(gate.device());
+  // rows of a [..., 2F] GEMM result split in halves stay in place: only the last axis must be contiguous
+  const int64_t cols = gate.size(-1);
+  auto rows2d = [&](const Tensor& t) {
+    Tensor f = t.dim() == 2 ? t : t.reshape({-1, cols});  // a view whenever the leading axes collapse
+    return f.stride(-1) == 1 ? f : f.contiguous();
+  };
+  Tensor g = rows2d(gate), u = rows2d(up);
+  Tensor out = torch::empty(gate.sizes(), gate.options());
+  check_status(l3ci_silu_mul(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.size(0), cols, g.stride(0), u.stride(0),
+                             current_stream()),
+               "silu_mul");
+  return out;
+}
+
 // reference: custom_kernels/custom_kernels.cu:418-442
 Tensor rot_embed(Tensor input, Tensor freq) {
   check_bf16_cuda(input, "input");
@@ -314,6 +351,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out") = py::none(), py::arg("scale") = 0.0, py::arg("max_ctas") = 0);
   m.def("rms_norm", torch::wrap_pybind_function(rms_norm), "rms_norm", py::arg("input"), py::arg("weight"),
         py::arg("eps"));
+  m.def("add_rms_norm", torch::wrap_pybind_function(add_rms_norm), "add_rms_norm", py::arg("x"), py::arg("residual"),
+        py::arg("weight"), py::arg("eps"));
+  m.def("silu_mul", torch::wrap_pybind_function(silu_mul), "silu_mul", py::arg("gate"), py::arg("up"));
   m.def("rot_embed", torch::wrap_pybind_function(rot_embed), "rot_embed", py::arg("input"), py::arg("freq"));
   m.def("rot_embed_kv_cache", torch::wrap_pybind_function(rot_embed_kv_cache), "rot_embed_kv_cache",
         py::arg("qkv"), py::arg("freq"), py::arg("cache_k"), py::arg("cache_v"), py::arg("start_pos"),

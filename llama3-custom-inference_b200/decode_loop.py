@@ -14,7 +14,9 @@ What differs from the reference's loop, all on the caller's side of the kernels:
     host scalar changes from step to step;
   * which lets one decode step be captured in a CUDA graph and replayed: no per-step Python dispatch, no
     per-step mask construction (model.py:211) and no `all(eos_reached)` host sync (model.py:380).
-GEMMs, embedding lookup, SiLU and argmax are plain torch ops (cuBLAS); prefill attention is torch SDPA, as in
+  * the residual add runs inside the RMSNorm that follows it (`add_rms_norm`), `c_fc2` and `c_fc` are one GEMM
+    over the stacked weight, and `silu(gate) * up` is one kernel (`silu_mul`) instead of two elementwise passes.
+GEMMs, embedding lookup and argmax are plain torch ops (cuBLAS); prefill attention is torch SDPA, as in
 the reference (model.py:114-116).
 """
 from __future__ import annotations
@@ -58,12 +60,14 @@ class Llama3Decoder:
         if weights is None:
             weights = init_weights(cfg, seed)
         self.w = {k: v.to(self.device) for k, v in weights.items()}
+        for l in range(cfg.n_layer):   # gate (c_fc2) and up (c_fc) projections as one [2F, E] GEMM operand
+            self.w[f"h{l}.gate_up"] = torch.cat([self.w.pop(f"h{l}.fc2"), self.w.pop(f"h{l}.fc")], dim=0)
         bf16 = dict(dtype=torch.bfloat16, device=self.device)
         self.cache_k = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
         self.cache_v = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
         self.freqs = rope_table.precompute_freqs_cis(D, max_len, cfg.rope_theta, True,
                                                      scale_factor=cfg.rope_scale_factor).to(self.device)
-        assert self.w["h0.attn"].shape == (qkv_rows, E) and self.w["h0.fc"].shape == (F_, E)
+        assert self.w["h0.attn"].shape == (qkv_rows, E) and self.w["h0.gate_up"].shape == (2 * F_, E)
         self._graph = None
 
     # ---- one forward pass over T new tokens per sequence ------------------------------------------------
@@ -73,10 +77,11 @@ class Llama3Decoder:
         cfg, ext, w = self.cfg, self.ext, self.w
         B, T = tokens.shape
         E, D, Hq, Hkv = cfg.n_embd, cfg.head_dim, cfg.n_head, cfg.n_kv_head
+        F_ = cfg.hidden_dim
         x = F.embedding(tokens, w["wte"])                                            # model.py:208
+        h = ext.rms_norm(x, w["h0.ln_1"], cfg.norm_eps)                                # model.py:147, 71
         for l in range(cfg.n_layer):
             p = f"h{l}."
-            h = ext.rms_norm(x, w[p + "ln_1"], cfg.norm_eps)                           # model.py:147, 71
             qkv = F.linear(h, w[p + "attn"])                                           # model.py:95
             q = ext.rot_embed_kv_cache(qkv, self.freqs, self.cache_k[l], self.cache_v[l], 0, Hq, Hkv,
                                        positions=positions)                            # model.py:96-108
@@ -89,11 +94,14 @@ class Llama3Decoder:
                 y = ext.flash_attention_decode(q.transpose(1, 2), self.cache_k[l][:B].transpose(1, 2),
                                                self.cache_v[l][:B].transpose(1, 2), seq_lens=seq_lens)  # model.py:118
             y = y.transpose(1, 2).reshape(B, T, E)                                     # model.py:120
-            x = x + F.linear(y, w[p + "proj"])                                         # model.py:121, 147
-            h = ext.rms_norm(x, w[p + "ln_2"], cfg.norm_eps)                           # model.py:148
-            x = x + F.linear(F.silu(F.linear(h, w[p + "fc2"])) * F.linear(h, w[p + "fc"]), w[p + "mlp_proj"])  # :134
-        x = ext.rms_norm(x[:, -1:, :].contiguous(), w["ln_f"], cfg.norm_eps)           # model.py:217
-        logits = F.linear(x, w["wte"]).float()                                         # model.py:225 (tied head)
+            x, h = ext.add_rms_norm(F.linear(y, w[p + "proj"]), x, w[p + "ln_2"], cfg.norm_eps)  # :121, 147-148
+            gu = F.linear(h, w[p + "gate_up"])                                         # c_fc2 | c_fc, model.py:134
+            m = F.linear(ext.silu_mul(gu[..., :F_], gu[..., F_:]), w[p + "mlp_proj"])
+            nxt = w[f"h{l + 1}.ln_1"] if l + 1 < cfg.n_layer else w["ln_f"]
+            x, h = ext.add_rms_norm(m, x, nxt, cfg.norm_eps)                           # model.py:148, next 147 / 217
+        logits = F.linear(h[:, -1:, :], w["wte"])                                      # model.py:225 (tied head)
+        # the reference widens the logits to fp32 first (model.py:226); the widening is monotonic, so the argmax
+        # of the bf16 values is the same index
         return logits[:, -1].argmax(dim=-1)                                            # model.py:371
 
     # ---- greedy generation --------------------------------------------------------------------------------

@@ -14,3 +14,18 @@ def rms_norm_reference(x: torch.Tensor, weight: torch.Tensor, eps: float) -> tor
     wf = weight.detach().cpu().float()
     inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
     return ((xf * inv) * wf).to(torch.bfloat16)
+
+
+def add_rms_norm_reference(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """(s, rmsnorm(s)) with s = x + residual as a bf16 tensor add gives it: Block.forward's residual add
+    followed by the next norm (model.py:147-148), the two steps kept separate as the reference runs them."""
+    s = (x.detach().cpu().float() + residual.detach().cpu().float()).to(torch.bfloat16)
+    return s, rms_norm_reference(s, weight, eps)
+
+
+def silu_mul_reference(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """F.silu(gate) * up on bf16 tensors (MLP.forward, model.py:134): silu in fp32 rounded to bf16, then
+    the product rounded to bf16."""
+    g = gate.detach().cpu().float()
+    s = (g / (1.0 + torch.exp(-g))).to(torch.bfloat16)
+    return (s.float() * up.detach().cpu().float()).to(torch.bfloat16)

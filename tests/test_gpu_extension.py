@@ -112,3 +112,23 @@ def test_errors_are_runtime_errors(ext, device):
         ext.flash_attention_decode(q, k, k)
     with pytest.raises(RuntimeError, match="bfloat16"):
         ext.rms_norm(torch.zeros(1, 1, 8, device=device), torch.zeros(8, device=device), 1e-5)
+
+
+def test_fused_elementwise_call_forms(ext, device):
+    """add_rms_norm and silu_mul on [B, T, *] tensors, silu_mul on the two halves of one GEMM result."""
+    from oracle.rms_norm import add_rms_norm_reference, silu_mul_reference
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 3, 256, generator=g).bfloat16().to(device)
+    r = torch.randn(4, 3, 256, generator=g).bfloat16().to(device)
+    w = torch.randn(256, generator=g).bfloat16().to(device)
+    s, h = ext.add_rms_norm(x, r, w, 1e-5)
+    s_want, h_want = add_rms_norm_reference(x, r, w, 1e-5)
+    assert s.shape == x.shape and torch.equal(s.cpu(), s_want)
+    assert compare.max_bf16_ulp(h, h_want) <= 1
+    gu = torch.randn(4, 3, 512, generator=g).bfloat16().to(device)
+    got = ext.silu_mul(gu[..., :256], gu[..., 256:])
+    assert got.shape == (4, 3, 256) and got.is_contiguous()
+    assert compare.max_bf16_ulp(got, silu_mul_reference(gu[..., :256], gu[..., 256:])) <= 1
+    with pytest.raises(RuntimeError):
+        ext.silu_mul(gu[..., :256], gu[..., 250:])

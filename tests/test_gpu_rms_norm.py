@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from oracle import compare, inputs
-from oracle.rms_norm import rms_norm_reference
+from oracle.rms_norm import add_rms_norm_reference, rms_norm_reference, silu_mul_reference
 
 pytestmark = pytest.mark.gpu
 MAX_ULP = 1  # stated tolerance for RMSNorm
@@ -63,3 +63,45 @@ def test_errors(capi, device):
     x = torch.zeros(2, 16, dtype=torch.bfloat16, device=device)
     assert lib.l3ci_rms_norm(x.data_ptr() + 2, x.data_ptr(), x.data_ptr(), 1, 8, 8, 8, 1e-5, None) == capi.ERR_ALIGNMENT
     assert lib.l3ci_rms_norm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 12, 12, 12, 1e-5, None) == capi.ERR_UNSUPPORTED
+
+
+# ---- residual add fused into the norm, and the SwiGLU gate (the elementwise passes either side of the norm) ----
+
+@pytest.mark.parametrize("rows,embed", [(64, 2048), (1, 2048), (7, 8), (33, 1000), (9, 4096), (3, 16384), (130, 2056)])
+def test_add_rms_norm(capi, device, rows, embed):
+    g = torch.Generator().manual_seed(rows * 17 + embed)
+    x = (torch.randn(rows, embed, generator=g) * 2).bfloat16().to(device)
+    r = (torch.randn(rows, embed, generator=g) * 3).bfloat16().to(device)
+    w = (1 + 0.1 * torch.randn(embed, generator=g)).bfloat16().to(device)
+    s, out = capi.add_rms_norm(x, r, w, 1e-5)
+    torch.cuda.synchronize()
+    s_want, out_want = add_rms_norm_reference(x, r, w, 1e-5)
+    assert torch.equal(s.cpu().view(torch.int16), s_want.view(torch.int16))  # the sum is bit-exact
+    assert compare.max_bf16_ulp(out, out_want) <= MAX_ULP
+    # and the norm of the fused call is the plain kernel applied to that sum
+    assert torch.equal(out, capi.rms_norm(s, w, 1e-5))
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 8192), (1, 8), (5, 1000), (3, 65536)])
+def test_silu_mul(capi, device, rows, cols):
+    g = torch.Generator().manual_seed(rows + cols)
+    gu = (torch.randn(rows, 2 * cols, generator=g) * 4).bfloat16().to(device)
+    gu[0, :8] = torch.tensor([0.0, -0.0, 30.0, -30.0, 100.0, -100.0, 1e-3, -1e-3], dtype=torch.bfloat16)
+    gate, up = gu[:, :cols], gu[:, cols:]          # halves of one GEMM result: strided rows
+    got = capi.silu_mul(gate, up)
+    torch.cuda.synchronize()
+    want = silu_mul_reference(gate, up)
+    assert torch.isfinite(got.float()).all()
+    assert compare.max_bf16_ulp(got, want) <= MAX_ULP
+    assert float((compare.bf16_ulp_distance(got.cpu(), want) > 0).float().mean()) < 0.01
+    assert torch.equal(got, capi.silu_mul(gate.contiguous(), up.contiguous()))
+
+
+def test_fused_errors(capi, device):
+    lib = capi.load()
+    x = torch.zeros(2, 16, dtype=torch.bfloat16, device=device)
+    p = x.data_ptr()
+    assert lib.l3ci_add_rms_norm(p, None, p, p, p, 1, 8, 1e-5, None) == capi.ERR_INVALID
+    assert lib.l3ci_add_rms_norm(p, p + 2, p, p, p, 1, 8, 1e-5, None) == capi.ERR_ALIGNMENT
+    assert lib.l3ci_silu_mul(p, p, p, 1, 12, 12, 12, None) == capi.ERR_ALIGNMENT
+    assert lib.l3ci_silu_mul(p, p, p, 0, 8, 8, 8, None) == capi.OK
