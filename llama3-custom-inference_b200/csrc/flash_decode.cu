@@ -43,8 +43,9 @@
 namespace l3ci {
 namespace {
 
-constexpr int kStages = 3;            // tiles in flight per warp
-constexpr int kStageBytes = 8192;     // K tile + V tile of one stage
+constexpr int kStages = 3;            // columns (one tile per head of the group) resident per CTA
+constexpr int kStageBytes = 8192;     // K tile + V tile of one head in a stage
+constexpr bool kScoresAhead = true;   // compute a tile's scores while the previous tile is still in its softmax
 constexpr int kHeaderBytes = 256;     // scratch header: status word
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bound of one mbarrier wait
 
@@ -68,11 +69,11 @@ struct FdCfg {
 __device__ unsigned long long* g_fd_trace = nullptr;
 #define FD_TRACE(slot)                                                                       \
   do {                                                                                       \
-    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 16 + (slot)] = global_ns(); \
+    if (g_fd_trace && lane == 0 && warp < 8) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 32 + (slot)] = global_ns(); \
   } while (0)
 #define FD_TRACE_VAL(slot, v)                                                                 \
   do {                                                                                       \
-    if (g_fd_trace && lane == 0) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 16 + (slot)] = (v); \
+    if (g_fd_trace && lane == 0 && warp < 8) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 32 + (slot)] = (v); \
   } while (0)
 #define FD_TRACE_ONLY(...) __VA_ARGS__
 #else
@@ -93,7 +94,7 @@ struct FdParams {
   int B, Hq, Hkv, R, n_seq, n_groups;
   long long q_sb, q_sh, o_sb, o_sh;
   float scale_log2e;
-  int rec_floats;       // floats per record: R * (D + 2), padded to a multiple of 32
+  int rec_floats;       // floats per record: R * D / 4 chunks of 8
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -107,6 +108,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -176,6 +180,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Transposes an 8x8 matrix of 16-bit values held one row per 4 lanes, two values per lane.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -232,8 +242,8 @@ struct SliceJob {
                                         int warp, int lane) {
     b = b_; head = head_; n = n_; R = p.R;
     const int Q = R * C4;
-    q0 = (int)(((long long)me * Q) / n);
-    q1 = (int)(((long long)(me + 1) * Q) / n);
+    q0 = (int)((unsigned)me * (unsigned)Q / (unsigned)n);  // me < n <= CTAs of a launch, Q <= 512: fits 32 bits
+    q1 = (int)((unsigned)(me + 1) * (unsigned)Q / (unsigned)n);
     lg = 5;
     while (lg > 0 && ((q1 - q0) << lg) > kWarp) --lg;
     lpc = 1 << lg;
@@ -248,16 +258,16 @@ struct SliceJob {
 
   __device__ __forceinline__ void load(Loads& ld, int base, int k0, int lane) const {
     const int q = q0 + base + (lane >> lg);
-    const int r = q / C4, d = (q & (C4 - 1)) * 4;
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       const int rec = k0 + sub + j * lpc;
       ld.act[j] = q < q1 && rec < n;
       if (ld.act[j]) {
-        const float* rc = rec == 0 ? rec0 : rec1 + (rec - 1) * rec_stride;
-        ld.m[j] = __ldcg(rc + R * D + r);
-        ld.l[j] = __ldcg(rc + R * D + R + r);
-        ld.v[j] = __ldcg(reinterpret_cast<const float4*>(rc + r * D + d));
+        const float* ch = (rec == 0 ? rec0 : rec1 + (rec - 1) * rec_stride) + q * 8;
+        ld.v[j] = __ldcg(reinterpret_cast<const float4*>(ch));
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(ch + 4));
+        ld.m[j] = ml.x;
+        ld.l[j] = ml.y;
       }
     }
   }
@@ -294,6 +304,7 @@ struct SliceJob {
   }
   // The general form: as many passes over chunks and rounds over records as the job needs.
   __device__ __forceinline__ void run(const FdParams& p, int lane) const {
+    FD_TRACE_ONLY(const int warp = threadIdx.x >> 5; FD_TRACE(7);)
     for (int base = 0; base < q1 - q0; base += per_pass) {
       Chunk4 acc;
       acc.clear();
@@ -302,6 +313,7 @@ struct SliceJob {
         load(ld, base, k0, lane);
         fold(acc, ld);
       }
+      FD_TRACE_ONLY(if (__any_sync(kFullMask, acc.l > 0.f)) FD_TRACE(11);)
       finish(acc, p, base, lane);
     }
   }
@@ -345,6 +357,7 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
   const bool on[2] = {def_n[0] > 1, def_n[1] > 1};
   int* const counter[2] = {p.counters + def_b[0] * p.Hkv + def_head[0], p.counters + def_b[1] * p.Hkv + def_head[1]};
   if (!wait_for_records(p, counter, def_n, on, lane)) return;
+  FD_TRACE(14);
   int left[2] = {0, 0};
   if (lane == 0) {
 #pragma unroll
@@ -369,6 +382,8 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
     if (on[0]) job[0].run(p, lane);
     if (on[1]) job[1].run(p, lane);
   }
+  FD_TRACE(15);
+  FD_TRACE_ONLY(if (on[0] && !on[1]) { FD_TRACE(16); job[0].run(p, lane); FD_TRACE(17); })
   if (lane == 0) {
 #pragma unroll
     for (int w = 0; w < 2; ++w)
@@ -377,38 +392,48 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel.  blockDim.x = 32 * HG; dynamic shared memory (1024-byte aligned by hand):
-//   [HG][kStages][kStageBytes] tiles | [HG][kStages] mbarriers | prefix[B+1] | len[B]
+// The kernel.  blockDim.x = 32 * (HG + 1): HG consumer warps, one per KV head of the group, and one producer
+// warp.  Dynamic shared memory (1024-byte aligned by hand):
+//   [kStages] stages | full[kStages], empty[kStages] mbarriers | prefix[B+1] | len[B]
+// A stage holds one column: K then V, each as kHalves boxes of [HG heads][kTile tokens][128 bytes], so the
+// tile of head w starts w * kBoxBytes into a box and all heads of a token arrive by the same bulk copy (the
+// issue of a bulk tensor copy keeps a warp busy for some hundred cycles; four copies per column and CTA, issued
+// by a warp that does nothing else, keep that off the warps that do the arithmetic).  full[s] completes when
+// the stage's bytes have landed, empty[s] when all HG consumers have released it.
 // ---------------------------------------------------------------------------------------------
 template <int D, bool RHI>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(288, 1)
 flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                     const FdParams p) {
   using C = FdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  const int HG = blockDim.x >> 5;
+  const int HG = (blockDim.x >> 5) - 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   FD_TRACE(0);
   const int gid = lane >> 2;  // MMA row within the 8-row half
   const int tig = lane & 3;   // MMA column pair
 
-  uint8_t* stages = smem + warp * (kStages * kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + HG * (kStages * kStageBytes)) + warp * kStages;
-  int* s_pref = reinterpret_cast<int*>(smem + HG * (kStages * kStageBytes) + HG * kStages * 8);
+  const uint32_t cta_stage_bytes = (uint32_t)HG * kStageBytes;
+  uint8_t* stages = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * cta_stage_bytes);  // full[kStages], empty[kStages]
+  int* s_pref = reinterpret_cast<int*>(bars + 2 * kStages);
   int* s_len = s_pref + (p.B + 1);
 
-  if (lane == 0) {
+  if (threadIdx.x == 0) {
 #pragma unroll
-    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&bars[s]), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[kStages + s]), HG);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kmap)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&vmap)) : "memory");
   }
-  __syncwarp();
+  __syncthreads();
 
   // ---- column prefix over sequences (only when lengths differ) ----
   FdWalker wk;
@@ -497,50 +522,67 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     c1 = fd_range_begin(cta + 1, total, G);
   }
 
-  const uint64_t policy = l2_evict_first_policy();
   const uint32_t stage0 = smem_u32(stages);
-  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + kStages * 8;
+  const uint32_t half_stride = (uint32_t)HG * C::kBoxBytes;  // between the 64-column halves of a K or V tile
 
-  // ---- producer side: lane 0 issues the loads of one column ----
-  auto issue = [&](const FdCursor& cu, int stage) {
-    const uint32_t bar = bar0 + stage * 8;
-    const uint32_t dst = stage0 + stage * kStageBytes;
-    const int tok = cu.j * C::kTile;
-    const int head = cu.g * HG + warp;
-    mbar_expect_tx(bar, kStageBytes);
+  if (warp == HG) {
+    // ---- producer warp: one column per step into the next free stage ----
+    const uint64_t policy = l2_evict_first_policy();
+    FdCursor prod = wk.seek(c0);
+    int k = 0;
+    bool alive = true;
+    for (; prod.col < c1; wk.advance(prod), ++k) {
+      const int stage = k % kStages;
+      if (k >= kStages && !mbar_wait_bounded(empty0 + stage * 8, ((k / kStages) - 1) & 1)) { alive = false; break; }
+      if (lane == 0) {
+        const uint32_t bar = full0 + stage * 8;
+        const uint32_t dst = stage0 + stage * cta_stage_bytes;
+        const int tok = prod.j * C::kTile;
+        const int head = prod.g * HG;
+        mbar_expect_tx(bar, cta_stage_bytes);
 #pragma unroll
-    for (int h = 0; h < C::kHalves; ++h) tma_load_4d(dst + h * C::kBoxBytes, &kmap, bar, h * 64, tok, head, cu.b, policy);
+        for (int h = 0; h < C::kHalves; ++h) tma_load_4d(dst + h * half_stride, &kmap, bar, h * 64, tok, head, prod.b, policy);
 #pragma unroll
-    for (int h = 0; h < C::kHalves; ++h)
-      tma_load_4d(dst + C::kKBytes + h * C::kBoxBytes, &vmap, bar, h * 64, tok, head, cu.b, policy);
-  };
-
-  FD_TRACE(1);
-  FdCursor prod = wk.seek(c0);
-  FdCursor cons = prod;
-  int issued = 0;
-#pragma unroll
-  for (int s = 0; s < kStages; ++s) {
-    if (prod.col < c1) {
-      if (lane == 0) issue(prod, s);
-      wk.advance(prod);
-      ++issued;
+        for (int h = 0; h < C::kHalves; ++h)
+          tma_load_4d(dst + HG * C::kKBytes + h * half_stride, &vmap, bar, h * 64, tok, head, prod.b, policy);
+      }
+      __syncwarp();
     }
+    // Stay until the consumers have released the last columns: the shared memory of a CTA must not go away
+    // under a copy in flight.  A consumer that gave up never releases; then these waits run out too.
+    for (int j = max(k - kStages, 0); alive && j < k; ++j)
+      alive = mbar_wait_bounded(empty0 + (j % kStages) * 8, (j / kStages) & 1);
+    if (!alive && lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+    return;
   }
 
+  FD_TRACE(1);
+  FdCursor cons = wk.seek(c0);
+
   // ---- lane constants of the ldmatrix addresses ----
+  // Scores are computed transposed, S^T = K Q^T, and so is the output, O^T = V^T P^T: the 16 rows of a
+  // tensor-core tile are tokens (or output columns) and its 8 columns are the query heads that share this KV
+  // head.  With up to 8 query heads per KV head no row of a tile is padding, which halves the tensor-core
+  // instructions and the accumulator registers against tiles whose 16 rows are query heads.
   const int mat = lane >> 3, r8 = lane & 7;
-  // K (non-transposed): matrices (tok 0-7, chunk c), (tok 0-7, c+1), (tok 8-15, c), (tok 8-15, c+1)
-  const uint32_t k_row_off = (r8 + 8 * (mat >> 1)) * 128;
-  const uint32_t k_x = (mat & 1) ^ r8;
-  // V (transposed): matrices (tok 0-7, chunk c), (tok 8-15, c), (tok 0-7, c+1), (tok 8-15, c+1)
-  const uint32_t v_row_off = (r8 + 8 * (mat & 1)) * 128;
-  const uint32_t v_x = (mat >> 1) ^ r8;
+  // K as A operand: matrices (tok 0-7, chunk c), (tok 8-15, c), (tok 0-7, c+1), (tok 8-15, c+1)
+  const uint32_t k_row_off = (r8 + 8 * (mat & 1)) * 128;
+  const uint32_t k_x = (mat >> 1) ^ r8;
+  // V, transposed, as A operand: matrices (tok 0-7, chunk c), (tok 0-7, c+1), (tok 8-15, c), (tok 8-15, c+1)
+  const uint32_t v_row_off = (r8 + 8 * (mat >> 1)) * 128;
+  const uint32_t v_x = (mat & 1) ^ r8;
 
   // ---- per-segment state ----
-  uint32_t qa[C::KS][RHI ? 4 : 2];
-  float o[C::NT_O][4];
-  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  constexpr int NB = RHI ? 2 : 1;    // blocks of 8 query rows
+  constexpr int MB = C::kTile / 16;  // blocks of 16 tokens in a tile
+  constexpr int MT = D / 16;         // blocks of 16 output columns
+  // This thread's query rows are nb * 8 + 2 * tig + j (j = 0, 1); its tokens / output columns are gid and gid + 8
+  // of a block of 16.
+  uint32_t qb[C::KS][NB][2];
+  float o[NB][MT][4];
+  float m_run[NB][2], l_run[NB][2];
   bool seg_start = true;
   int k_iter = 0;
   const int R = p.R;
@@ -548,71 +590,101 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   int def_b[2] = {0, 0}, def_head[2] = {0, 0}, def_first[2] = {0, 0}, def_n[2] = {0, 0};  // shared units to merge at the end
 
   FD_TRACE_ONLY(long long trace_wait = 0, trace_c0 = 0, tr_qk = 0, tr_sm = 0, tr_pv = 0, tr_t = 0;)
-  // S = Q K^T for the kTile tokens of the stage at kb.  The k-steps are dealt to kChains accumulator sets that
+  // S^T = K Q^T for the kTile tokens of the tile at kb.  The k-steps are dealt to kChains accumulator sets that
   // are added at the end, so that no tensor-core instruction waits on more than one predecessor.
-  auto qk_scores = [&](uint32_t kb, float (&sc)[C::NT_S][4]) {
+  auto qk_scores = [&](uint32_t kb, float (&sc)[NB][MB][4]) {
     constexpr int kChains = C::KS / 2;
-    float part[kChains][C::NT_S][4];
+    float part[kChains][NB][MB][4];
 #pragma unroll
     for (int c = 0; c < kChains; ++c)
 #pragma unroll
-      for (int nt = 0; nt < C::NT_S; ++nt) part[c][nt][0] = part[c][nt][1] = part[c][nt][2] = part[c][nt][3] = 0.f;
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) part[c][nb][mb][0] = part[c][nb][mb][1] = part[c][nb][mb][2] = part[c][nb][mb][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < C::KS; ++ks) {
 #pragma unroll
-      for (int ntp = 0; ntp < C::NT_S / 2; ++ntp) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t addr = kb + (ks >> 2) * C::kBoxBytes + ntp * 2048 + k_row_off +
-                              (((2u * (ks & 3)) ^ k_x) << 4);
-        ldsm_x4(addr, b0, b1, b2, b3);
-        if constexpr (RHI) {
-          mma_bf16(part[ks % kChains][2 * ntp], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b0, b1);
-          mma_bf16(part[ks % kChains][2 * ntp + 1], qa[ks][0], qa[ks][2], qa[ks][1], qa[ks][3], b2, b3);
-        } else {
-          mma_bf16(part[ks % kChains][2 * ntp], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-          mma_bf16(part[ks % kChains][2 * ntp + 1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
-        }
+      for (int mb = 0; mb < MB; ++mb) {
+        uint32_t a0, a1, a2, a3;
+        const uint32_t addr = kb + (ks >> 2) * half_stride + mb * 2048 + k_row_off + (((2u * (ks & 3)) ^ k_x) << 4);
+        ldsm_x4(addr, a0, a1, a2, a3);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_bf16(part[ks % kChains][nb][mb], a0, a1, a2, a3, qb[ks][nb][0], qb[ks][nb][1]);
       }
     }
 #pragma unroll
-    for (int nt = 0; nt < C::NT_S; ++nt)
+    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float a = part[0][nt][e];
+      for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
-        for (int c = 1; c < kChains; ++c) a += part[c][nt][e];
-        sc[nt][e] = a;
+        for (int e = 0; e < 4; ++e) {
+          float a = part[0][nb][mb][e];
+#pragma unroll
+          for (int c = 1; c < kChains; ++c) a += part[c][nb][mb][e];
+          sc[nb][mb][e] = a;
+        }
+  };
+  // Reductions over the 8 lanes that hold the same query rows (same tig).
+  auto rows_max = [&](float v) {
+    v = fmaxf(v, __shfl_xor_sync(kFullMask, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(kFullMask, v, 8));
+    return fmaxf(v, __shfl_xor_sync(kFullMask, v, 16));
+  };
+  auto rows_sum = [&](float v) {
+    v += __shfl_xor_sync(kFullMask, v, 4);
+    v += __shfl_xor_sync(kFullMask, v, 8);
+    return v + __shfl_xor_sync(kFullMask, v, 16);
+  };
+  // Hands every pair of adjacent output columns of every query row of this thread to emit(nb, j, row, d, v0, v1)
+  // (d even, v0/v1 the unnormalised outputs of columns d, d + 1).  A thread holds columns gid and gid + 8 of a
+  // block; neighbours in gid swap one value each so that both end up with an aligned pair.
+  auto for_each_pair = [&](auto&& emit) {
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int row = nb * 8 + 2 * tig + j;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const float x = o[nb][mt][j], y = o[nb][mt][2 + j];
+          const bool odd = gid & 1;
+          const float got = __shfl_xor_sync(kFullMask, odd ? x : y, 4);
+          if (row < R) emit(nb, j, row, 16 * mt + (odd ? gid + 7 : gid), odd ? got : x, odd ? y : got);
+        }
       }
   };
-  float s[C::NT_S][4];
+  float s[NB][MB][4];
   bool have_s = false;
   while (cons.col < c1) {
     const int head = cons.g * HG + warp;
     if (seg_start) {
-      const __nv_bfloat16* qb = p.q + (long long)cons.b * p.q_sb + (long long)(head * R) * p.q_sh;
+      const __nv_bfloat16* qp = p.q + (long long)cons.b * p.q_sb + (long long)(head * R) * p.q_sh;
 #pragma unroll
       for (int ks = 0; ks < C::KS; ++ks) {
         const int col = ks * 16 + 2 * tig;
-        qa[ks][0] = gid < R ? ld_global_u32(qb + gid * p.q_sh + col) : 0u;
-        qa[ks][1] = gid < R ? ld_global_u32(qb + gid * p.q_sh + col + 8) : 0u;
-        if constexpr (RHI) {
-          qa[ks][2] = gid + 8 < R ? ld_global_u32(qb + (gid + 8) * p.q_sh + col) : 0u;
-          qa[ks][3] = gid + 8 < R ? ld_global_u32(qb + (gid + 8) * p.q_sh + col + 8) : 0u;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const int row = nb * 8 + gid;
+          qb[ks][nb][0] = row < R ? ld_global_u32(qp + row * p.q_sh + col) : 0u;
+          qb[ks][nb][1] = row < R ? ld_global_u32(qp + row * p.q_sh + col + 8) : 0u;
         }
       }
 #pragma unroll
-      for (int nt = 0; nt < C::NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-      m_lo = m_hi = -INFINITY;
-      l_lo = l_hi = 0.f;
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) o[nb][mt][0] = o[nb][mt][1] = o[nb][mt][2] = o[nb][mt][3] = 0.f;
+        m_run[nb][0] = m_run[nb][1] = -INFINITY;
+        l_run[nb][0] = l_run[nb][1] = 0.f;
+      }
       seg_start = false;
     }
 
     const int stage = k_iter % kStages;
-    const uint32_t kb = stage0 + stage * kStageBytes;
-    const uint32_t vb = kb + C::kKBytes;
+    const uint32_t kb = stage0 + stage * cta_stage_bytes + warp * C::kBoxBytes;
+    const uint32_t vb = kb + HG * C::kKBytes;
     if (!have_s) {
       FD_TRACE_ONLY(const long long tw0 = clock64();)
-      if (!mbar_wait_bounded(bar0 + stage * 8, (k_iter / kStages) & 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(full0 + stage * 8, (k_iter / kStages) & 1)) { ok = false; break; }
       FD_TRACE_ONLY(trace_wait += clock64() - tw0; if (k_iter == 0) trace_c0 = clock64();)
       if (k_iter == 0) FD_TRACE(2);
       qk_scores(kb, s);
@@ -621,14 +693,15 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     // chain of tensor-core instructions has nothing to do with the softmax and the P.V of the current tile, so
     // the two overlap in the instruction stream.
     const bool more = !fd_unit_ends(cons, c1);
-    float s_next[C::NT_S][4];
-    if (more) {
+    const bool ahead = kScoresAhead && more;
+    float s_next[NB][MB][4];
+    if (ahead) {
       const int st2 = (k_iter + 1) % kStages;
       FD_TRACE_ONLY(const long long tw0 = clock64();)
-      if (!mbar_wait_bounded(bar0 + st2 * 8, ((k_iter + 1) / kStages) & 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(full0 + st2 * 8, ((k_iter + 1) / kStages) & 1)) { ok = false; break; }
       FD_TRACE_ONLY(trace_wait += clock64() - tw0;)
       FD_TRACE_ONLY(tr_t = clock64();)
-      qk_scores(stage0 + st2 * kStageBytes, s_next);
+      qk_scores(stage0 + st2 * cta_stage_bytes + warp * C::kBoxBytes, s_next);
       FD_TRACE_ONLY(tr_qk += clock64() - tr_t;)
     }
     FD_TRACE_ONLY(tr_t = clock64();)
@@ -637,100 +710,98 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     const int tok0 = cons.j * C::kTile;
     if (tok0 + C::kTile > cons.len) {
 #pragma unroll
-      for (int nt = 0; nt < C::NT_S; ++nt) {
-        const int t = tok0 + nt * 8 + 2 * tig;
-        if (t >= cons.len) s[nt][0] = s[nt][2] = -INFINITY;
-        if (t + 1 >= cons.len) s[nt][1] = s[nt][3] = -INFINITY;
-      }
-    }
-    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-    for (int nt = 0; nt < C::NT_S; ++nt) {
-      mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
-      if constexpr (RHI) mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
-    }
-    mx_lo = group_max<4>(mx_lo) * p.scale_log2e;
-    const float mn_lo = fmaxf(m_lo, mx_lo);
-    const float mu_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
-    const float al_lo = fast_exp2(m_lo - mu_lo);
-    m_lo = mn_lo;
-    float mu_hi = 0.f, al_hi = 1.f;
-    if constexpr (RHI) {
-      mx_hi = group_max<4>(mx_hi) * p.scale_log2e;
-      const float mn_hi = fmaxf(m_hi, mx_hi);
-      mu_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      al_hi = fast_exp2(m_hi - mu_hi);
-      m_hi = mn_hi;
-    }
-    float ps_lo = 0.f, ps_hi = 0.f;
-    uint32_t pa[C::KS_PV][4];
-#pragma unroll
-    for (int nt = 0; nt < C::NT_S; ++nt) {
-      const float p0 = fast_exp2(fmaf(s[nt][0], p.scale_log2e, -mu_lo));
-      const float p1 = fast_exp2(fmaf(s[nt][1], p.scale_log2e, -mu_lo));
-      ps_lo += p0 + p1;
-      pa[nt >> 1][(nt & 1) * 2] = pack_bf16x2(p0, p1);
-      if constexpr (RHI) {
-        const float p2 = fast_exp2(fmaf(s[nt][2], p.scale_log2e, -mu_hi));
-        const float p3 = fast_exp2(fmaf(s[nt][3], p.scale_log2e, -mu_hi));
-        ps_hi += p2 + p3;
-        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(p2, p3);
-      } else {
-        pa[nt >> 1][(nt & 1) * 2 + 1] = 0u;
-      }
-    }
-    l_lo = fmaf(l_lo, al_lo, ps_lo);
-    if constexpr (RHI) l_hi = fmaf(l_hi, al_hi, ps_hi);
-    // Rescale the accumulator only when some row's maximum moved (warp-uniform test).
-    if (__any_sync(kFullMask, al_lo != 1.f || al_hi != 1.f)) {
-#pragma unroll
-      for (int nt = 0; nt < C::NT_O; ++nt) {
-        o[nt][0] *= al_lo;
-        o[nt][1] *= al_lo;
-        if constexpr (RHI) {
-          o[nt][2] *= al_hi;
-          o[nt][3] *= al_hi;
+        for (int mb = 0; mb < MB; ++mb) {
+          const int t = tok0 + mb * 16 + gid;
+          if (t >= cons.len) s[nb][mb][0] = s[nb][mb][1] = -INFINITY;
+          if (t + 8 >= cons.len) s[nb][mb][2] = s[nb][mb][3] = -INFINITY;
         }
+    }
+    uint32_t pb[NB][MB][2];  // P^T as B operand, one 16-token k-step per mb
+    float alpha[NB][2];
+    bool moved = false;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      float mu[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) mx = fmaxf(mx, fmaxf(s[nb][mb][j], s[nb][mb][2 + j]));
+        mx = rows_max(mx) * p.scale_log2e;
+        const float mn = fmaxf(m_run[nb][j], mx);
+        mu[j] = mn == -INFINITY ? 0.f : mn;
+        alpha[nb][j] = fast_exp2(m_run[nb][j] - mu[j]);
+        m_run[nb][j] = mn;
+        moved |= alpha[nb][j] != 1.f;
       }
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) {
+        const float p0 = fast_exp2(fmaf(s[nb][mb][0], p.scale_log2e, -mu[0]));
+        const float p1 = fast_exp2(fmaf(s[nb][mb][1], p.scale_log2e, -mu[1]));
+        const float p2 = fast_exp2(fmaf(s[nb][mb][2], p.scale_log2e, -mu[0]));
+        const float p3 = fast_exp2(fmaf(s[nb][mb][3], p.scale_log2e, -mu[1]));
+        ps0 += p0 + p2;
+        ps1 += p1 + p3;
+        // (token gid | gid + 8, rows 2 tig, 2 tig + 1)  ->  (row gid, tokens 2 tig, 2 tig + 1 | + 8)
+        pb[nb][mb][0] = movmatrix_trans(pack_bf16x2(p0, p1));
+        pb[nb][mb][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+      }
+      l_run[nb][0] = fmaf(l_run[nb][0], alpha[nb][0], ps0);
+      l_run[nb][1] = fmaf(l_run[nb][1], alpha[nb][1], ps1);
+    }
+    // Rescale the accumulator only when some row's maximum moved (warp-uniform test).
+    if (__any_sync(kFullMask, moved)) {
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          o[nb][mt][0] *= alpha[nb][0];
+          o[nb][mt][1] *= alpha[nb][1];
+          o[nb][mt][2] *= alpha[nb][0];
+          o[nb][mt][3] *= alpha[nb][1];
+        }
     }
 
     FD_TRACE_ONLY(tr_sm += clock64() - tr_t; tr_t = clock64();)
-    // ---- O += P V ----
+    // ---- O^T += V^T P^T ----
 #pragma unroll
-    for (int kk = 0; kk < C::KS_PV; ++kk) {
+    for (int kk = 0; kk < MB; ++kk) {
 #pragma unroll
-      for (int np = 0; np < C::NT_O / 2; ++np) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t addr = vb + (np >> 2) * C::kBoxBytes + kk * 2048 + v_row_off +
-                              (((2u * (np & 3)) ^ v_x) << 4);
-        ldsm_x4_trans(addr, b0, b1, b2, b3);
-        mma_bf16(o[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
-        mma_bf16(o[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a0, a1, a2, a3;
+        const uint32_t addr = vb + (mt >> 2) * half_stride + kk * 2048 + v_row_off + (((2u * (mt & 3)) ^ v_x) << 4);
+        ldsm_x4_trans(addr, a0, a1, a2, a3);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_bf16(o[nb][mt], a0, a1, a2, a3, pb[nb][kk][0], pb[nb][kk][1]);
       }
     }
 
     FD_TRACE_ONLY(tr_pv += clock64() - tr_t;)
-    // ---- release the stage and refill it ----
+    // ---- release the stage to the producer ----
     __syncwarp();
-    if (prod.col < c1) {
-      if (lane == 0) issue(prod, stage);
-      wk.advance(prod);
-      ++issued;
-    }
+    if (lane == 0) mbar_arrive(empty0 + stage * 8);
     ++k_iter;
-    have_s = more;
-    if (more) {
+    have_s = ahead;
+    if (ahead) {
 #pragma unroll
-      for (int nt = 0; nt < C::NT_S; ++nt)
+      for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[nt][e] = s_next[nt][e];
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nb][mb][e] = s_next[nb][mb][e];
     }
 
     // ---- end of this (sequence, head) unit inside the CTA's range? ----
-    if (fd_unit_ends(cons, c1)) {
+    if (!more) {
       seg_start = true;
-      l_lo = group_sum<4>(l_lo);
-      if constexpr (RHI) l_hi = group_sum<4>(l_hi);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        l_run[nb][0] = rows_sum(l_run[nb][0]);
+        l_run[nb][1] = rows_sum(l_run[nb][1]);
+      }
       const int u0 = wk.unit_begin(cons);
       const int cfirst = whole ? cta : fd_cta_of(u0, total, G);
       const int clast = whole ? cta : fd_cta_of(u0 + cons.tc - 1, total, G);
@@ -738,64 +809,42 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 
       if (cfirst == clast) {
         // The whole unit was seen by this warp: normalise and write.
-        const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f;
-        const float inv_hi = (RHI && l_hi > 0.f) ? 1.f / l_hi : 0.f;
+        float inv[NB][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) inv[nb][j] = l_run[nb][j] > 0.f ? 1.f / l_run[nb][j] : 0.f;
         if (p.out) {
           __nv_bfloat16* ob = p.out + (long long)cons.b * p.o_sb + hq0 * p.o_sh;
-#pragma unroll
-          for (int nt = 0; nt < C::NT_O; ++nt) {
-            const int d = nt * 8 + 2 * tig;
-            if (gid < R)
-              *reinterpret_cast<uint32_t*>(ob + gid * p.o_sh + d) = pack_bf16x2(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
-            if constexpr (RHI) {
-              if (gid + 8 < R)
-                *reinterpret_cast<uint32_t*>(ob + (gid + 8) * p.o_sh + d) =
-                    pack_bf16x2(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
-            }
-          }
+          for_each_pair([&](int nb, int j, int row, int d, float v0, float v1) {
+            *reinterpret_cast<uint32_t*>(ob + row * p.o_sh + d) = pack_bf16x2(v0 * inv[nb][j], v1 * inv[nb][j]);
+          });
         }
         if (p.o_partial) {
           float* ob = p.o_partial + ((long long)cons.b * p.Hq + hq0) * D;
           float* lb = p.lse + (long long)cons.b * p.Hq + hq0;
+          for_each_pair([&](int nb, int j, int row, int d, float v0, float v1) {
+            *reinterpret_cast<float2*>(ob + row * D + d) = make_float2(v0 * inv[nb][j], v1 * inv[nb][j]);
+          });
+          if (gid == 0) {
 #pragma unroll
-          for (int nt = 0; nt < C::NT_O; ++nt) {
-            const int d = nt * 8 + 2 * tig;
-            if (gid < R) *reinterpret_cast<float2*>(ob + gid * D + d) = make_float2(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
-            if constexpr (RHI) {
-              if (gid + 8 < R)
-                *reinterpret_cast<float2*>(ob + (gid + 8) * D + d) = make_float2(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
-            }
-          }
-          if (tig == 0) {
-            if (gid < R) lb[gid] = l_lo > 0.f ? (m_lo + log2f(l_lo)) * 0.6931471805599453f : -INFINITY;
-            if constexpr (RHI) {
-              if (gid + 8 < R) lb[gid + 8] = l_hi > 0.f ? (m_hi + log2f(l_hi)) * 0.6931471805599453f : -INFINITY;
-            }
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int row = nb * 8 + 2 * tig + j;
+                if (row < R)
+                  lb[row] = l_run[nb][j] > 0.f ? (m_run[nb][j] + log2f(l_run[nb][j])) * 0.6931471805599453f : -INFINITY;
+              }
           }
         }
       } else {
         // Shared with other CTAs: leave an unnormalised record and a count on the unit's arrival counter.
         float* rec = p.records + (long long)fd_record_index(cta, cfirst, HG, warp) * p.rec_floats;
-#pragma unroll
-        for (int nt = 0; nt < C::NT_O; ++nt) {
-          const int d = nt * 8 + 2 * tig;
-          if (gid < R) __stcg(reinterpret_cast<float2*>(rec + gid * D + d), make_float2(o[nt][0], o[nt][1]));
-          if constexpr (RHI) {
-            if (gid + 8 < R) __stcg(reinterpret_cast<float2*>(rec + (gid + 8) * D + d), make_float2(o[nt][2], o[nt][3]));
-          }
-        }
-        if (tig == 0) {
-          if (gid < R) {
-            __stcg(rec + R * D + gid, m_lo);
-            __stcg(rec + R * D + R + gid, l_lo);
-          }
-          if constexpr (RHI) {
-            if (gid + 8 < R) {
-              __stcg(rec + R * D + gid + 8, m_hi);
-              __stcg(rec + R * D + R + gid + 8, l_hi);
-            }
-          }
-        }
+        for_each_pair([&](int nb, int j, int row, int d, float v0, float v1) {
+          float* ch = rec + (row * (D / 4) + (d >> 2)) * 8;  // the chunk of columns d & ~3 .. d | 3
+          __stcg(reinterpret_cast<float2*>(ch + (d & 3)), make_float2(v0, v1));
+          if ((d & 3) == 0) __stcg(reinterpret_cast<float2*>(ch + 4), make_float2(m_run[nb][j], l_run[nb][j]));
+        });
         // The record is announced (and the unit merged) after the whole range has been streamed.  A warp
         // has at most two such units: one that began in an earlier CTA, one that continues in the next.
         const int which = cta == cfirst ? 1 : 0;
@@ -809,11 +858,9 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   }
 
   if (!ok) {
-    // A bulk copy never signalled.  Record it, then give the other copies of this warp a bounded
-    // chance to land before the shared memory goes away.  Shared units are left unmerged.
+    // A column never arrived.  Record it and leave; shared units stay unmerged.  The producer warp notices
+    // the missing release, gives the copies in flight a bounded time to land and ends the CTA.
     if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
-    for (int k = k_iter + 1; k < issued; ++k)
-      (void)mbar_wait_bounded(bar0 + (k % kStages) * 8, (k / kStages) & 1);
     return;
   }
   FD_TRACE(3);
@@ -872,9 +919,9 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   return fn;
 }
 
-// Rank-4 map over a [B, Hkv, n_seq, D] view: dims (d, token, head, batch), box 64 x tile tokens.
+// Rank-4 map over a [B, Hkv, n_seq, D] view: dims (d, token, head, batch), box 64 x tile tokens x HG heads.
 int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, int B, long long st,
-                long long sh, long long sb, int tile) {
+                long long sh, long long sb, int tile, int HG) {
   auto enc = tensor_map_encoder();
   if (!enc) return fail(L3CI_ERR_CUDA, "flash_decode: cuTensorMapEncodeTiled is not available");
   const cuuint64_t row_bytes = (cuuint64_t)D * 2;
@@ -884,7 +931,7 @@ int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, i
   const cuuint64_t sb_b = B > 1 ? (cuuint64_t)sb * 2 : row_bytes;
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)n_seq, (cuuint64_t)Hkv, (cuuint64_t)B};
   cuuint64_t strides[3] = {st_b, sh_b, sb_b};
-  cuuint32_t box[4] = {64u, (cuuint32_t)tile, 1u, 1u};
+  cuuint32_t box[4] = {64u, (cuuint32_t)tile, (cuuint32_t)HG, 1u};
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -894,9 +941,11 @@ int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, i
   return L3CI_OK;
 }
 
-// Floats of one (m, l, o) record: R rows of D outputs, then R maxima and R sums, padded to 128 bytes so
-// that every record (and its 16-byte vector reads) stays aligned.
-int record_floats(int R, int D) { return (R * (D + 2) + 31) & ~31; }
+// Floats of one (m, l, o) record: R * D / 4 chunks of {o[4], m, l, -, -}.  A chunk is the unit a lane of the
+// merge reads, and it is one 32-byte sector: the row's maximum and sum travel with every four outputs, so a
+// merge of n records reads n sectors per chunk instead of 3 n (the sums and maxima of a row are wanted by all
+// the lanes, in several CTAs, that hold chunks of that row).
+int record_floats(int R, int D) { return R * D * 2; }
 
 // Scratch layout: header | arrival counters | records.  The counter area has the same place and size
 // for every call with up to kFixedCounters (sequence, kv head) units, so a scratch buffer that was zeroed
@@ -910,7 +959,7 @@ size_t counters_bytes(int B, int Hkv) {
 }
 
 size_t smem_bytes(int HG, int B, bool ragged) {
-  size_t s = 1024 + (size_t)HG * kStages * kStageBytes + (size_t)HG * kStages * 8;
+  size_t s = 1024 + (size_t)HG * kStages * kStageBytes + 2 * kStages * 8;
   if (ragged) s += (size_t)(2 * B + 1) * sizeof(int);
   return s;
 }
@@ -926,7 +975,7 @@ int launch_fd(const CUtensorMap& kmap, const CUtensorMap& vmap, const FdParams& 
   static std::mutex mu;
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
-  const int block = HG * 32;
+  const int block = (HG + 1) * 32;  // HG consumer warps and the producer warp
   int per_sm = 0;
   {
     std::lock_guard<std::mutex> lock(mu);
@@ -1031,8 +1080,8 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
   if ((long long)smem > max_smem_optin()) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: needs %zu bytes of shared memory", smem);
 
   CUtensorMap kmap, vmap;
-  if (int st = make_kv_map(&kmap, a->k, D, n_seq, Hkv, B, a->k_st, a->k_sh, a->k_sb, tile)) return st;
-  if (int st = make_kv_map(&vmap, a->v, D, n_seq, Hkv, B, a->v_st, a->v_sh, a->v_sb, tile)) return st;
+  if (int st = make_kv_map(&kmap, a->k, D, n_seq, Hkv, B, a->k_st, a->k_sh, a->k_sb, tile, HG)) return st;
+  if (int st = make_kv_map(&vmap, a->v, D, n_seq, Hkv, B, a->v_st, a->v_sh, a->v_sb, tile, HG)) return st;
 
   FdParams p;
   p.q = static_cast<const __nv_bfloat16*>(a->q);
