@@ -176,7 +176,7 @@ L3CI_API int l3ci_flash_decode(const l3ci_flash_decode_args* args);
  * Limits and rules:
  *  - the shape must fit: l3ci_flash_decode_scratch_bytes(B, Hq, Hkv, D) <= L3CI_STATIC_SCRATCH_BYTES
  *    and B * Hkv <= 65536; otherwise L3CI_ERR_SCRATCH with a message that states both sizes
- *    (12 MiB covers head ratios up to 8 at head size 128 on a 148-SM part);
+ *    (12 MiB covers head ratios up to 4 at head size 128, up to 9 at head size 64, on a 148-SM part);
  *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *    that device current); make that first call outside any stream capture;
  *  - all calls on a device share the one array and find in it what the previous call left: the entry

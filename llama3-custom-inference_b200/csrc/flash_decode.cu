@@ -226,13 +226,15 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 // lpc lanes per chunk (a power of two, as many as 32 lanes allow); the lanes of a chunk take every
 // lpc-th record, fold them in registers (up to 8 records' loads in flight per lane) and meet in a
 // shuffle butterfly.  So a unit shared by many CTAs costs each of them a handful of loads, and a
-// unit shared by two or three costs one round of loads.
+// unit shared by two or three costs one round of loads.  Neighbouring lanes hold neighbouring chunks
+// of the same record (the lanes of one chunk are 32 / lpc apart), so a load instruction of the warp
+// reads runs of consecutive 32-byte chunks instead of 32 scattered ones.
 template <int D>
 struct SliceJob {
   static constexpr int C4 = D / 4;  // chunks per output row (a power of two)
   static constexpr int kBatch = 8;  // (chunk, record) loads a lane has in flight
   int b, head, n, R;
-  int q0, q1, lg, lpc, per_pass, sub;
+  int q0, q1, lg, lpc, per_pass, sub, slot;
   const float* rec0;   // record of the first participant (position 1 of its CTA)
   const float* rec1;   // record of the second participant (position 0); later ones follow at rec_stride
   long long rec_stride;
@@ -248,7 +250,8 @@ struct SliceJob {
     while (lg > 0 && ((q1 - q0) << lg) > kWarp) --lg;
     lpc = 1 << lg;
     per_pass = kWarp >> lg;
-    sub = lane & (lpc - 1);
+    slot = lane & (per_pass - 1);  // which of the pass's chunks
+    sub = lane >> (5 - lg);        // which of the chunk's lpc lanes
     rec0 = p.records + (long long)fd_record_index(first_cta, first_cta, HG, warp) * p.rec_floats;
     rec1 = p.records + (long long)fd_record_index(first_cta + 1, first_cta, HG, warp) * p.rec_floats;
     rec_stride = 2LL * HG * p.rec_floats;
@@ -257,7 +260,7 @@ struct SliceJob {
   __device__ __forceinline__ bool single_round() const { return q1 - q0 <= per_pass && n <= kBatch * lpc; }
 
   __device__ __forceinline__ void load(Loads& ld, int base, int k0, int lane) const {
-    const int q = q0 + base + (lane >> lg);
+    const int q = q0 + base + slot;
 #pragma unroll
     for (int j = 0; j < kBatch; ++j) {
       const int rec = k0 + sub + j * lpc;
@@ -278,13 +281,13 @@ struct SliceJob {
   }
   // Butterfly over the lanes of a chunk, then the chunk's four outputs are normalised and written.
   __device__ __forceinline__ void finish(Chunk4& acc, const FdParams& p, int base, int lane) const {
-    for (int off = lpc >> 1; off >= 1; off >>= 1) {
+    for (int off = kWarp >> 1; off >= per_pass; off >>= 1) {
       const float m2 = __shfl_xor_sync(kFullMask, acc.m, off), l2 = __shfl_xor_sync(kFullMask, acc.l, off);
       const float x = __shfl_xor_sync(kFullMask, acc.o[0], off), y = __shfl_xor_sync(kFullMask, acc.o[1], off);
       const float z = __shfl_xor_sync(kFullMask, acc.o[2], off), w = __shfl_xor_sync(kFullMask, acc.o[3], off);
       acc.fold(m2, l2, x, y, z, w);
     }
-    const int q = q0 + base + (lane >> lg);
+    const int q = q0 + base + slot;
     if (q < q1 && sub == 0) {
       const int r = q / C4, d = (q & (C4 - 1)) * 4;
       const long long hq = (long long)head * R + r;
