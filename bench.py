@@ -645,13 +645,13 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
         "config": {"workload": f"C5 random-init Llama-3.2-1B architecture, batch {B}/GPU, prompt {P}, {G} greedy tokens",
                    "global_batch": B * world, "parallelism": "replicas x%d" % world,
                    "l2": "working set per decode step (2.5 GB weights + KV cache) >> 126 MB L2",
-                   "note": "GEMMs are cuBLAS via torch; RMSNorm (+ residual add), SiLU*mul, RoPE + cache write and decode attention are this "
+                   "note": "GEMMs are cuBLAS via torch; RMSNorm (+ residual add), SiLU*mul, RoPE + cache write, decode attention and the greedy step are this "
                            "repository's kernels; the decode step is replayed from a CUDA graph",
                    "reference_published_rtx4060_tokens_per_s": 2041.67},
         "e2e": e2e,
         # per decode step: 33 RMSNorm (32 with the residual add) + 16 SiLU*mul + 16 fused RoPE/cache + 16
-        # flash-decode launches of this library; the prefill pass has no flash-decode
-        "gpu_launches": decode_steps * 81 + steps * 65, "clocks": sampler.summary(),
+        # flash-decode + 1 greedy-step launches of this library; the prefill pass has no flash-decode
+        "gpu_launches": decode_steps * 82 + steps * 65, "clocks": sampler.summary(),
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu

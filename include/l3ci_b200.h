@@ -71,6 +71,18 @@ L3CI_API int l3ci_add_rms_norm(const void* x, const void* residual, const void* 
 L3CI_API int l3ci_silu_mul(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
                            int64_t gate_row_stride, int64_t up_row_stride, l3ci_stream_t stream);
 
+/* Greedy decode step: for every row b of bf16 logits [rows, vocab] (row_stride elements apart),
+ *   tok = argmax (ties: smallest index, as torch.argmax; NaN counts as the maximum);
+ *   out_tokens[b * out_stride + steps[b]] = tok (if steps[b] < out_cols);  steps[b] += 1;
+ *   next_input[b] = tok;  positions[b] += 1;  seq_lens[b] += 1.
+ * Any of out_tokens / steps / next_input / positions / seq_lens may be null (without steps the token goes
+ * to out_tokens[b * out_stride]).  One kernel for what the reference's greedy branch does with an argmax and
+ * several elementwise launches per generated token (model.py:370-381). */
+L3CI_API int l3ci_greedy_step(const void* logits, int64_t rows, int64_t vocab, int64_t row_stride,
+                              int64_t* out_tokens, int64_t out_stride, int64_t out_cols, int64_t* steps,
+                              int64_t* next_input, int32_t* positions, int32_t* seq_lens,
+                              l3ci_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Rotary embedding, interleaved-pair (Meta) convention:
  *   (x', y') = (x*c - y*s, x*s + y*c) for (x, y) = in[.., 2i], in[.., 2i+1] and

@@ -16,7 +16,8 @@ What differs from the reference's loop, all on the caller's side of the kernels:
     per-step mask construction (model.py:211) and no `all(eos_reached)` host sync (model.py:380).
   * the residual add runs inside the RMSNorm that follows it (`add_rms_norm`), `c_fc2` and `c_fc` are one GEMM
     over the stacked weight, and `silu(gate) * up` is one kernel (`silu_mul`) instead of two elementwise passes.
-GEMMs, embedding lookup and argmax are plain torch ops (cuBLAS); prefill attention is torch SDPA, as in
+GEMMs and the embedding lookup are plain torch ops (cuBLAS); the greedy argmax with its token bookkeeping is one
+kernel (`greedy_step`); prefill attention is torch SDPA, as in
 the reference (model.py:114-116).
 """
 from __future__ import annotations
@@ -73,7 +74,7 @@ class Llama3Decoder:
     # ---- one forward pass over T new tokens per sequence ------------------------------------------------
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor) -> torch.Tensor:
         """tokens [B, T] int64; positions int32 [B] = tokens already cached per sequence; seq_lens int32 [B] =
-        positions + T.  Returns the greedy next token per sequence, int64 [B]."""
+        positions + T.  Returns the logits of the last position, bf16 [B, vocab]."""
         cfg, ext, w = self.cfg, self.ext, self.w
         B, T = tokens.shape
         E, D, Hq, Hkv = cfg.n_embd, cfg.head_dim, cfg.n_head, cfg.n_kv_head
@@ -99,10 +100,9 @@ class Llama3Decoder:
             m = F.linear(ext.silu_mul(gu[..., :F_], gu[..., F_:]), w[p + "mlp_proj"])
             nxt = w[f"h{l + 1}.ln_1"] if l + 1 < cfg.n_layer else w["ln_f"]
             x, h = ext.add_rms_norm(m, x, nxt, cfg.norm_eps)                           # model.py:148, next 147 / 217
-        logits = F.linear(h[:, -1:, :], w["wte"])                                      # model.py:225 (tied head)
         # the reference widens the logits to fp32 first (model.py:226); the widening is monotonic, so the argmax
         # of the bf16 values is the same index
-        return logits[:, -1].argmax(dim=-1)                                            # model.py:371
+        return F.linear(h[:, -1, :], w["wte"])                                         # model.py:225 (tied head)
 
     # ---- greedy generation --------------------------------------------------------------------------------
     @torch.inference_mode()
@@ -115,21 +115,18 @@ class Llama3Decoder:
         out = torch.empty(B, max_gen_len, dtype=torch.int64, device=dev)
         positions = torch.zeros(B, dtype=torch.int32, device=dev)
         seq_lens = torch.full((B,), P, dtype=torch.int32, device=dev)
-        tok = self.forward(prompts, positions, seq_lens)                               # prefill
+        tok = self.forward(prompts, positions, seq_lens).argmax(dim=-1)                # prefill; model.py:371
         out[:, 0] = tok
         # static state of the decode step: everything the step reads or writes lives in these tensors
         cur = tok.view(B, 1).clone()
         positions.fill_(P)
         seq_lens.fill_(P + 1)
-        step_idx = torch.ones(1, dtype=torch.int64, device=dev)
+        steps = torch.ones(B, dtype=torch.int64, device=dev)   # next free column of `out`, per sequence
 
         def step():
-            nxt = self.forward(cur, positions, seq_lens)
-            out.scatter_(1, step_idx.view(1, 1).expand(B, 1), nxt.view(B, 1))
-            cur.copy_(nxt.view(B, 1))
-            positions.add_(1)
-            seq_lens.add_(1)
-            step_idx.add_(1)
+            logits = self.forward(cur, positions, seq_lens)
+            # argmax, out[b, steps[b]] = token, cur[b] = token, steps / positions / seq_lens += 1: one kernel
+            self.ext.greedy_step(logits, out, steps, cur.view(B), positions, seq_lens)  # model.py:370-381
 
         n_steps = max_gen_len - 1
         if n_steps <= 0:

@@ -132,3 +132,42 @@ def test_fused_elementwise_call_forms(ext, device):
     assert compare.max_bf16_ulp(got, silu_mul_reference(gu[..., :256], gu[..., 256:])) <= 1
     with pytest.raises(RuntimeError):
         ext.silu_mul(gu[..., :256], gu[..., 250:])
+
+
+def test_greedy_step_matches_torch_argmax_and_keeps_the_books(ext, device):
+    """model.py:370-381 as one call: argmax (first index on ties), token into the output and the next input,
+    per-sequence counters advanced."""
+    g = torch.Generator().manual_seed(11)
+    B, V, G = 7, 128256, 5
+    logits = (torch.randn(B, V, generator=g) * 3).bfloat16()
+    logits[1, 77] = logits[1].max()            # a tie further left than the maximum's first place?
+    logits[2, :] = 0.5                         # all equal: index 0
+    logits[3, V - 1] = 100.0                   # the last element, reached by the scalar tail when V % 8 != 0
+    logits[4, 12345] = float("nan")            # torch.argmax treats NaN as the maximum
+    want = logits.float().argmax(dim=-1)
+    d = logits.to(device)
+    out = torch.full((B, G), -1, dtype=torch.int64, device=device)
+    steps = torch.tensor([0, 1, 2, 3, 4, 5, 0], dtype=torch.int64, device=device)   # row 5: output already full
+    cur = torch.zeros(B, dtype=torch.int64, device=device)
+    pos = torch.arange(B, dtype=torch.int32, device=device)
+    lens = pos + 1
+    ext.greedy_step(d, out, steps, cur, pos, lens)
+    assert torch.equal(cur.cpu(), want)
+    for b in range(B):
+        s0 = [0, 1, 2, 3, 4, 5, 0][b]
+        row = out[b].cpu()
+        if s0 < G:
+            assert int(row[s0]) == int(want[b]) and int((row != -1).sum()) == 1
+        else:
+            assert bool((row == -1).all())
+    assert steps.cpu().tolist() == [1, 2, 3, 4, 5, 6, 1]
+    assert pos.cpu().tolist() == list(range(1, B + 1)) and lens.cpu().tolist() == list(range(2, B + 2))
+    # a strided view (rows of a wider buffer, vocabulary not a multiple of 8, rows not 16-byte aligned)
+    wide = (torch.randn(3, 1003, generator=g)).bfloat16().to(device)
+    view = wide[:, 1:1000]
+    out2 = torch.zeros(3, 1, dtype=torch.int64, device=device)
+    st2 = torch.zeros(3, dtype=torch.int64, device=device)
+    cur2 = torch.zeros(3, dtype=torch.int64, device=device)
+    ext.greedy_step(view, out2, st2, cur2, torch.zeros(3, dtype=torch.int32, device=device),
+                    torch.zeros(3, dtype=torch.int32, device=device))
+    assert torch.equal(cur2.cpu(), view.float().argmax(dim=-1).cpu())
