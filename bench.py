@@ -220,11 +220,12 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=100)
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "rmsnorm", "rope", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "rmsnorm", "rope", "c5", "prefill"])
     ap.add_argument("--gen-len", type=int, default=2048, help="c5: tokens generated per sequence")
     ap.add_argument("--batch", type=int, default=64, help="c5: sequences per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="prefill: head size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-comparator", action="store_true", help="c1-c3: skip the torch SDPA timing on the GPU")
     ap.add_argument("--no-graph", action="store_true", help="c1-c3: launch every step through the extension call "
@@ -255,6 +256,8 @@ def main():
 
     if args.workload == "c5":
         line = bench_end_to_end(args, ext, pkg, dev, rank, world)
+    elif args.workload == "prefill":
+        line = bench_prefill(args, ext, pkg, dev, rank, world)
     elif args.workload in ("rmsnorm", "rope"):
         line = bench_pre_attention(args, ext, pkg, dev, rank, world)
     else:
@@ -531,6 +534,65 @@ def eager_runner(step):
 
     run_steps.prepare = lambda K: None
     return run_steps
+
+
+def bench_prefill(args, ext, pkg, dev, rank, world):
+    """Causal GQA prefill attention at the 1B shape with 2048-token prompts (the long-prompt scenarios of the
+    reference's README tables; there the call is torch's SDPA, model.py:114-116): B=4, Hq=32, Hkv=8, D=64, T=2048.
+    Compute-bound: the figure is TFLOP/s over the causal half, 4 * B * Hq * D * T * (T + 1) / 2 flops."""
+    import torch.nn.functional as F
+
+    B, Hq, Hkv, D, T = 4, 32, 8, args.head_dim, 2048
+    g = torch.Generator(device=dev).manual_seed(42 + rank)
+    n_rot = 4
+    qs = [torch.randn(B, T, Hq, D, generator=g, device=dev).bfloat16().transpose(1, 2) for _ in range(n_rot)]
+    ks = [torch.randn(B, T, Hkv, D, generator=g, device=dev).bfloat16().transpose(1, 2) for _ in range(n_rot)]
+    vs = [torch.randn(B, T, Hkv, D, generator=g, device=dev).bfloat16().transpose(1, 2) for _ in range(n_rot)]
+    flops = 4.0 * B * Hq * D * T * (T + 1) / 2
+    steps = min(args.steps, 400)
+
+    def timed(step):
+        run_steps = eager_runner(step) if args.no_graph else graph_runner(step, n_rot, dev)
+        run_steps.prepare(args.warmup)
+        run_steps.prepare(steps)
+        run_steps(args.warmup)
+        sync_all(world)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        run_steps(steps)
+        end.record()
+        torch.cuda.synchronize()
+        sync_all(world)
+        return start.elapsed_time(end)
+
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    sampler.mark("t0")
+    ms_total = timed(lambda i: ext.prefill_attention(qs[i % n_rot], ks[i % n_rot], vs[i % n_rot]))
+    sampler.mark("t1")
+    sampler.stop()
+    ms_max = max_over_ranks(ms_total, world, dev)
+    sd_ms = timed(lambda i: F.scaled_dot_product_attention(qs[i % n_rot], ks[i % n_rot], vs[i % n_rot], is_causal=True,
+                                                           enable_gqa=True)) / steps
+    got = ext.prefill_attention(qs[0], ks[0], vs[0]).float()
+    ref = F.scaled_dot_product_attention(qs[0], ks[0], vs[0], is_causal=True, enable_gqa=True).float()
+    peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json"))) \
+        if os.path.exists(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    achieved = flops / (ms_total / steps * 1e-3) / 1e12
+    return {
+        "metric": "prefill attention TFLOP/s", "value": flops * world * steps / (ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": steps, "warmup": args.warmup, "ms_per_step": ms_max / steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"causal GQA prefill B={B} Hq={Hq} Hkv={Hkv} D={D} T={T}", "flops_per_step": flops,
+                   "l2": f"{n_rot} rotating q/k/v sets", "max_abs_diff_vs_torch_sdpa_gpu": float((got - ref).abs().max())},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": "measured" if peaks else "fallback", "kernel": "prefill_attention_kernel",
+                     "note": "mma.sync path; its own ceiling is about a quarter of the tcgen05 peak the denominator was measured with"},
+        "comparators": {"torch_sdpa_gpu": {"ms_per_step": sd_ms, "TFLOP/s": flops / (sd_ms * 1e-3) / 1e12,
+                                           "call": "F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)"}},
+        "gpu_launches": steps, "clocks": sampler.summary(),
+    }
 
 
 def bench_pre_attention(args, ext, pkg, dev, rank, world):

@@ -208,6 +208,30 @@ L3CI_API int l3ci_flash_decode_static(const l3ci_flash_decode_args* args);
 L3CI_API int l3ci_flash_decode_poll(void* scratch, size_t scratch_bytes, l3ci_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Causal GQA attention for T > 1 new tokens per sequence (prefill / chunked prefill).
+ *
+ * The reference sends this case to PyTorch (model.py:114-116,
+ * F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True) over cache rows [0, T)); this
+ * entry point has no counterpart in its extension.  Query t of a sequence attends keys
+ * j <= start_pos + t, j < n_keys (start_pos = 0, n_keys = T is the reference's call).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct l3ci_prefill_args {
+  const void* q;          /* bf16 [B, Hq, T, D] by strides (elements); last axis contiguous          */
+  const void* k;          /* bf16 [B, Hkv, n_keys, D] by strides; rows 16-byte aligned               */
+  const void* v;
+  void* out;              /* bf16 [B, Hq, T, D] by strides                                            */
+  int32_t* status;        /* optional device word that receives L3CI_ERR_DEVICE_WAIT if a bounded wait
+                             on a bulk copy runs out; may be null                                      */
+  int32_t B, Hq, Hkv, D;  /* D in {64, 128}; Hq a multiple of Hkv                                      */
+  int32_t T, n_keys, start_pos;
+  int64_t q_sb, q_sh, q_st, k_sb, k_sh, k_st, v_sb, v_sh, v_st, o_sb, o_sh, o_st;
+  float scale;            /* <= 0: 1/sqrt(D)                                                           */
+  l3ci_stream_t stream;
+} l3ci_prefill_args;
+
+L3CI_API int l3ci_prefill_attention(const l3ci_prefill_args* args);
+
+/* ------------------------------------------------------------------------------------------
  * Log-sum-exp merge of `parts` partial results of the same queries over disjoint KV ranges
  * (the per-GPU results of a sequence-sharded cache):
  *   L = logsumexp_p lse[p, r];  out[r, :] = bf16( sum_p exp(lse[p, r] - L) * o[p, r, :] )

@@ -21,7 +21,7 @@ EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
     "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
-    "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge",
+    "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge", "l3ci_prefill_attention",
 )
 
 
@@ -37,6 +37,20 @@ class FlashDecodeArgs(C.Structure):
         ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_st", C.c_int64),
         ("o_sb", C.c_int64), ("o_sh", C.c_int64),
         ("scale", C.c_float), ("max_ctas", C.c_int32), ("stream", C.c_void_p),
+    ]
+
+
+class PrefillArgs(C.Structure):
+    """struct l3ci_prefill_args"""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
+        ("T", C.c_int32), ("n_keys", C.c_int32), ("start_pos", C.c_int32),
+        ("q_sb", C.c_int64), ("q_sh", C.c_int64), ("q_st", C.c_int64),
+        ("k_sb", C.c_int64), ("k_sh", C.c_int64), ("k_st", C.c_int64),
+        ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_st", C.c_int64),
+        ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_st", C.c_int64),
+        ("scale", C.c_float), ("stream", C.c_void_p),
     ]
 
 
@@ -72,6 +86,8 @@ def load() -> C.CDLL:
     lib.l3ci_add_rms_norm.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, vp]
     lib.l3ci_silu_mul.restype = C.c_int
     lib.l3ci_silu_mul.argtypes = [vp, vp, vp, i64, i64, i64, i64, vp]
+    lib.l3ci_prefill_attention.restype = C.c_int
+    lib.l3ci_prefill_attention.argtypes = [C.POINTER(PrefillArgs)]
     lib.l3ci_greedy_step.restype = C.c_int
     lib.l3ci_greedy_step.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, vp, vp, vp, vp]
     lib.l3ci_rot_embed.restype = C.c_int
@@ -288,6 +304,27 @@ def flash_attention_decode_partial(q, k, v, seq_lens=None, scratch: Optional[Dec
     with _on(q):
         _check(load().l3ci_flash_decode(C.byref(a)), "l3ci_flash_decode")
     return o, lse
+
+
+def prefill_attention(q, k, v, start_pos: int = 0, scale: float = 0.0, status=None):
+    """Causal GQA attention of q [B,Hq,T,D] over k, v [B,Hkv,S,D]: query t sees keys j <= start_pos + t.  Returns a
+    bf16 tensor laid out like q."""
+    import torch
+
+    B, Hq, T, D = q.shape
+    out = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device)
+    a = PrefillArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.status = status.data_ptr() if status is not None else None
+    a.B, a.Hq, a.Hkv, a.D, a.T, a.n_keys, a.start_pos = B, Hq, k.shape[1], D, T, k.shape[2], start_pos
+    a.q_sb, a.q_sh, a.q_st = q.stride(0), q.stride(1), q.stride(2)
+    a.k_sb, a.k_sh, a.k_st = k.stride(0), k.stride(1), k.stride(2)
+    a.v_sb, a.v_sh, a.v_st = v.stride(0), v.stride(1), v.stride(2)
+    a.o_sb, a.o_sh, a.o_st = out.stride(0), out.stride(1), out.stride(2)
+    a.scale, a.stream = scale, _stream(q)
+    with _on(q):
+        _check(load().l3ci_prefill_attention(C.byref(a)), "l3ci_prefill_attention")
+    return out
 
 
 def lse_merge(o_parts, lse_parts):

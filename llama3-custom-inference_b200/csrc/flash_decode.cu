@@ -38,6 +38,8 @@
 #include "bf16x8.cuh"
 #include "flash_decode_plan.h"
 #include "host_common.h"
+#include "ptx_sm100.cuh"
+#include "tensor_map.h"
 #include "warp_reduce.cuh"
 
 namespace l3ci {
@@ -47,7 +49,6 @@ constexpr int kStages = 3;            // columns (one tile per head of the group
 constexpr int kStageBytes = 8192;     // K tile + V tile of one head in a stage
 constexpr bool kScoresAhead = true;   // compute a tile's scores while the previous tile is still in its softmax
 constexpr int kHeaderBytes = 256;     // scratch header: status word
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bound of one mbarrier wait
 
 template <int D>
 struct FdCfg {
@@ -96,104 +97,6 @@ struct FdParams {
   float scale_log2e;
   int rec_floats;       // floats per record: R * D / 4 chunks of 8
 };
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Waits for the phase with the given parity, at most kWaitLimitNs.  Warp-uniform result.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  bool ok = mbar_try_wait(bar, parity);
-  if (!__all_sync(kFullMask, ok)) {
-    const unsigned long long t0 = global_ns();
-    for (uint32_t it = 0;; ++it) {
-      ok = mbar_try_wait(bar, parity);
-      if (__all_sync(kFullMask, ok)) break;
-      if ((it & 63u) == 63u) {
-        const bool late = global_ns() - t0 > kWaitLimitNs;
-        if (__any_sync(kFullMask, late)) return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  return pol;
-}
-// One tile (box) of a rank-4 tensor map into shared memory; completion is counted in bytes on `bar`.
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
-                                            int c1, int c2, int c3, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
-      "l"(policy)
-      : "memory");
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-// c += a(16x16, row) * b(16x8, col), bf16 inputs, fp32 accumulate.
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Transposes an 8x8 matrix of 16-bit values held one row per 4 lanes, two values per lane.
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
-  uint32_t r;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
-  return r;
-}
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t ld_global_u32(const __nv_bfloat16* p) {
-  return __ldg(reinterpret_cast<const uint32_t*>(p));
-}
 
 // ---------------------------------------------------------------------------------------------
 // Folding of partial attention states.  A state is (m, l, o): running maximum of the scaled scores
@@ -909,41 +812,6 @@ __global__ void zero_out_kernel(__nv_bfloat16* out, float* o_partial, float* lse
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(f);
-  });
-  return fn;
-}
-
-// Rank-4 map over a [B, Hkv, n_seq, D] view: dims (d, token, head, batch), box 64 x tile tokens x HG heads.
-int make_kv_map(CUtensorMap* map, const void* base, int D, int n_seq, int Hkv, int B, long long st,
-                long long sh, long long sb, int tile, int HG) {
-  auto enc = tensor_map_encoder();
-  if (!enc) return fail(L3CI_ERR_CUDA, "flash_decode: cuTensorMapEncodeTiled is not available");
-  const cuuint64_t row_bytes = (cuuint64_t)D * 2;
-  // A dimension of extent 1 may carry any stride in the caller's view; give it a valid one.
-  const cuuint64_t st_b = n_seq > 1 ? (cuuint64_t)st * 2 : row_bytes;
-  const cuuint64_t sh_b = Hkv > 1 ? (cuuint64_t)sh * 2 : row_bytes;
-  const cuuint64_t sb_b = B > 1 ? (cuuint64_t)sb * 2 : row_bytes;
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)n_seq, (cuuint64_t)Hkv, (cuuint64_t)B};
-  cuuint64_t strides[3] = {st_b, sh_b, sb_b};
-  cuuint32_t box[4] = {64u, (cuuint32_t)tile, (cuuint32_t)HG, 1u};
-  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
-                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         D == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(L3CI_ERR_CUDA, "flash_decode: cuTensorMapEncodeTiled failed with %d", (int)r);
-  return L3CI_OK;
-}
-
 // Floats of one (m, l, o) record: R * D / 4 chunks of {o[4], m, l, -, -}.  A chunk is the unit a lane of the
 // merge reads, and it is one 32-byte sector: the row's maximum and sum travel with every four outputs, so a
 // merge of n records reads n sectors per chunk instead of 3 n (the sums and maxima of a row are wanted by all

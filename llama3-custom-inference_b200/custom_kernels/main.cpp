@@ -162,6 +162,39 @@ std::tuple<Tensor, Tensor> flash_attention_decode_partial(Tensor query, Tensor k
   return {o, lse};
 }
 
+// Causal attention for T > 1 new tokens (model.py:114-116 sends this case to torch's SDPA): query [B,Hq,T,D],
+// keys / values [B,Hkv,S,D] (views of the cache are fine), query t sees keys j <= start_pos + t.  Returns a tensor
+// laid out like `query`.
+Tensor prefill_attention(Tensor query, Tensor keys, Tensor values, int64_t start_pos, double scale) {
+  check_bf16_cuda(query, "query");
+  check_bf16_cuda(keys, "keys");
+  check_bf16_cuda(values, "values");
+  TORCH_CHECK(query.dim() == 4 && keys.dim() == 4 && values.dim() == 4, "query, keys, values must be 4-D");
+  TORCH_CHECK(keys.sizes() == values.sizes() && keys.size(0) == query.size(0) && keys.size(3) == query.size(3),
+              "shape mismatch between query, keys and values");
+  TORCH_CHECK(query.stride(3) == 1 && keys.stride(3) == 1 && values.stride(3) == 1, "last axis must be contiguous");
+  TORCH_CHECK(keys.get_device() == query.get_device() && values.get_device() == query.get_device(), "tensors on different devices");
+  const int64_t B = query.size(0), Hq = query.size(1), T = query.size(2), D = query.size(3), Hkv = keys.size(1), S = keys.size(2);
+  TORCH_CHECK(D == 64 || D == 128, "Unsupported head size for prefill_attention kernel: ", D);
+  TORCH_CHECK(Hkv > 0 && Hq % Hkv == 0, "query heads must be a multiple of kv heads");
+  TORCH_CHECK(start_pos >= 0 && start_pos + T <= S, "start_pos + T must not exceed the keys given");
+  const c10::cuda::CUDAGuard guard(query.device());
+  Tensor out = torch::empty_strided(query.sizes(), query.strides(), query.options());
+  if (B == 0 || T == 0) return out;
+  l3ci_prefill_args a{};
+  a.q = query.data_ptr(); a.k = keys.data_ptr(); a.v = values.data_ptr(); a.out = out.data_ptr(); a.status = nullptr;
+  a.B = (int32_t)B; a.Hq = (int32_t)Hq; a.Hkv = (int32_t)Hkv; a.D = (int32_t)D;
+  a.T = (int32_t)T; a.n_keys = (int32_t)S; a.start_pos = (int32_t)start_pos;
+  a.q_sb = query.stride(0); a.q_sh = query.stride(1); a.q_st = query.stride(2);
+  a.k_sb = keys.stride(0); a.k_sh = keys.stride(1); a.k_st = keys.stride(2);
+  a.v_sb = values.stride(0); a.v_sh = values.stride(1); a.v_st = values.stride(2);
+  a.o_sb = out.stride(0); a.o_sh = out.stride(1); a.o_st = out.stride(2);
+  a.scale = (float)scale;
+  a.stream = current_stream();
+  check_status(l3ci_prefill_attention(&a), "prefill_attention");
+  return out;
+}
+
 // out[b, h, 0, :] = sum_p softmax_p(lse[p, b, h]) * o[p, b, h, :]
 Tensor lse_merge(Tensor o_parts, Tensor lse_parts) {
   TORCH_CHECK(o_parts.is_cuda() && o_parts.scalar_type() == torch::kFloat32 && o_parts.dim() == 4 &&
@@ -397,6 +430,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return (int64_t)l3ci_lse_exchange_bytes((int32_t)ranks, (int32_t)B, (int32_t)Hq, (int32_t)D);
   });
   m.def("lse_merge", torch::wrap_pybind_function(lse_merge), "lse_merge", py::arg("o_parts"), py::arg("lse_parts"));
+  m.def("prefill_attention", torch::wrap_pybind_function(prefill_attention), "prefill_attention", py::arg("query"),
+        py::arg("keys"), py::arg("values"), py::kw_only(), py::arg("start_pos") = 0, py::arg("scale") = 0.0);
   m.def("flash_decode_status", torch::wrap_pybind_function(flash_decode_status), "flash_decode_status",
         py::arg("like"));
   m.def("c_abi_version", [] { return std::string(l3ci_version()); });

@@ -17,8 +17,7 @@ What differs from the reference's loop, all on the caller's side of the kernels:
   * the residual add runs inside the RMSNorm that follows it (`add_rms_norm`), `c_fc2` and `c_fc` are one GEMM
     over the stacked weight, and `silu(gate) * up` is one kernel (`silu_mul`) instead of two elementwise passes.
 GEMMs and the embedding lookup are plain torch ops (cuBLAS); the greedy argmax with its token bookkeeping is one
-kernel (`greedy_step`); prefill attention is torch SDPA, as in
-the reference (model.py:114-116).
+kernel (`greedy_step`); prefill attention (torch SDPA in the reference, model.py:114-116) is `prefill_attention`.
 """
 from __future__ import annotations
 
@@ -90,7 +89,7 @@ class Llama3Decoder:
                 # prefill: all sequences start at position 0 with T tokens (model.py:114-116)
                 k = self.cache_k[l][:B, :T].transpose(1, 2)
                 v = self.cache_v[l][:B, :T].transpose(1, 2)
-                y = F.scaled_dot_product_attention(q.transpose(1, 2), k, v, is_causal=True, enable_gqa=True)
+                y = ext.prefill_attention(q.transpose(1, 2), k, v)                     # causal, GQA
             else:
                 y = ext.flash_attention_decode(q.transpose(1, 2), self.cache_k[l][:B].transpose(1, 2),
                                                self.cache_v[l][:B].transpose(1, 2), seq_lens=seq_lens)  # model.py:118

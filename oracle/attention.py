@@ -76,3 +76,17 @@ def lse_merge_reference(o_parts: torch.Tensor, lse_parts: torch.Tensor) -> torch
     tot = w.sum(dim=0, keepdim=True)
     w = torch.where(tot > 0, w / tot.clamp_min(1e-300), torch.zeros_like(w))
     return (w.unsqueeze(-1) * o).sum(dim=0).float()
+
+
+def prefill_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, start_pos: int = 0,
+                      scale: Optional[float] = None, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Causal attention of T new tokens: the reference's prefill call (model.py:114-116,
+    `F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)` over the first T cache rows),
+    on CPU in fp32 by default.  q [B,Hq,T,D]; k, v [B,Hkv,S,D].  With start_pos > 0 (a later chunk) the same call
+    takes the explicit mask j <= start_pos + t instead of `is_causal`."""
+    qc, kc, vc = (t.detach().cpu().to(dtype) for t in (q, k, v))
+    T, S = q.shape[2], k.shape[2]
+    if start_pos == 0 and S == T:
+        return F.scaled_dot_product_attention(qc, kc, vc, is_causal=True, scale=scale, enable_gqa=True)
+    mask = torch.arange(S).view(1, S) <= (start_pos + torch.arange(T)).view(T, 1)
+    return F.scaled_dot_product_attention(qc, kc, vc, attn_mask=mask.view(1, 1, T, S), scale=scale, enable_gqa=True)
