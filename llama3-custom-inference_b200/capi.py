@@ -50,7 +50,7 @@ class PrefillArgs(C.Structure):
         ("k_sb", C.c_int64), ("k_sh", C.c_int64), ("k_st", C.c_int64),
         ("v_sb", C.c_int64), ("v_sh", C.c_int64), ("v_st", C.c_int64),
         ("o_sb", C.c_int64), ("o_sh", C.c_int64), ("o_st", C.c_int64),
-        ("scale", C.c_float), ("stream", C.c_void_p),
+        ("scale", C.c_float), ("variant", C.c_int32), ("stream", C.c_void_p),
     ]
 
 
@@ -306,7 +306,7 @@ def flash_attention_decode_partial(q, k, v, seq_lens=None, scratch: Optional[Dec
     return o, lse
 
 
-def prefill_attention(q, k, v, start_pos: int = 0, scale: float = 0.0, status=None):
+def prefill_attention(q, k, v, start_pos: int = 0, scale: float = 0.0, status=None, variant: int = 0):
     """Causal GQA attention of q [B,Hq,T,D] over k, v [B,Hkv,S,D]: query t sees keys j <= start_pos + t.  Returns a
     bf16 tensor laid out like q."""
     import torch
@@ -321,7 +321,7 @@ def prefill_attention(q, k, v, start_pos: int = 0, scale: float = 0.0, status=No
     a.k_sb, a.k_sh, a.k_st = k.stride(0), k.stride(1), k.stride(2)
     a.v_sb, a.v_sh, a.v_st = v.stride(0), v.stride(1), v.stride(2)
     a.o_sb, a.o_sh, a.o_st = out.stride(0), out.stride(1), out.stride(2)
-    a.scale, a.stream = scale, _stream(q)
+    a.scale, a.variant, a.stream = scale, variant, _stream(q)
     with _on(q):
         _check(load().l3ci_prefill_attention(C.byref(a)), "l3ci_prefill_attention")
     return out

@@ -23,6 +23,9 @@
 #include "warp_reduce.cuh"
 
 namespace l3ci {
+// prefill_attention_tc.cu: the tcgen05 kernel; -1 when it cannot take the call (Q rows not 16-byte aligned)
+int launch_prefill_tc(const l3ci_prefill_args* a);
+
 namespace {
 
 constexpr int kPfRows = 64;     // query rows per CTA
@@ -279,6 +282,12 @@ extern "C" int l3ci_prefill_attention(const l3ci_prefill_args* a) {
   if ((S > 1 && (a->k_st <= 0 || a->v_st <= 0)) || (Hkv > 1 && (a->k_sh <= 0 || a->v_sh <= 0)) ||
       (B > 1 && (a->k_sb <= 0 || a->v_sb <= 0)))
     return fail(L3CI_ERR_INVALID, "prefill_attention: k/v strides must be positive");
+  if (a->variant < 0 || a->variant > 2) return fail(L3CI_ERR_INVALID, "prefill_attention: variant %d", a->variant);
+  if (a->variant == 1 || (a->variant == 0 && T >= 128)) {
+    const int st = launch_prefill_tc(a);
+    if (st != -1) return st;
+    if (a->variant == 1) return fail(L3CI_ERR_ALIGNMENT, "prefill_attention: the tcgen05 kernel needs 16-byte aligned q rows");
+  }
   CUtensorMap kmap, vmap;
   if (int st = make_kv_map(&kmap, a->k, D, S, Hkv, B, a->k_st, a->k_sh, a->k_sb, kPfKeys, 1)) return st;
   if (int st = make_kv_map(&vmap, a->v, D, S, Hkv, B, a->v_st, a->v_sh, a->v_sb, kPfKeys, 1)) return st;

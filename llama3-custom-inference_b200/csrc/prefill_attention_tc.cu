@@ -1,0 +1,358 @@
+// Causal GQA prefill attention on the 5th-generation tensor cores of sm_100a: tcgen05.mma with operands in shared
+// memory (filled by bulk tensor copies) or tensor memory, accumulators in tensor memory (TMEM).
+//
+// Same computation as prefill_attention.cu (the reference's model.py:114-116 SDPA call), for prompts long enough
+// that the arithmetic, not the launch, is what costs.  One CTA = 128 query rows of one query head:
+//   warp 0        producer: Q once, then K and V tiles of 128 keys through 2-stage rings of bulk tensor copies
+//   warp 1        allocates TMEM and issues the MMAs (one thread): S_j = Q K_j^T into one of two 128-column
+//                 accumulators, O_j = P_j V_j into a third; tcgen05.commit signals the mbarriers
+//   warps 2-5     softmax: thread r owns query row r (tcgen05.ld 32x32b gives a thread its row), two passes over
+//                 S_j (row maximum, then p = 2^(s - m) packed to bf16 and stored over S_j as the A operand of the
+//                 second MMA), then o = o * alpha + O_j with o kept in registers
+// S_{j+1} is computed while the softmax of S_j runs.  K is the B operand as it lies in the cache ([keys][D],
+// K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM is freed on every path.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "bf16x8.cuh"
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+#include "tensor_map.h"
+#include "warp_reduce.cuh"
+
+namespace l3ci {
+namespace {
+
+constexpr int kTcRows = 128;   // query rows per CTA (M of the MMA)
+constexpr int kTcKeys = 128;   // keys per tile (N of S, K of P V)
+constexpr int kTcStages = 2;
+constexpr int kTcThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+struct TcParams {
+  __nv_bfloat16* out;
+  int B, Hq, Hkv, R, T, n_keys, start_pos, m_blocks;
+  long long o_sb, o_sh, o_st;
+  float scale_log2e;
+  int* status;
+};
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, rows (or 8-row groups) 1024 bytes apart: address and byte
+// offsets in 16-byte units, descriptor version 1 (bits 46-47), layout type 2 = SWIZZLE_128B (bits 61-63).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), B MN-major
+// (bit 16), N / 8 (bits 17-22), M / 16 (bits 24-28).
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap, const TcParams p) {
+  constexpr int kHalves = D / 64;
+  constexpr int kBoxBytes = 128 * 128;             // 128 rows of 128 bytes
+  constexpr int kTileBytes = kHalves * kBoxBytes;  // a Q, K or V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_smem = smem_u32(smem);
+  const uint32_t k_smem = q_smem + kTileBytes;                 // [kTcStages]
+  const uint32_t v_smem = k_smem + kTcStages * kTileBytes;     // [kTcStages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kTcStages) * kTileBytes);
+  // barrier indices
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, O_EMPTY = 14, N_BARS = 15 };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i == O_EMPTY) ? 4 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&vmap)) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s[2] = {tmem, tmem + 128u};
+  const uint32_t t_o = tmem + 256u;
+
+  const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
+  const int hq = (int)((blockIdx.x / p.m_blocks) % p.Hq);
+  const int b = (int)(blockIdx.x / ((long long)p.m_blocks * p.Hq));
+  const int hkv = hq / p.R;
+  const int m0 = mb * kTcRows;
+  const int last_row = min(m0 + kTcRows, p.T) - 1;
+  const int keys = min(p.n_keys, p.start_pos + last_row + 1);
+  const int n_tiles = (keys + kTcKeys - 1) / kTcKeys;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ---- producer ----
+    const uint64_t policy = l2_evict_first_policy();
+    if (lane == 0) {
+      mbar_expect_tx(bar(Q_FULL), kTileBytes);
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h) tma_load_4d(q_smem + h * kBoxBytes, &qmap, bar(Q_FULL), h * 64, m0, hq, b, policy);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kTcStages;
+      const uint32_t par = ((j / kTcStages) - 1) & 1;
+      if (j >= kTcStages && !mbar_wait_bounded(bar(K_EMPTY + s), par)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(bar(K_FULL + s), kTileBytes);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_4d(k_smem + s * kTileBytes + h * kBoxBytes, &kmap, bar(K_FULL + s), h * 64, j * kTcKeys, hkv, b, policy);
+      }
+      if (j >= kTcStages && !mbar_wait_bounded(bar(V_EMPTY + s), par)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(bar(V_FULL + s), kTileBytes);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_4d(v_smem + s * kTileBytes + h * kBoxBytes, &vmap, bar(V_FULL + s), h * 64, j * kTcKeys, hkv, b, policy);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (lane 0), the whole warp takes the waits ----
+    constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
+    constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
+    auto issue_s = [&](int j) {  // S_j = Q K_j^T
+      const int s = j % kTcStages;
+      if (lane == 0) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t a = smem_desc(q_smem + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(k_smem + s * kTileBytes + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
+          mma_ss(t_s[j & 1], a, bd, idesc_qk, ks > 0);
+        }
+        tc_commit(bar(S_FULL + (j & 1)));
+        tc_commit(bar(K_EMPTY + s));
+      }
+      __syncwarp();
+    };
+    if (!mbar_wait_bounded(bar(Q_FULL), 0)) ok = false;
+    if (ok && !mbar_wait_bounded(bar(K_FULL), 0)) ok = false;
+    if (ok) {
+      tc_fence_after();
+      issue_s(0);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kTcStages;
+      if (j + 1 < n_tiles) {
+        if (!mbar_wait_bounded(bar(K_FULL + (j + 1) % kTcStages), ((j + 1) / kTcStages) & 1)) { ok = false; break; }
+        tc_fence_after();
+        issue_s(j + 1);
+      }
+      // O_j = P_j V_j once P_j is in TMEM, V_j in shared memory and O_{j-1} has been taken
+      if (!mbar_wait_bounded(bar(P_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(bar(V_FULL + s), (j / kTcStages) & 1)) { ok = false; break; }
+      if (j >= 1 && !mbar_wait_bounded(bar(O_EMPTY), (j - 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int kk = 0; kk < kTcKeys / 16; ++kk) {
+          // V tile: [keys][64 columns] boxes; 16 keys = 2048 bytes further; second 64-column half one box further
+          const uint64_t bd = smem_desc(v_smem + s * kTileBytes + kk * 2048, kBoxBytes, 1024);
+          mma_ts(t_o, t_s[j & 1] + kk * 8, bd, idesc_pv, kk > 0);
+        }
+        tc_commit(bar(O_FULL));
+        tc_commit(bar(V_EMPTY + s));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---- softmax and output: thread owns query row r ----
+    const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int r = q4 * 32 + lane;
+    const int t = m0 + r;                          // query index
+    const int limit = p.start_pos + t;             // last key this row may see
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait_bounded(bar(S_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = t_s[j & 1] + lane_addr;
+      const int j0 = j * kTcKeys;
+      const bool edge = j0 + kTcKeys - 1 > p.start_pos + m0 || j0 + kTcKeys > p.n_keys;  // some row of the block is cut
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t x[32];
+        tmem_ld32(ts + c * 32, x);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = j0 + c * 32 + i;
+          const float v = __uint_as_float(x[i]);
+          if (!edge || (key <= limit && key < p.n_keys)) mx = fmaxf(mx, v);
+        }
+      }
+      const float mn = fmaxf(m_run, mx * p.scale_log2e);
+      const float mu = mn == -INFINITY ? 0.f : mn;
+      const float alpha = fast_exp2(m_run - mu);
+      m_run = mn;
+      // pass 2: p = 2^(s * scale - m), packed to bf16 over the columns already read
+      float ps = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t x[32], pk[16];
+        tmem_ld32(ts + c * 32, x);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int key = j0 + c * 32 + 2 * i;
+          float p0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), p.scale_log2e, -mu));
+          float p1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), p.scale_log2e, -mu));
+          if (edge) {
+            if (key > limit || key >= p.n_keys) p0 = 0.f;
+            if (key + 1 > limit || key + 1 >= p.n_keys) p1 = 0.f;
+          }
+          ps += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(ts + c * 16, pk);
+      }
+      l_run = fmaf(l_run, alpha, ps);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + (j & 1)));
+      // O_j
+      if (!mbar_wait_bounded(bar(O_FULL), j & 1)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t x[32];
+        tmem_ld32(t_o + lane_addr + c * 32, x);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(x[i]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(O_EMPTY));
+    }
+    if (ok && t < p.T) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st;
+#pragma unroll
+      for (int i = 0; i < D; i += 2) *reinterpret_cast<uint32_t*>(orow + i) = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
+    }
+  }
+  if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+  // Every thread comes here (all waits are bounded); then nothing of this CTA uses TMEM any more.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+// Launch for prompts of at least one full block; called by l3ci_prefill_attention.
+int launch_prefill_tc(const l3ci_prefill_args* a) {
+  const int B = a->B, Hq = a->Hq, Hkv = a->Hkv, D = a->D, T = a->T, S = a->n_keys;
+  if (!aligned16(a->q) || a->q_st % 8 || (Hq > 1 && a->q_sh % 8) || (B > 1 && a->q_sb % 8) || a->q_st <= 0 ||
+      (Hq > 1 && a->q_sh <= 0) || (B > 1 && a->q_sb <= 0))
+    return -1;  // Q cannot be described to the copy engine: the caller falls back to the other kernel
+  CUtensorMap qmap, kmap, vmap;
+  if (int st = make_kv_map(&qmap, a->q, D, T, Hq, B, a->q_st, a->q_sh, a->q_sb, kTcRows, 1)) return st;
+  if (int st = make_kv_map(&kmap, a->k, D, S, Hkv, B, a->k_st, a->k_sh, a->k_sb, kTcKeys, 1)) return st;
+  if (int st = make_kv_map(&vmap, a->v, D, S, Hkv, B, a->v_st, a->v_sh, a->v_sb, kTcKeys, 1)) return st;
+  TcParams p;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.R = Hq / Hkv; p.T = T; p.n_keys = S; p.start_pos = a->start_pos;
+  p.m_blocks = (T + kTcRows - 1) / kTcRows;
+  p.o_sb = a->o_sb; p.o_sh = a->o_sh; p.o_st = a->o_st;
+  const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)D);
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = a->status;
+  const long long ctas = (long long)B * Hq * p.m_blocks;
+  if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", ctas);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 15 * 8 + 16;
+  static bool configured[2][64] = {{false}};
+  int dev = 0;
+  L3CI_CUDA_TRY(cudaGetDevice(&dev));
+  const int di = D == 64 ? 0 : 1;
+  if (dev < 0 || dev >= 64 || !configured[di][dev]) {
+    if (D == 64) L3CI_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    else L3CI_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 64) configured[di][dev] = true;
+  }
+  if (D == 64) prefill_tc_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+  else prefill_tc_kernel<128><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+  L3CI_CHECK_LAUNCH("prefill_tc_kernel");
+  return L3CI_OK;
+}
+
+}  // namespace l3ci

@@ -165,7 +165,7 @@ std::tuple<Tensor, Tensor> flash_attention_decode_partial(Tensor query, Tensor k
 // Causal attention for T > 1 new tokens (model.py:114-116 sends this case to torch's SDPA): query [B,Hq,T,D],
 // keys / values [B,Hkv,S,D] (views of the cache are fine), query t sees keys j <= start_pos + t.  Returns a tensor
 // laid out like `query`.
-Tensor prefill_attention(Tensor query, Tensor keys, Tensor values, int64_t start_pos, double scale) {
+Tensor prefill_attention(Tensor query, Tensor keys, Tensor values, int64_t start_pos, double scale, int64_t variant) {
   check_bf16_cuda(query, "query");
   check_bf16_cuda(keys, "keys");
   check_bf16_cuda(values, "values");
@@ -190,6 +190,7 @@ Tensor prefill_attention(Tensor query, Tensor keys, Tensor values, int64_t start
   a.v_sb = values.stride(0); a.v_sh = values.stride(1); a.v_st = values.stride(2);
   a.o_sb = out.stride(0); a.o_sh = out.stride(1); a.o_st = out.stride(2);
   a.scale = (float)scale;
+  a.variant = (int32_t)variant;
   a.stream = current_stream();
   check_status(l3ci_prefill_attention(&a), "prefill_attention");
   return out;
@@ -431,7 +432,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("lse_merge", torch::wrap_pybind_function(lse_merge), "lse_merge", py::arg("o_parts"), py::arg("lse_parts"));
   m.def("prefill_attention", torch::wrap_pybind_function(prefill_attention), "prefill_attention", py::arg("query"),
-        py::arg("keys"), py::arg("values"), py::kw_only(), py::arg("start_pos") = 0, py::arg("scale") = 0.0);
+        py::arg("keys"), py::arg("values"), py::kw_only(), py::arg("start_pos") = 0, py::arg("scale") = 0.0,
+        py::arg("variant") = 0);
   m.def("flash_decode_status", torch::wrap_pybind_function(flash_decode_status), "flash_decode_status",
         py::arg("like"));
   m.def("c_abi_version", [] { return std::string(l3ci_version()); });

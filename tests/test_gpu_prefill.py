@@ -17,10 +17,11 @@ def _case(B, Hq, Hkv, D, T, S, seed):
     return q, k, v
 
 
-def _check(capi, device, B, Hq, Hkv, D, T, S=None, start_pos=0, seed=0, scale=0.0):
+def _check(capi, device, B, Hq, Hkv, D, T, S=None, start_pos=0, seed=0, scale=0.0, variant=0):
     S = T + start_pos if S is None else S
     q, k, v = _case(B, Hq, Hkv, D, T, S, seed)
-    got = capi.prefill_attention(q.to(device), k.to(device), v.to(device), start_pos=start_pos, scale=scale)
+    got = capi.prefill_attention(q.to(device), k.to(device), v.to(device), start_pos=start_pos, scale=scale,
+                                 variant=variant)
     torch.cuda.synchronize()
     assert got.shape == q.shape and got.stride() == q.stride() and got.dtype == torch.bfloat16
     want = attention.prefill_reference(q, k[:, :, :start_pos + T], v[:, :, :start_pos + T], start_pos,
@@ -28,10 +29,11 @@ def _check(capi, device, B, Hq, Hkv, D, T, S=None, start_pos=0, seed=0, scale=0.
     compare.assert_close_attention(got, want, ATOL, RTOL, REL_L2)
 
 
+@pytest.mark.parametrize("variant", [1, 2])      # 1: tcgen05 / tensor-memory kernel, 2: mma.sync kernel
 @pytest.mark.parametrize("D", [64, 128])
-@pytest.mark.parametrize("T", [2, 17, 64, 65, 128, 200, 513])
-def test_prompt_lengths_around_the_block_sizes(capi, device, D, T):
-    _check(capi, device, 2, 8, 2, D, T, seed=T + D)
+@pytest.mark.parametrize("T", [2, 17, 64, 65, 128, 129, 200, 256, 513])
+def test_prompt_lengths_around_the_block_sizes(capi, device, D, T, variant):
+    _check(capi, device, 2, 8, 2, D, T, seed=T + D, variant=variant)
 
 
 @pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (6, 2), (16, 1), (24, 8)])
@@ -44,18 +46,22 @@ def test_model_prefill_shape(capi, device):
     _check(capi, device, 4, 32, 8, 64, 128, seed=5)
 
 
-def test_long_prompt(capi, device):
-    _check(capi, device, 1, 32, 8, 128, 2048, seed=6)
+@pytest.mark.parametrize("variant", [1, 2])
+def test_long_prompt(capi, device, variant):
+    _check(capi, device, 1, 32, 8, 128, 2048, seed=6, variant=variant)
+    _check(capi, device, 2, 32, 8, 64, 1000, seed=7, variant=variant)
 
 
-@pytest.mark.parametrize("start_pos,T,S", [(100, 60, 160), (64, 64, 200), (1, 1, 2), (300, 5, 305), (7, 130, 137)])
-def test_later_chunk_and_longer_cache(capi, device, start_pos, T, S):
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("start_pos,T,S", [(100, 60, 160), (64, 64, 200), (1, 1, 2), (300, 5, 305), (7, 130, 137),
+                                           (200, 300, 640), (128, 128, 256)])
+def test_later_chunk_and_longer_cache(capi, device, start_pos, T, S, variant):
     # a chunk that starts at start_pos; rows beyond start_pos + T of the cache must not be seen
     q, k, v = _case(2, 8, 4, 128, T, S, seed=start_pos)
     k2, v2 = k.clone(), v.clone()
     k2[:, :, start_pos + T:] = 1e4                       # poison what lies beyond the causal limit
     v2[:, :, start_pos + T:] = 1e4
-    got = capi.prefill_attention(q.to(device), k2.to(device), v2.to(device), start_pos=start_pos)
+    got = capi.prefill_attention(q.to(device), k2.to(device), v2.to(device), start_pos=start_pos, variant=variant)
     want = attention.prefill_reference(q, k[:, :, :start_pos + T], v[:, :, :start_pos + T], start_pos)
     compare.assert_close_attention(got, want, ATOL, RTOL, REL_L2)
 
