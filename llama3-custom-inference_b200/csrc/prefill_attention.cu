@@ -283,7 +283,9 @@ extern "C" int l3ci_prefill_attention(const l3ci_prefill_args* a) {
       (B > 1 && (a->k_sb <= 0 || a->v_sb <= 0)))
     return fail(L3CI_ERR_INVALID, "prefill_attention: k/v strides must be positive");
   if (a->variant < 0 || a->variant > 2) return fail(L3CI_ERR_INVALID, "prefill_attention: variant %d", a->variant);
-  if (a->variant == 1 || (a->variant == 0 && T >= 128)) {
+  // By measurement (B=4, Hq=32, T=2048): the tcgen05 kernel wins at head size 128 (427 vs 324 TFLOP/s), the mma.sync
+  // kernel at head size 64 (278 vs 245), where the tensor work per tile is half and the softmax the same.
+  if (a->variant == 1 || (a->variant == 0 && T >= 128 && D == 128)) {
     const int st = launch_prefill_tc(a);
     if (st != -1) return st;
     if (a->variant == 1) return fail(L3CI_ERR_ALIGNMENT, "prefill_attention: the tcgen05 kernel needs 16-byte aligned q rows");

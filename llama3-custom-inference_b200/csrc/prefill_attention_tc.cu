@@ -5,12 +5,17 @@
 // that the arithmetic, not the launch, is what costs.  One CTA = 128 query rows of one query head:
 //   warp 0        producer: Q once, then K and V tiles of 128 keys through 2-stage rings of bulk tensor copies
 //   warp 1        allocates TMEM and issues the MMAs (one thread): S_j = Q K_j^T into one of two 128-column
-//                 accumulators, O_j = P_j V_j into a third; tcgen05.commit signals the mbarriers
-//   warps 2-5     softmax: thread r owns query row r (tcgen05.ld 32x32b gives a thread its row), two passes over
-//                 S_j (row maximum, then p = 2^(s - m) packed to bf16 and stored over S_j as the A operand of the
-//                 second MMA), then o = o * alpha + O_j with o kept in registers
-// S_{j+1} is computed while the softmax of S_j runs.  K is the B operand as it lies in the cache ([keys][D],
-// K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM is freed on every path.
+//                 accumulators, O += P_j V_j into a third; tcgen05.commit signals the mbarriers
+//   warps 2-9     softmax, two threads per query row (tcgen05.ld 32x32b gives a thread its row; warps w and w + 4
+//                 reach the same rows and take columns 0-63 and 64-127): the half row of S_j goes to registers, the
+//                 two halves swap their maxima through shared memory, p = 2^(s * scale - m_ref) is packed to bf16
+//                 and stored over S_j as the A operand of the second MMA.  O stays in TMEM and the MMA accumulates
+//                 into it; the reference maximum m_ref of a row only moves when the running maximum has outgrown
+//                 it by more than 2^8 (p stays below 2^8, harmless in fp32 / bf16), and only then is the row of O
+//                 rescaled in TMEM
+// S_{j+1} is computed while the softmax of S_j runs, P_j V_j while the softmax of S_{j+1} runs.  K is the B operand
+// as it lies in the cache ([keys][D], K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM
+// is freed on every path.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -28,8 +33,9 @@ namespace {
 constexpr int kTcRows = 128;   // query rows per CTA (M of the MMA)
 constexpr int kTcKeys = 128;   // keys per tile (N of S, K of P V)
 constexpr int kTcStages = 2;
-constexpr int kTcThreads = 192;
-constexpr uint32_t kTmemCols = 512;
+constexpr int kTcSoftmaxWarps = 8;                       // two groups of four: columns 0-63 and 64-127 of a row
+constexpr int kTcThreads = 32 * (2 + kTcSoftmaxWarps);   // + producer warp + MMA warp
+constexpr uint32_t kTmemCols = 512;                      // S_0, S_1 (128 columns each), O (D columns)
 
 struct TcParams {
   __nv_bfloat16* out;
@@ -115,15 +121,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   const uint32_t k_smem = q_smem + kTileBytes;                 // [kTcStages]
   const uint32_t v_smem = k_smem + kTcStages * kTileBytes;     // [kTcStages]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kTcStages) * kTileBytes);
-  // barrier indices
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, O_EMPTY = 14, N_BARS = 15 };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, N_BARS = 14 };
+  float* xchg = reinterpret_cast<float*>(bars + N_BARS);       // [3][2 halves][128 rows]: maxima of even / odd tiles, sums
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg + 6 * kTcRows);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i == O_EMPTY) ? 4 : 1);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
@@ -182,7 +188,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     // ---- MMA issue (lane 0), the whole warp takes the waits ----
     constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
     constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
-    auto issue_s = [&](int j) {  // S_j = Q K_j^T
+    auto issue_s = [&](int j) {  // S_j = Q K_j^T; its accumulator held P_{j-2}, read by an MMA issued before this one
       const int s = j % kTcStages;
       if (lane == 0) {
 #pragma unroll
@@ -209,17 +215,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         tc_fence_after();
         issue_s(j + 1);
       }
-      // O_j = P_j V_j once P_j is in TMEM, V_j in shared memory and O_{j-1} has been taken
+      // O += P_j V_j once P_j is in TMEM (any rescaling of O happened before that) and V_j in shared memory
       if (!mbar_wait_bounded(bar(P_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
       if (!mbar_wait_bounded(bar(V_FULL + s), (j / kTcStages) & 1)) { ok = false; break; }
-      if (j >= 1 && !mbar_wait_bounded(bar(O_EMPTY), (j - 1) & 1)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int kk = 0; kk < kTcKeys / 16; ++kk) {
           // V tile: [keys][64 columns] boxes; 16 keys = 2048 bytes further; second 64-column half one box further
           const uint64_t bd = smem_desc(v_smem + s * kTileBytes + kk * 2048, kBoxBytes, 1024);
-          mma_ts(t_o, t_s[j & 1] + kk * 8, bd, idesc_pv, kk > 0);
+          mma_ts(t_o, t_s[j & 1] + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(bar(O_FULL));
         tc_commit(bar(V_EMPTY + s));
@@ -227,86 +232,113 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       __syncwarp();
     }
   } else {
-    // ---- softmax and output: thread owns query row r ----
+    // ---- softmax and output: two threads per query row r, `half` says which 64 columns of S (and which half of
+    // the columns of O) are this thread's ----
     const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;              // warps 2-5: 0, warps 6-9: 1
     const int r = q4 * 32 + lane;
     const int t = m0 + r;                          // query index
     const int limit = p.start_pos + t;             // last key this row may see
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait_bounded(bar(S_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
+    constexpr float kLazy = 8.f;                   // log2 of how far the running maximum may outgrow m_ref
+    constexpr int kOHalf = D / 2;                  // columns of O this thread rescales and writes
+    float m_ref = -INFINITY, l_run = 0.f;          // l_run: this thread's half of the row sum
+    auto pair_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"r"(32 * kTcSoftmaxWarps) : "memory"); };
+    for (int j = 0; j < n_tiles; ++j) {
+      // (a failed wait must not leave the other half of the rows alone at the pair barrier: keep going, flagged)
+      if (ok && !mbar_wait_bounded(bar(S_FULL + (j & 1)), (j >> 1) & 1)) ok = false;
       tc_fence_after();
       const uint32_t ts = t_s[j & 1] + lane_addr;
-      const int j0 = j * kTcKeys;
-      const bool edge = j0 + kTcKeys - 1 > p.start_pos + m0 || j0 + kTcKeys > p.n_keys;  // some row of the block is cut
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32];
-        tmem_ld32(ts + c * 32, x);
-        tc_wait_ld();
+      const int j0 = j * kTcKeys + half * 64;      // first key of this thread's columns
+      const bool edge = j * kTcKeys + kTcKeys - 1 > p.start_pos + m0 || (j + 1) * kTcKeys > p.n_keys;
+      uint32_t x[2][32];
+      tmem_ld32(ts + half * 64, x[0]);
+      tmem_ld32(ts + half * 64 + 32, x[1]);
+      tc_wait_ld();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int key = j0 + c * 32 + i;
-          const float v = __uint_as_float(x[i]);
-          if (!edge || (key <= limit && key < p.n_keys)) mx = fmaxf(mx, v);
+          if (edge) {
+            const int key = j0 + c * 32 + i;
+            if (key > limit || key >= p.n_keys) x[c][i] = 0xff800000u;  // -inf
+          }
+          mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[c][i]));
         }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* xm = xchg + (j & 1) * 2 * kTcRows;    // tiles alternate between two areas: a thread may be a tile ahead
+      xm[half * kTcRows + r] = mx;
+      pair_sync();                                 // both halves of every row have read S_j and posted their maximum
+      mx = fmaxf(mx, xm[(half ^ 1) * kTcRows + r]) * p.scale_log2e;
+      // Move the reference maximum (and rescale this warp's rows of O) only when some row needs it.  Both threads
+      // of a row see the same numbers and decide alike.
+      if (__any_sync(kFullMask, mx > m_ref + kLazy)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        if (j > 0) {
+          // O holds the products up to tile j-1 once their MMA has completed
+          if (ok && !mbar_wait_bounded(bar(O_FULL), (j - 1) & 1)) ok = false;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < kOHalf / 32; ++c) {
+            uint32_t y[32];
+            const uint32_t at = t_o + lane_addr + half * kOHalf + c * 32;
+            tmem_ld32(at, y);
+            tc_wait_ld();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(y[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(y[16 + i]) * alpha);
+            }
+            tmem_st16(at, lo);
+            tmem_st16(at + 16, hi);
+          }
+          l_run *= alpha;
+        }
+        m_ref = m_new;
       }
-      const float mn = fmaxf(m_run, mx * p.scale_log2e);
-      const float mu = mn == -INFINITY ? 0.f : mn;
-      const float alpha = fast_exp2(m_run - mu);
-      m_run = mn;
-      // pass 2: p = 2^(s * scale - m), packed to bf16 over the columns already read
-      float ps = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32], pk[16];
-        tmem_ld32(ts + c * 32, x);
-        tc_wait_ld();
+      const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int key = j0 + c * 32 + 2 * i;
-          float p0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), p.scale_log2e, -mu));
-          float p1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), p.scale_log2e, -mu));
-          if (edge) {
-            if (key > limit || key >= p.n_keys) p0 = 0.f;
-            if (key + 1 > limit || key + 1 >= p.n_keys) p1 = 0.f;
-          }
-          ps += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(x[c][2 * i]), p.scale_log2e, -mu));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(x[c][2 * i + 1]), p.scale_log2e, -mu));
+          ps4[i & 3] += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st16(ts + c * 16, pk);
+        tmem_st16(ts + half * 32 + c * 16, pk);    // P_j: 64 packed columns over the first 64 of S_j
       }
-      l_run = fmaf(l_run, alpha, ps);
+      l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_FULL + (j & 1)));
-      // O_j
-      if (!mbar_wait_bounded(bar(O_FULL), j & 1)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t x[32];
-        tmem_ld32(t_o + lane_addr + c * 32, x);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(x[i]));
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(O_EMPTY));
     }
-    if (ok && t < p.T) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st;
+    if (ok && !mbar_wait_bounded(bar(O_FULL), (n_tiles - 1) & 1)) ok = false;
+    tc_fence_after();
+    xchg[(4 + half) * kTcRows + r] = l_run;
+    pair_sync();
+    const float l_all = l_run + xchg[(4 + (half ^ 1)) * kTcRows + r];
+    if (ok) {
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st + half * kOHalf;
 #pragma unroll
-      for (int i = 0; i < D; i += 2) *reinterpret_cast<uint32_t*>(orow + i) = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
+      for (int c = 0; c < kOHalf / 32; ++c) {
+        uint32_t y[32];
+        tmem_ld32(t_o + lane_addr + half * kOHalf + c * 32, y);
+        tc_wait_ld();
+        if (t < p.T) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            *reinterpret_cast<uint32_t*>(orow + c * 32 + i) =
+                pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
+        }
+      }
     }
   }
   if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
@@ -339,7 +371,7 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   const long long ctas = (long long)B * Hq * p.m_blocks;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", ctas);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 15 * 8 + 16;
+  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 14 * 8 + 6 * kTcRows * 4 + 16;
   static bool configured[2][64] = {{false}};
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
