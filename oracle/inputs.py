@@ -66,3 +66,13 @@ def config4(seed: int = 42, B: int = 2, S: int = 2048, hidden: int = 2048, n_hea
 
 ROPE_CONFIG4 = dict(theta=500000.0, use_scaled=True, scale_factor=32, low_freq_factor=1, high_freq_factor=4,
                     old_context_len=8192)
+
+
+def prefill_case(B: int, Hq: int, Hkv: int, D: int, T: int, seed: int = 42):
+    """Seeded q [B,Hq,T,D], k, v [B,Hkv,T,D] in the model's layout (views of [B,T,H,D], model.py:96-112), bf16,
+    N(0,1): the operands of the reference's prefill attention call (model.py:114-116)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, T, Hq, D, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(B, T, Hkv, D, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(B, T, Hkv, D, generator=g).bfloat16().transpose(1, 2)
+    return q, k, v

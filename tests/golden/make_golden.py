@@ -1,7 +1,7 @@
 """Generates tests/golden/reference_vectors.pt by RUNNING the reference's own Python code.
 
-Needs the reference checkout (default /root/reference, or argv[1]); the produced file is committed, so
-the tests never read the checkout.  What is executed from the reference:
+Needs a checkout of the reference (its path as argv[1]); the produced file is committed, so the tests
+never read the checkout.  What is executed from the reference:
 
   * model.precompute_freqs_cis / model.apply_scaling (model.py:27-60), imported from the reference's
     model.py with its compiled extension replaced by an empty stub module (model.py:23 imports it at
@@ -28,6 +28,10 @@ sys.path.insert(0, str(REPO))
 from oracle import inputs  # noqa: E402
 
 
+# name -> (B, Hq, Hkv, D, T, seed) of oracle.inputs.prefill_case
+PREFILL_CASES = {"d64_r4_t40": (2, 8, 2, 64, 40, 21), "d128_r2_t150": (1, 4, 2, 128, 150, 22)}
+
+
 def sha(t: torch.Tensor) -> str:
     return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
 
@@ -50,7 +54,9 @@ def reference_attention(case) -> torch.Tensor:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    ref = Path(sys.argv[1])
     model = import_reference_model(ref)
     out = {}
     rows = [0, 1, 2, 3, 17, 127, 511, 2047, 8191, 16383]
@@ -73,6 +79,12 @@ def main() -> None:
     for name, case in cases.items():
         out[f"sdpa_{name}_bf16"] = reference_attention(case).contiguous()
         out[f"sdpa_{name}_inputs_sha256"] = sha(case.q) + sha(case.k) + sha(case.v)
+    # the prefill call of model.py:114-116, same backend selection, on bf16 CPU tensors
+    for name, shape in PREFILL_CASES.items():
+        q, k, v = inputs.prefill_case(*shape)
+        with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
+            out[f"prefill_{name}_bf16"] = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True).contiguous()
+        out[f"prefill_{name}_inputs_sha256"] = sha(q) + sha(k) + sha(v)
     out["torch_version"] = str(torch.__version__)
     dst = Path(__file__).with_name("reference_vectors.pt")
     torch.save(out, dst)

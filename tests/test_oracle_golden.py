@@ -66,6 +66,23 @@ def test_attention_oracle_matches_reference_sdpa(golden, name):
     assert torch.equal(again, ref_bf16)
 
 
+PREFILL_CASES = {"d64_r4_t40": (2, 8, 2, 64, 40, 21), "d128_r2_t150": (1, 4, 2, 128, 150, 22)}
+
+
+@pytest.mark.parametrize("name", sorted(PREFILL_CASES))
+def test_prefill_oracle_matches_reference_sdpa(golden, name):
+    """The golden tensors are outputs of the reference's prefill call (model.py:114-116) on these inputs."""
+    q, k, v = inputs.prefill_case(*PREFILL_CASES[name])
+    assert _sha(q) + _sha(k) + _sha(v) == golden[f"prefill_{name}_inputs_sha256"], "input generator drifted"
+    ref_bf16 = golden[f"prefill_{name}_bf16"]
+    compare.assert_close_attention(ref_bf16, attention.prefill_reference(q, k, v), atol=2e-2, rtol=1e-2, max_rel_l2=2e-2)
+    assert torch.equal(attention.prefill_reference(q, k, v, dtype=torch.bfloat16), ref_bf16)
+    # the explicit-mask form used for later chunks is the same function at start_pos = 0
+    T = q.shape[2]
+    chunk = attention.prefill_reference(q[:, :, T // 2:], k, v, start_pos=T // 2)
+    compare.assert_close_attention(chunk, attention.prefill_reference(q, k, v)[:, :, T // 2:], atol=1e-5, rtol=1e-5, max_rel_l2=1e-5)
+
+
 @pytest.mark.parametrize("ragged", [False, True])
 def test_attention_oracle_matches_float64_restatement(ragged):
     case = inputs.decode_case(3, 12, 4, 64, 150, seed=3, ragged=ragged)
