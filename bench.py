@@ -702,7 +702,9 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
     decode_steps = (G - 1) * steps
     line = {
         "metric": "Llama-3.2-1B decode tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": 1, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": 1, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+        # the reference's README publishes 2041.67 tokens/s for this configuration (on an RTX 4060)
+        "vs_baseline": value / 2041.67 if (G == 2048 and B == 64) else None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"C5 random-init Llama-3.2-1B architecture, batch {B}/GPU, prompt {P}, {G} greedy tokens",
                    "global_batch": B * world, "parallelism": "replicas x%d" % world,
