@@ -10,13 +10,17 @@
 //  * Persistent grid.  The work is the list of "columns" (sequence b, head group g, tile j of
 //    kTile tokens); a column covers the same tokens for HG = gcd(Hkv, 8) neighbouring KV heads.
 //    The list is cut into gridDim.x equal contiguous ranges, so every SM streams the same number
-//    of bytes whatever the sequence lengths are.  A CTA has HG warps; warp w owns KV head
-//    g*HG + w of every column, so a CTA walks HG*D*2 contiguous bytes per token.
-//  * Each warp runs its own kStages-deep pipeline of TMA tile loads (cp.async.bulk.tensor, 128-byte
-//    swizzle) signalled through its own mbarriers: no CTA-wide barrier in the loop.
-//  * Q.K^T and P.V run on tensor cores (mma.sync m16n8k16 bf16, the R <= 16 query heads of the
-//    group padded to the 16-row A tile), which leaves the issue slots to the memory pipeline.
-//    Online softmax statistics live in registers; row reductions are 4-lane shuffles.
+//    of bytes whatever the sequence lengths are.  A CTA has HG consumer warps and a producer
+//    warp; consumer w owns KV head g*HG + w of every column, so a CTA walks HG*D*2 contiguous
+//    bytes per token.
+//  * The producer warp fills a kStages-deep ring of CTA-wide stages with bulk tensor copies
+//    (cp.async.bulk.tensor, one box of all HG heads per 64-column half of K and of V, 128-byte
+//    swizzle); full / empty mbarriers pair it with the consumers, no CTA-wide barrier in the loop.
+//  * Q.K^T and P.V run on tensor cores (mma.sync m16n8k16 bf16) in transposed form, tokens and
+//    output columns on the 16 rows of a tile and the query heads of the group on its 8 columns, so
+//    that up to 8 query heads per KV head leave no padding; online softmax statistics live in
+//    registers.  Tensor cores are there to spare issue slots, not for throughput: the kernel
+//    waits on HBM.
 //  * A (sequence, head) unit that is cut by a range boundary leaves an fp32 (m, l, o) record per
 //    CTA and a count on the unit's arrival counter.  When a warp has streamed its whole range it
 //    comes back to the (at most two) shared units it took part in, waits until all their records
