@@ -6,16 +6,17 @@
 //   warp 0        producer: Q once, then K and V tiles of 128 keys through 2-stage rings of bulk tensor copies
 //   warp 1        allocates TMEM and issues the MMAs (one thread): S_j = Q K_j^T into one of two 128-column
 //                 accumulators, O += P_j V_j into a third; tcgen05.commit signals the mbarriers
-//   warps 2-9     softmax, two threads per query row (tcgen05.ld 32x32b gives a thread its row; warps w and w + 4
-//                 reach the same rows and take columns 0-63 and 64-127): the half row of S_j goes to registers, the
-//                 two halves swap their maxima through shared memory, p = 2^(s * scale - m_ref) is packed to bf16
-//                 and stored over S_j as the A operand of the second MMA.  O stays in TMEM and the MMA accumulates
-//                 into it; the reference maximum m_ref of a row only moves when the running maximum has outgrown
-//                 it by more than 2^8 (p stays below 2^8, harmless in fp32 / bf16), and only then is the row of O
-//                 rescaled in TMEM
-// S_{j+1} is computed while the softmax of S_j runs, P_j V_j while the softmax of S_{j+1} runs.  K is the B operand
-// as it lies in the cache ([keys][D], K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM
-// is freed on every path.
+//   warps 2-9     softmax, two groups of four warps: group e takes the tiles j with j % 2 == e, with its own
+//                 score accumulator S_e, its own output accumulator O_e and its own running (m_ref, l) per row, so
+//                 the two groups never wait for each other and one group's TMEM reads run under the other's
+//                 exponentials.  Thread r of a group owns query row r (tcgen05.ld 32x32b gives a thread its row):
+//                 the row of S_j goes to registers, p = 2^(s * scale - m_ref) is packed to bf16 and stored over
+//                 S_j as the A operand of the second MMA.  O_e stays in TMEM and the MMA accumulates into it; the
+//                 reference maximum m_ref of a row only moves when the running maximum has outgrown it by more
+//                 than 2^8 (p stays below 2^8, harmless in fp32 / bf16), and only then is the row of O_e rescaled
+//                 in TMEM.  At the end the two groups' (m_ref, l, O) of a row are merged like two split-KV partials
+// S_{j+1} is computed while the softmax of S_j runs.  K is the B operand as it lies in the cache ([keys][D],
+// K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM is freed on every path.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -33,9 +34,9 @@ namespace {
 constexpr int kTcRows = 128;   // query rows per CTA (M of the MMA)
 constexpr int kTcKeys = 128;   // keys per tile (N of S, K of P V)
 constexpr int kTcStages = 2;
-constexpr int kTcSoftmaxWarps = 8;                       // two groups of four: columns 0-63 and 64-127 of a row
+constexpr int kTcSoftmaxWarps = 8;                       // two groups of four: even tiles, odd tiles
 constexpr int kTcThreads = 32 * (2 + kTcSoftmaxWarps);   // + producer warp + MMA warp
-constexpr uint32_t kTmemCols = 512;                      // S_0, S_1 (128 columns each), O (D columns)
+constexpr uint32_t kTmemCols = 512;                      // S_0, S_1 (128 columns each), O_0, O_1 (D columns each)
 
 struct TcParams {
   __nv_bfloat16* out;
@@ -128,15 +129,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   const uint32_t k_smem = q_smem + kTileBytes;                 // [kTcStages]
   const uint32_t v_smem = k_smem + kTcStages * kTileBytes;     // [kTcStages]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kTcStages) * kTileBytes);
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, N_BARS = 14 };
-  float* xchg = reinterpret_cast<float*>(bars + N_BARS);       // [3][2 halves][128 rows]: maxima of even / odd tiles, sums
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg + 6 * kTcRows);
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, N_BARS = 15 };
+  float* xchg = reinterpret_cast<float*>(bars + N_BARS);       // [2 groups][128 rows][m_ref, l]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xchg + 4 * kTcRows);
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps : 1);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps / 2 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
@@ -152,7 +153,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_s[2] = {tmem, tmem + 128u};
-  const uint32_t t_o = tmem + 256u;
+  const uint32_t t_o[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
 
   const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
   const int hq = (int)((blockIdx.x / p.m_blocks) % p.Hq);
@@ -222,7 +223,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         tc_fence_after();
         issue_s(j + 1);
       }
-      // O += P_j V_j once P_j is in TMEM (any rescaling of O happened before that) and V_j in shared memory
+      // O_e += P_j V_j (e = j % 2) once P_j is in TMEM (any rescaling of O_e happened before that) and V_j in
+      // shared memory
       if (!mbar_wait_bounded(bar(P_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
       if (!mbar_wait_bounded(bar(V_FULL + s), (j / kTcStages) & 1)) { ok = false; break; }
       tc_fence_after();
@@ -231,40 +233,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         for (int kk = 0; kk < kTcKeys / 16; ++kk) {
           // V tile: [keys][64 columns] boxes; 16 keys = 2048 bytes further; second 64-column half one box further
           const uint64_t bd = smem_desc(v_smem + s * kTileBytes + kk * 2048, kBoxBytes, 1024);
-          mma_ts(t_o, t_s[j & 1] + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(t_o[j & 1], t_s[j & 1] + kk * 8, bd, idesc_pv, (j > 1 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(bar(O_FULL));
+        tc_commit(bar(O_FULL + (j & 1)));
         tc_commit(bar(V_EMPTY + s));
       }
       __syncwarp();
     }
   } else {
-    // ---- softmax and output: two threads per query row r, `half` says which 64 columns of S (and which half of
-    // the columns of O) are this thread's ----
+    // ---- softmax and output: group e = tiles j % 2 == e; thread owns query row r of its group's tiles ----
     const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
-    const int half = (warp - 2) >> 2;              // warps 2-5: 0, warps 6-9: 1
+    const int e = (warp - 2) >> 2;                 // warps 2-5: even tiles, warps 6-9: odd tiles
     const int r = q4 * 32 + lane;
     const int t = m0 + r;                          // query index
     const int limit = p.start_pos + t;             // last key this row may see
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    const uint32_t ts = t_s[e] + lane_addr, to = t_o[e] + lane_addr;
     constexpr float kLazy = 8.f;                   // log2 of how far the running maximum may outgrow m_ref
-    constexpr int kOHalf = D / 2;                  // columns of O this thread rescales and writes
-    float m_ref = -INFINITY, l_run = 0.f;          // l_run: this thread's half of the row sum
-    auto pair_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"r"(32 * kTcSoftmaxWarps) : "memory"); };
-    for (int j = 0; j < n_tiles; ++j) {
-      // (a failed wait must not leave the other half of the rows alone at the pair barrier: keep going, flagged)
-      if (ok && !mbar_wait_bounded(bar(S_FULL + (j & 1)), (j >> 1) & 1)) ok = false;
+    float m_ref = -INFINITY, l_run = 0.f;
+    int done = 0;                                  // tiles of this group so far
+    for (int j = e; j < n_tiles && ok; j += 2, ++done) {
+      if (!mbar_wait_bounded(bar(S_FULL + e), done & 1)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t ts = t_s[j & 1] + lane_addr;
-      const int j0 = j * kTcKeys + half * 64;      // first key of this thread's columns
-      const bool edge = j * kTcKeys + kTcKeys - 1 > p.start_pos + m0 || (j + 1) * kTcKeys > p.n_keys;
-      uint32_t xx[64];
-      tmem_ld64(ts + half * 64, xx);
+      const int j0 = j * kTcKeys;
+      const bool edge = j0 + kTcKeys - 1 > p.start_pos + m0 || j0 + kTcKeys > p.n_keys;  // some row of the block is cut
+      uint32_t x[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, x[c]);
       tc_wait_ld();
-      uint32_t (&x)[2][32] = reinterpret_cast<uint32_t (&)[2][32]>(xx);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (edge) {
@@ -273,25 +272,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
           }
           mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[c][i]));
         }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      float* xm = xchg + (j & 1) * 2 * kTcRows;    // tiles alternate between two areas: a thread may be a tile ahead
-      xm[half * kTcRows + r] = mx;
-      pair_sync();                                 // both halves of every row have read S_j and posted their maximum
-      mx = fmaxf(mx, xm[(half ^ 1) * kTcRows + r]) * p.scale_log2e;
-      // Move the reference maximum (and rescale this warp's rows of O) only when some row needs it.  Both threads
-      // of a row see the same numbers and decide alike.
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+      // Move the reference maximum (and rescale this warp's rows of O_e) only when some row needs it.
       if (__any_sync(kFullMask, mx > m_ref + kLazy)) {
         const float m_new = fmaxf(m_ref, mx);
         const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
-        if (j > 0) {
-          // O holds the products up to tile j-1 once their MMA has completed
-          if (ok && !mbar_wait_bounded(bar(O_FULL), (j - 1) & 1)) ok = false;
+        if (done > 0) {
+          // O_e holds the products of this group's earlier tiles once their MMA has completed
+          if (!mbar_wait_bounded(bar(O_FULL + e), (done - 1) & 1)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < kOHalf / 32; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t y[32];
-            const uint32_t at = t_o + lane_addr + half * kOHalf + c * 32;
-            tmem_ld32(at, y);
+            tmem_ld32(to + c * 32, y);
             tc_wait_ld();
             uint32_t lo[16], hi[16];
 #pragma unroll
@@ -299,8 +292,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
               lo[i] = __float_as_uint(__uint_as_float(y[i]) * alpha);
               hi[i] = __float_as_uint(__uint_as_float(y[16 + i]) * alpha);
             }
-            tmem_st16(at, lo);
-            tmem_st16(at + 16, hi);
+            tmem_st16(to + c * 32, lo);
+            tmem_st16(to + c * 32 + 16, hi);
           }
           l_run *= alpha;
         }
@@ -309,7 +302,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -318,32 +311,51 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
           ps4[i & 3] += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st16(ts + half * 32 + c * 16, pk);    // P_j: 64 packed columns over the first 64 of S_j
+        tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
       }
       l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL + (j & 1)));
+      if (lane == 0) mbar_arrive(bar(P_FULL + e));
     }
-    if (ok && !mbar_wait_bounded(bar(O_FULL), (n_tiles - 1) & 1)) ok = false;
+    // this group's last product
+    if (ok && done > 0 && !mbar_wait_bounded(bar(O_FULL + e), (done - 1) & 1)) ok = false;
     tc_fence_after();
-    xchg[(4 + half) * kTcRows + r] = l_run;
-    pair_sync();
-    const float l_all = l_run + xchg[(4 + (half ^ 1)) * kTcRows + r];
-    if (ok) {
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st + half * kOHalf;
+    // Merge the two groups' partial results of a row like two split-KV partials; each of the two threads of a row
+    // writes one half of the output columns.
+    xchg[(e * kTcRows + r) * 2] = m_ref;
+    xchg[(e * kTcRows + r) * 2 + 1] = l_run;
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * kTcSoftmaxWarps) : "memory");
+    const float m_other = xchg[((e ^ 1) * kTcRows + r) * 2], l_other = xchg[((e ^ 1) * kTcRows + r) * 2 + 1];
+    const float m_all = fmaxf(m_ref, m_other);
+    const float a_me = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_all);
+    const float a_ot = m_other == -INFINITY ? 0.f : fast_exp2(m_other - m_all);
+    const float l_all = l_run * a_me + l_other * a_ot;
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    constexpr int kOHalf = D / 2;
+    const bool any_me = __any_sync(kFullMask, a_me != 0.f), any_ot = __any_sync(kFullMask, a_ot != 0.f);
+    __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st + e * kOHalf;
 #pragma unroll
-      for (int c = 0; c < kOHalf / 32; ++c) {
-        uint32_t y[32];
-        tmem_ld32(t_o + lane_addr + half * kOHalf + c * 32, y);
-        tc_wait_ld();
-        if (t < p.T) {
+    for (int c = 0; c < kOHalf / 32; ++c) {
+      uint32_t y0[32], y1[32];
+      // (a group without tiles never wrote its accumulator: its columns are not read, let alone used)
+      if (any_me) tmem_ld32(t_o[e] + lane_addr + e * kOHalf + c * 32, y0);
+      if (any_ot) tmem_ld32(t_o[e ^ 1] + lane_addr + e * kOHalf + c * 32, y1);
+      tc_wait_ld();
+      if (ok && t < p.T) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            *reinterpret_cast<uint32_t*>(orow + c * 32 + i) =
-                pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
+        for (int i = 0; i < 32; i += 2) {
+          float v0 = 0.f, v1 = 0.f;
+          if (a_me != 0.f) {
+            v0 = __uint_as_float(y0[i]) * a_me;
+            v1 = __uint_as_float(y0[i + 1]) * a_me;
+          }
+          if (a_ot != 0.f) {
+            v0 = fmaf(__uint_as_float(y1[i]), a_ot, v0);
+            v1 = fmaf(__uint_as_float(y1[i + 1]), a_ot, v1);
+          }
+          *reinterpret_cast<uint32_t*>(orow + c * 32 + i) = pack_bf16x2(v0 * inv, v1 * inv);
         }
       }
     }
@@ -378,7 +390,7 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   const long long ctas = (long long)B * Hq * p.m_blocks;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", ctas);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 14 * 8 + 6 * kTcRows * 4 + 16;
+  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 15 * 8 + 4 * kTcRows * 4 + 16;
   static bool configured[2][64] = {{false}};
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
