@@ -55,16 +55,17 @@ L3CI_HD constexpr int fd_cta_of(int col, int total, int ctas) {
 // Whole-unit cut.  When sequences are short, cutting them across CTAs buys little streaming time and costs a
 // cross-CTA merge (several dependent memory round trips).  The alternative gives every CTA whole
 // (sequence, head group) units: units u of CTA c are [c * units / ctas, (c + 1) * units / ctas), ctas =
-// min(grid, units).  The choice compares rough costs in units of ~0.16 us: a column costs a busy device about
-// 10 and a part-filled device about 7, the merge tail about 30.  It depends on launch-wide numbers only, so
-// every CTA decides alike.  (Measured on B200: a lone CTA walks a column in about 1 us, a full device
-// needs about 1.6 us per column and CTA, the merge tail is 4-5 us.)
+// min(grid, units).  The choice compares rough costs in units of ~0.16 us: a column costs a CTA of a busy device
+// about 9 and of a part-filled device about 6, the merge tail about 38.  It depends on launch-wide numbers only,
+// so every CTA decides alike.  (Measured on B200 with 64 sequences, 8 KV heads of 64: whole units take
+// 6.3 us + 0.9 us per column of a unit, the cut 12.3 us + 1.45 us per column of a CTA; they cross near 700
+// tokens.)
 L3CI_HD constexpr bool fd_whole_units(int total, int units, int grid) {
   if (units <= 0 || total <= 0) return false;
   const int ga = grid < units ? grid : units;
   const int gs = grid < total ? grid : total;
-  const long long whole = (long long)((units + ga - 1) / ga) * ((total + units - 1) / units) * 7;
-  const long long split = (long long)((total + gs - 1) / gs) * 10 + 30;
+  const long long whole = (long long)((units + ga - 1) / ga) * ((total + units - 1) / units) * 6;
+  const long long split = (long long)((total + gs - 1) / gs) * 9 + 38;
   return whole < split;
 }
 
