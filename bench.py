@@ -333,7 +333,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     def step(i):
         j = i % n_rot
         if sharded_seq and xchg is not None:
-            return pkg.sharding.decode_kv_sharded_fused(ext, q, ks[j], vs[j], xchg)
+            return pkg.sharding.decode_kv_sharded_fused(ext, q, ks[j], vs[j], xchg, device_epoch=True)
         if sharded_seq:
             return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
         return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
@@ -341,9 +341,10 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     # The launches of the rotating caches are captured back to back in one CUDA graph: the timed loop then
     # costs the host one graph launch per n_rot steps instead of the extension's argument checks and
     # tensor-map encoding per step, which take as long as a short kernel.  (The fused exchange numbers its
-    # calls on the host and stays eager.)
-    use_graph = not args.no_graph and not sharded_seq
-    run_steps = graph_runner(step, n_rot, dev) if use_graph else eager_runner(step)
+    # calls on the device, so its two launches per step are captured too; the NCCL variant stays eager.)
+    use_graph = not args.no_graph and (not sharded_seq or xchg is not None)
+    n_graph = max(n_rot, 8)  # launches per graph: a graph launch costs the host about as much as an eager call
+    run_steps = graph_runner(step, n_graph, dev) if use_graph else eager_runner(step)
     run_steps.prepare(args.warmup)
     run_steps.prepare(args.steps)
 
@@ -396,10 +397,11 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         try:
             sd_step = lambda i: F.scaled_dot_product_attention(q, ks[i % n_rot], vs[i % n_rot], attn_mask=mask,  # noqa: E731
                                                                enable_gqa=True)
-            sd_run = graph_runner(sd_step, n_rot, dev) if use_graph else eager_runner(sd_step)
+            sd_run = graph_runner(sd_step, n_graph, dev) if use_graph else eager_runner(sd_step)
             n_sd = max(n_rot, min(args.steps, 200))
             sd_run.prepare(n_sd)
-            sd_run(n_rot)
+            sd_run.prepare(n_graph)
+            sd_run(n_graph)
             torch.cuda.synchronize()
             start.record()
             sd_run(n_sd)
@@ -435,7 +437,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         dk, dv = dk_cache.transpose(1, 2), dv_cache.transpose(1, 2)
         dl = hl.to(dev, non_blocking=True) if hl is not None else None
         if sharded_seq and xchg is not None:
-            o = pkg.sharding.decode_kv_sharded_fused(ext, dq, dk, dv, xchg)
+            o = pkg.sharding.decode_kv_sharded_fused(ext, dq, dk, dv, xchg, device_epoch=True)
         elif sharded_seq:
             o = pkg.sharding.decode_kv_sharded(ext, dq, dk, dv, None)
         else:
@@ -472,7 +474,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         "scaling": "strong" if sharded_seq else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
                    "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
-                   "launch": f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back" if use_graph
+                   "launch": f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
                              else "each step is an eager extension call",
                    "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
                                                                   "fused NVLink exchange/merge kernel")) if sharded_seq else

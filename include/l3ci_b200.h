@@ -253,13 +253,18 @@ L3CI_API int l3ci_lse_merge(const float* o, const float* lse, void* out,
  * Every rank owns a buffer of l3ci_lse_exchange_bytes(ranks, B, Hq, D) bytes, zero-filled once, that
  * all ranks of the box can address (CUDA IPC / torch symmetric memory); `bufs` is a DEVICE array of
  * `ranks` base pointers as seen from this process, bufs[rank] being the local one.  Layout (fp32):
- *   data  [2][ranks][B*Hq*D outputs, then B*Hq lse padded to a multiple of 4 floats]
- *   flags [2][ranks][B*Hq] (uint32, after the data)
+ *   data    [2][ranks][B*Hq*D outputs, then B*Hq lse padded to a multiple of 4 floats]
+ *   flags   [2][ranks][B*Hq] (uint32, after the data, padded to a multiple of 4 words)
+ *   staging one more slot of the data layout
+ *   control 4 words: call number, finished warps, 2 unused
  * A call with epoch e (1, 2, 3, ... the same on all ranks) uses parity e & 1.  Before the call the
  * rank's own shard result must be in ITS OWN slot [e & 1][rank] (l3ci_flash_decode with o_partial /
- * lse pointing there).  The kernel waits at most one second for the peers' rows; if that runs out it
- * writes L3CI_ERR_DEVICE_WAIT to *status (optional device word) and leaves `out` unwritten for
- * those rows.  Every rank must call it, on its own GPU, once per epoch.
+ * lse pointing there).  With epoch 0 the call number is kept on the device instead (control word 0
+ * + 1, advanced by the kernel itself) and the rank's own result is expected in the staging slot, a
+ * fixed address: such a call has no host-side state and can be captured in a CUDA graph; use one of
+ * the two forms per buffer, not both.  The kernel waits at most one second for the peers' rows; if
+ * that runs out it writes L3CI_ERR_DEVICE_WAIT to *status (optional device word) and leaves `out`
+ * unwritten for those rows.  Every rank must call it, on its own GPU, once per epoch.
  * ------------------------------------------------------------------------------------------ */
 L3CI_API size_t l3ci_lse_exchange_bytes(int32_t ranks, int32_t B, int32_t Hq, int32_t D);
 L3CI_API int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t ranks, uint32_t epoch,

@@ -60,6 +60,12 @@ lse_merge_kernel(const float* __restrict__ o, const float* __restrict__ lse, __n
 //   4. merges the W rows by log-sum-exp from LOCAL memory and writes bf16.
 // Two parities make the slots safe to reuse: a rank can only start call e + 2 after its call e + 1 finished,
 // which needed every peer's call-(e+1) rows, which a peer sends only after its own call e has finished reading.
+//
+// The call number can live on the device (epoch argument 0): behind the flags every buffer has a staging slot and
+// two control words.  The rank's own result is then expected in the staging slot (a fixed address, whatever the
+// call number), the call number is control word 0 plus one, and the last warp of the launch to finish stores it
+// back (control word 1 counts the finished warps).  A launch sequence without any host-side state can be
+// captured in a CUDA graph and replayed.
 // ---------------------------------------------------------------------------------------------
 constexpr unsigned long long kXchgWaitNs = 1000000000ull;  // bound of the wait for the peers' rows
 
@@ -78,21 +84,36 @@ __device__ __forceinline__ unsigned long long xchg_ns() {
 }
 
 __global__ void __launch_bounds__(kMergeBlock)
-lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsigned epoch, long long rows, int Hq,
+lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsigned epoch_arg, long long rows, int Hq,
                           int D, __nv_bfloat16* __restrict__ out, long long o_sb, long long o_sh, int* status) {
   const long long row = (long long)blockIdx.x * (kMergeBlock / kWarp) + threadIdx.x / kWarp;
   const int lane = threadIdx.x % kWarp;
   if (row >= rows) return;
-  const int parity = epoch & 1u;
   const long long slot_floats = rows * D + ((rows + 3) & ~3LL);
   const long long data_floats = 2LL * W * slot_floats;
+  const long long flag_words = (2LL * W * rows + 3) & ~3LL;
+  float* local = bufs[rank];
+  float* staging = local + data_floats + flag_words;
+  unsigned* ctrl = reinterpret_cast<unsigned*>(staging + slot_floats);
+  const bool auto_epoch = epoch_arg == 0u;
+  // every warp of the launch reads the call number before the last of them to finish can advance it
+  const unsigned epoch = auto_epoch ? __ldcg(ctrl) + 1u : epoch_arg;
+  auto leave = [&]() {
+    if (auto_epoch && lane == 0) {
+      if (atomicAdd(ctrl + 1, 1u) == (unsigned)rows - 1u) {
+        ctrl[1] = 0u;
+        __threadfence();
+        ctrl[0] = epoch;
+      }
+    }
+  };
+  const int parity = epoch & 1u;
   auto slot = [&](float* base, int src) { return base + ((long long)parity * W + src) * slot_floats; };
   auto flag = [&](float* base, int src) {
     return reinterpret_cast<unsigned*>(base + data_floats) + ((long long)parity * W + src) * rows + row;
   };
-  float* local = bufs[rank];
   // 1. push this rank's row to every peer
-  const float* mine = slot(local, rank);
+  const float* mine = auto_epoch ? staging : slot(local, rank);
   const float my_lse = mine[rows * D + row];
   for (int p = 0; p < W; ++p) {
     if (p == rank) continue;
@@ -121,15 +142,17 @@ lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsi
     }
     if (late) {
       if (lane == 0 && status) atomicExch(status, (int)L3CI_ERR_DEVICE_WAIT);
+      leave();
       return;
     }
   }
   // 4. merge from local memory
+  auto src = [&](int s) { return s == rank ? mine : slot(local, s); };
   float M = -INFINITY;
-  for (int s = 0; s < W; ++s) M = fmaxf(M, __ldcg(slot(local, s) + rows * D + row));
+  for (int s = 0; s < W; ++s) M = fmaxf(M, __ldcg(src(s) + rows * D + row));
   const float Mu = M == -INFINITY ? 0.f : M;
   float L = 0.f;
-  for (int s = 0; s < W; ++s) L += __expf(__ldcg(slot(local, s) + rows * D + row) - Mu);
+  for (int s = 0; s < W; ++s) L += __expf(__ldcg(src(s) + rows * D + row) - Mu);
   const float invL = L > 0.f ? 1.f / L : 0.f;
   const long long b = row / Hq;
   const int h = (int)(row % Hq);
@@ -137,7 +160,7 @@ lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsi
   for (int d = lane * 2; d < D; d += 2 * kWarp) {
     float ax = 0.f, ay = 0.f;
     for (int s = 0; s < W; ++s) {
-      const float* sl = slot(local, s);
+      const float* sl = src(s);
       const float w = __expf(__ldcg(sl + rows * D + row) - Mu) * invL;
       const float2 v = __ldcg(reinterpret_cast<const float2*>(sl + row * D + d));
       ax = fmaf(v.x, w, ax);
@@ -145,6 +168,7 @@ lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsi
     }
     *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16x2(ax, ay);
   }
+  leave();
 }
 
 }  // namespace
@@ -154,7 +178,9 @@ extern "C" size_t l3ci_lse_exchange_bytes(int32_t ranks, int32_t B, int32_t Hq, 
   if (ranks <= 0 || B <= 0 || Hq <= 0 || D <= 0) return 0;
   const size_t rows = (size_t)B * Hq;
   const size_t slot_floats = rows * D + ((rows + 3) & ~(size_t)3);
-  return 2 * (size_t)ranks * slot_floats * sizeof(float) + 2 * (size_t)ranks * rows * sizeof(unsigned);
+  const size_t flag_words = (2 * (size_t)ranks * rows + 3) & ~(size_t)3;
+  // data | flags | staging slot | control words (call number, finished warps) padded to 16 bytes
+  return (2 * (size_t)ranks * slot_floats + flag_words + slot_floats + 4) * sizeof(float);
 }
 
 extern "C" int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t ranks, uint32_t epoch, void* out,
@@ -163,8 +189,8 @@ extern "C" int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t 
   using namespace l3ci;
   clear_error();
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (ranks <= 0 || rank < 0 || rank >= ranks || B < 0 || Hq <= 0 || D <= 0 || epoch == 0)
-    return fail(L3CI_ERR_INVALID, "lse_exchange_merge: bad size, rank or epoch (epochs start at 1)");
+  if (ranks <= 0 || rank < 0 || rank >= ranks || B < 0 || Hq <= 0 || D <= 0)
+    return fail(L3CI_ERR_INVALID, "lse_exchange_merge: bad size or rank");
   if (B == 0) return L3CI_OK;
   if (!bufs || !out) return fail(L3CI_ERR_INVALID, "lse_exchange_merge: null pointer");
   if (D % 4) return fail(L3CI_ERR_UNSUPPORTED, "lse_exchange_merge: head size %d is not a multiple of 4", D);

@@ -111,6 +111,8 @@ class KvShardExchange:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.rows = B * Hq
         self.slot_floats = self.rows * D + ((self.rows + 3) & ~3)
+        # behind the data and the flags: a staging slot for this rank's own result, then the control words
+        self.staging_base = 2 * self.world * self.slot_floats + ((2 * self.world * self.rows + 3) & ~3)
         self.epoch = 0
         torch.cuda.synchronize(device)
         self.handle.barrier()          # every rank's buffer is zeroed before anyone may push into it
@@ -123,6 +125,20 @@ class KvShardExchange:
         lse = self.buf[base + self.rows * self.D: base + self.rows * self.D + self.rows].view(self.B, self.Hq)
         return o, lse
 
+    def staging(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(o [B,Hq,D], lse [B,Hq]) views of the staging slot: where this rank's shard result goes when the call
+        number is kept on the device (`merge_auto`).  The address never changes, so a decode step that writes
+        there and calls `merge_auto` can be captured in a CUDA graph."""
+        base = self.staging_base
+        o = self.buf[base: base + self.rows * self.D].view(self.B, self.Hq, self.D)
+        lse = self.buf[base + self.rows * self.D: base + self.rows * self.D + self.rows].view(self.B, self.Hq)
+        return o, lse
+
+    def merge_auto(self) -> torch.Tensor:
+        """`merge` with the call number kept in the buffer itself (no host state); use either this or
+        `slot()` / `merge()` on an instance, not both."""
+        return self.ext.lse_exchange_merge(self.bufs, self.rank, 0, self.B, self.Hq, self.D, status=self.status)
+
     def merge(self) -> torch.Tensor:
         """Pushes this rank's slot to the peers, waits for theirs, merges: bf16 [B,Hq,1,D] on every rank."""
         return self.ext.lse_exchange_merge(self.bufs, self.rank, self.epoch, self.B, self.Hq, self.D,
@@ -134,9 +150,12 @@ class KvShardExchange:
 
 
 def decode_kv_sharded_fused(ext, q: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
-                            xchg: KvShardExchange, seq_lens_local: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            xchg: KvShardExchange, seq_lens_local: Optional[torch.Tensor] = None,
+                            device_epoch: bool = False) -> torch.Tensor:
     """`decode_kv_sharded` with the exchange and the merge in one kernel over peer memory: two launches per step
-    (shard attention into the exchange slot, then push + wait + merge) and no collective call."""
-    o, lse = xchg.slot()
+    (shard attention into the exchange buffer, then push + wait + merge) and no collective call.  With
+    `device_epoch` the step keeps no host state (fixed addresses, call number in the buffer) and can be captured
+    in a CUDA graph."""
+    o, lse = xchg.staging() if device_epoch else xchg.slot()
     ext.flash_attention_decode_partial(q, k_local, v_local, seq_lens=seq_lens_local, out_o=o, out_lse=lse)
-    return xchg.merge()
+    return xchg.merge_auto() if device_epoch else xchg.merge()

@@ -49,6 +49,35 @@ def _rank_main(rank, world, port, q):
             torch.cuda.synchronize()
             compare.assert_close_attention(got, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
         assert xchg.check() == 0
+        # --- the call number kept on the device: no host state, so the two launches of a step can be captured in
+        #     a CUDA graph; eager steps first (both parities), then replays of one captured step on new inputs
+        xa = pkg.sharding.KvShardExchange(ext, 2, 32, 128, dev)
+        for step in range(3):
+            c = inputs.decode_case(2, 32, 8, 128, 6000, seed=80 + step, ragged=True, min_len=100)
+            d = c.to(dev)
+            ll = pkg.sharding.local_seq_lens(d.seq_lens, lo, hi)
+            got = pkg.sharding.decode_kv_sharded_fused(ext, d.q, d.k[:, :, lo:hi], d.v[:, :, lo:hi], xa, ll, device_epoch=True)
+            torch.cuda.synchronize()
+            compare.assert_close_attention(got, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
+        c0 = inputs.decode_case(2, 32, 8, 128, 6000, seed=90, ragged=True, min_len=100)
+        sq, sk, sv = c0.q.to(dev), c0.k[:, :, lo:hi].to(dev).contiguous(), c0.v[:, :, lo:hi].to(dev).contiguous()
+        sl = pkg.sharding.local_seq_lens(c0.seq_lens.to(dev), lo, hi)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            pkg.sharding.decode_kv_sharded_fused(ext, sq, sk, sv, xa, sl, device_epoch=True)   # workspace of this stream
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                gout = pkg.sharding.decode_kv_sharded_fused(ext, sq, sk, sv, xa, sl, device_epoch=True)
+            for step in range(3):
+                c = inputs.decode_case(2, 32, 8, 128, 6000, seed=91 + step, ragged=True, min_len=100)
+                sq.copy_(c.q.to(dev)); sk.copy_(c.k[:, :, lo:hi].to(dev)); sv.copy_(c.v[:, :, lo:hi].to(dev))
+                sl.copy_(pkg.sharding.local_seq_lens(c.seq_lens.to(dev), lo, hi))
+                graph.replay()
+                torch.cuda.synchronize()
+                compare.assert_close_attention(gout, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
+        torch.cuda.current_stream(dev).wait_stream(side)
+        assert xa.check() == 0
         # --- batch sharded by sequence: every rank computes its own sequences, nothing is exchanged
         batch = inputs.config2(seed=62)
         mine = pkg.sharding.partition_batch(batch.seq_lens.tolist(), world)[rank]
