@@ -160,7 +160,10 @@ typedef struct l3ci_flash_decode_args {
   int64_t v_sb, v_sh, v_st;
   int64_t o_sb, o_sh;
   float scale;           /* softmax scale; <= 0 selects 1/sqrt(D) (custom_kernels.cu:253)      */
-  int32_t max_ctas;      /* 0 = fill the device; >0 caps the persistent grid (tests, tuning)   */
+  int32_t max_ctas;      /* 0 = library's choice: the persistent grid fills the device; short    *
+                          * caches (at most 32 B*Hkv units of at most 32 tiles, Hq/Hkv <= 8) run *
+                          * one CTA per unit instead.  >0 = persistent grid capped at this size;   *
+                          * <0 = the one-CTA-per-unit kernel at any size with Hq/Hkv <= 8.        */
   l3ci_stream_t stream;
 } l3ci_flash_decode_args;
 

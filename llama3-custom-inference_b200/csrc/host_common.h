@@ -20,6 +20,11 @@ int sm_count();
 // Largest opt-in dynamic shared memory per block of the current device (cached).
 int max_smem_optin();
 
+// Decode attention for short caches (flash_decode_small.cu): whether l3ci_flash_decode hands a call of these
+// sizes to it, and its launch (arguments already validated by the caller).
+bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq);
+int flash_decode_small_launch(const l3ci_flash_decode_args* a);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 #define L3CI_CUDA_TRY(expr)                                                              \

@@ -51,21 +51,36 @@ def test_config3_long_context(capi, device):
 
 # ---- shapes: head sizes, group ratios, lengths around the tile sizes -------------------------------
 
+# Short caches take the one-CTA-per-unit kernel unless max_ctas asks for the persistent grid: both are checked.
+KERNELS = pytest.mark.parametrize("max_ctas", [0, 148], ids=["auto", "persistent"])
 HEADS = [(4, 4), (4, 2), (6, 2), (32, 8), (8, 1), (12, 1), (16, 1), (24, 3), (32, 32), (10, 5)]
 LENGTHS = [1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 255, 300, 1000]
 
 
+@KERNELS
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("Hq,Hkv", HEADS)
-def test_head_configurations(capi, device, D, Hq, Hkv):
+def test_head_configurations(capi, device, D, Hq, Hkv, max_ctas):
     for i, S in enumerate([1, 33, 300]):
-        _check(capi, inputs.decode_case(2, Hq, Hkv, D, S, seed=100 + i), device)
+        _check(capi, inputs.decode_case(2, Hq, Hkv, D, S, seed=100 + i), device, max_ctas=max_ctas)
+
+
+@KERNELS
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("S", LENGTHS)
+def test_lengths_around_tile_boundaries(capi, device, D, S, max_ctas):
+    _check(capi, inputs.decode_case(3, 8, 2, D, S, seed=S), device, max_ctas=max_ctas)
 
 
 @pytest.mark.parametrize("D", [64, 128])
-@pytest.mark.parametrize("S", LENGTHS)
-def test_lengths_around_tile_boundaries(capi, device, D, S):
-    _check(capi, inputs.decode_case(3, 8, 2, D, S, seed=S), device)
+def test_short_cache_kernel_agrees_with_the_persistent_one(capi, device, D):
+    # largest sizes the short-cache kernel takes: 32 units of 32 tiles would exceed its tile budget, so 16 units
+    S = 32 * (16 if D == 128 else 32)
+    for B, Hq, Hkv in ((1, 32, 8), (2, 64, 8), (4, 16, 4), (16, 8, 1)):
+        case = inputs.decode_case(B, Hq, Hkv, D, S, seed=60 + B, ragged=True, min_len=1)
+        a = _check(capi, case, device, max_ctas=0).float()
+        b = _run(capi, case, device, max_ctas=148).float()
+        assert (a - b).abs().max().item() <= 2e-2
 
 
 @pytest.mark.parametrize("name,shape", [("d128_r4_s300", (2, 8, 2, 128, 300, 7)), ("d64_r1_s65", (2, 4, 4, 64, 65, 8)),
@@ -84,11 +99,12 @@ def test_uniform01_inputs_as_the_reference_benchmark_draws_them(capi, device, go
 
 # ---- ragged batches ---------------------------------------------------------------------------------
 
+@KERNELS
 @pytest.mark.parametrize("D", [64, 128])
-def test_ragged_lengths_including_empty_and_full(capi, device, D):
-    case = inputs.decode_case(9, 16, 4, D, 200, seed=11, ragged=True)
+def test_ragged_lengths_including_empty_and_full(capi, device, D, max_ctas):
+    case = inputs.decode_case(9, 12, 3, D, 200, seed=11, ragged=True)
     case.seq_lens[:] = torch.tensor([0, 1, 200, 16, 17, 199, 32, 33, 150], dtype=torch.int32)
-    out = _check(capi, case, device)
+    out = _check(capi, case, device, max_ctas=max_ctas)
     assert out[0].abs().max().item() == 0  # a sequence without cached tokens yields zeros
 
 
