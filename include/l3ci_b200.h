@@ -160,10 +160,13 @@ typedef struct l3ci_flash_decode_args {
   int64_t v_sb, v_sh, v_st;
   int64_t o_sb, o_sh;
   float scale;           /* softmax scale; <= 0 selects 1/sqrt(D) (custom_kernels.cu:253)      */
-  int32_t max_ctas;      /* 0 = library's choice: the persistent grid fills the device; short    *
-                          * caches (at most 32 B*Hkv units of at most 32 tiles, Hq/Hkv <= 8) run *
-                          * one CTA per unit instead.  >0 = persistent grid capped at this size;   *
-                          * <0 = the one-CTA-per-unit kernel at any size with Hq/Hkv <= 8.        */
+  int32_t max_ctas;      /* 0 = library's choice between its two kernels: a persistent grid that  *
+                          * fills the device and balances any mix of lengths, and one that deals  *
+                          * units statically to warps, CTAs or clusters and merges in shared      *
+                          * memory (Hq/Hkv <= 8; faster up to a few MB of cache per CTA).          *
+                          * >0 = the persistent grid, capped at this size.  -1 = the static kernel *
+                          * with its own split; -(16*C + W) = with C CTAs per unit (1, 2, 4, 8) and *
+                          * W of a CTA's 8 warps per unit (1, 2, 4, 8; 8 if C > 1): tests, tuning.  */
   l3ci_stream_t stream;
 } l3ci_flash_decode_args;
 

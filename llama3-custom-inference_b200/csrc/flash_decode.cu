@@ -951,10 +951,11 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
     return fail(L3CI_ERR_SCRATCH, "flash_decode: scratch has %zu bytes, needs %zu", a->scratch_bytes, need);
   if (reinterpret_cast<uintptr_t>(a->scratch) & 255) return fail(L3CI_ERR_ALIGNMENT, "flash_decode: scratch must be 256-byte aligned");
 
-  // Short caches: one CTA per (sequence, KV head), nothing crosses a CTA (flash_decode_small.cu).  The scratch
-  // stays untouched.  An explicit max_ctas asks for the persistent kernel.
-  if ((a->max_ctas == 0 && flash_decode_small_applies(B, Hq, Hkv, D, n_seq)) || (a->max_ctas < 0 && R <= 8))
-    return flash_decode_small_launch(a);
+  // Where the static deal of units to warps, CTAs or clusters is expected to be faster (flash_decode_small.cu),
+  // nothing goes through global memory and the scratch stays untouched.  A positive max_ctas asks for the
+  // persistent kernel.
+  if ((a->max_ctas == 0 && flash_decode_small_applies(B, Hq, Hkv, D, n_seq, ragged)) || (a->max_ctas < 0 && R <= 8))
+    return flash_decode_small_launch(a, a->max_ctas < -1 ? -a->max_ctas : 0);
 
   const size_t smem = smem_bytes(HG, B, ragged);
   if ((long long)smem > max_smem_optin()) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: needs %zu bytes of shared memory", smem);
@@ -1039,7 +1040,7 @@ extern "C" int l3ci_flash_decode_static(const l3ci_flash_decode_args* a) {
   // the status word and the arrival counters of this call's units must start at zero.
   // (The kernel for short caches uses no scratch.)
   const bool small = a->max_ctas == 0 && a->n_seq > 0 && (a->D == 64 || a->D == 128) &&
-                     flash_decode_small_applies(a->B, a->Hq, a->Hkv, a->D, a->n_seq);
+                     flash_decode_small_applies(a->B, a->Hq, a->Hkv, a->D, a->n_seq, a->seq_lens != nullptr);
   const size_t clear = kHeaderBytes + (((size_t)a->B * a->Hkv * sizeof(int) + 255) & ~(size_t)255);
   if (!small) L3CI_CUDA_TRY(cudaMemsetAsync(area, 0, clear, reinterpret_cast<cudaStream_t>(a->stream)));
   l3ci_flash_decode_args b = *a;

@@ -1,14 +1,17 @@
-// Decode attention for small problems: one CTA per (sequence, KV head), the cached tokens dealt to its eight
-// warps, partial results merged through shared memory.
+// Decode attention without a pass through global memory: the partial results of one unit (a sequence's KV head)
+// meet in shared memory.
 //
-// The persistent kernel of flash_decode.cu pays fixed latencies per launch (tensor-map fetch, cross-CTA merge
-// through global memory) of 7-8 us, which is all there is to a call like the reference's own example (one
-// sequence of 256 tokens, benchmark_kernel.py:160-163: 0.5 MB of K and V).  Here nothing crosses a CTA: K and V
-// rows go from global to shared memory with 16-byte asynchronous copies (written in the 128-byte-swizzled layout
-// that ldmatrix expects), the tile arithmetic is the one of the large kernel (S^T = K Q^T and O^T = V^T P^T on
-// mma.sync.m16n8k16, tokens on the rows of a tile, the group's query heads on its 8 columns), and the eight
-// (m, l, o) states of a CTA meet in shared memory.  Taken by l3ci_flash_decode for short caches with at most 8
-// query heads per KV head; results are the same within rounding.
+// The persistent kernel of flash_decode.cu balances any mix of lengths over the whole device, and pays for it
+// with fixed latencies per launch (tensor-map fetch, cross-CTA merge through global memory) of about 10 us.  That
+// is most of a call like the reference's own example (one sequence of 256 tokens, benchmark_kernel.py:160-163:
+// 0.5 MB of K and V) and a third of a batched decode step of a few thousand tokens per sequence.  Here a unit is
+// dealt statically: to W of a CTA's eight warps (8 / W units per CTA, for many short units), to the eight warps
+// of one CTA, or to the C CTAs of a thread-block cluster (for few long units), whose per-CTA results meet through
+// distributed shared memory.  K and V rows go from global to shared memory with 16-byte asynchronous copies
+// (written in the 128-byte-swizzled layout that ldmatrix expects), three tiles in flight per warp; the tile
+// arithmetic is the one of the persistent kernel (S^T = K Q^T and O^T = V^T P^T on mma.sync.m16n8k16, tokens on
+// the rows of a tile, the group's query heads on its 8 columns).  Taken by l3ci_flash_decode where the cost model
+// below expects it to be faster, for at most 8 query heads per KV head; results agree within rounding.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -32,6 +35,7 @@ struct SmallParams {
   float* lse;
   const int* seq_lens;
   int B, Hq, Hkv, R, n_seq;
+  int lgW, lgC;  // log2 of: warps per unit (1, 2, 4, 8), CTAs per unit (a cluster; > 1 only with 8 warps per unit)
   long long q_sb, q_sh, k_sb, k_sh, k_st, v_sb, v_sh, v_st, o_sb, o_sh;
   float scale_log2e;
 };
@@ -43,8 +47,28 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster: shared-memory writes before it are visible to the cluster after it.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Reads a float at this CTA's shared address `addr`, but in the shared memory of CTA `cta` of the cluster.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t cta) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(cta));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 
-template <int D>
+// kCluster: launched as clusters of CTAs per unit (the instances without hold no cluster instruction and are
+// launched the plain way, which starts sooner).  kWholeCta: all eight warps on one unit, known at compile time
+// (the merge loops then unroll without predicates: 0.5 us on a call of a few microseconds).
+template <int D, bool kCluster, bool kWholeCta>
 __global__ void __launch_bounds__(32 * kSmWarps)
 flash_decode_small_kernel(const SmallParams p) {
   constexpr int kTile = fd_tile_tokens(D);   // tokens per tile: 4 KB of K and 4 KB of V
@@ -58,13 +82,24 @@ flash_decode_small_kernel(const SmallParams p) {
   float* states = reinterpret_cast<float*>(smem);  // [kSmWarps][kStateFloats], over the tile slots once all warps are done
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
-  const int b = blockIdx.x / p.Hkv, head = blockIdx.x % p.Hkv;
-  const int R = p.R;
-  const int len = p.seq_lens ? min(max(__ldg(p.seq_lens + b), 0), p.n_seq) : p.n_seq;
+  // (shifts, not divisions: they sit on the path to the first copy)
+  const int R = p.R, lgW = kWholeCta ? 3 : p.lgW, lgC = kCluster ? p.lgC : 0;
+  const int W = 1 << lgW, C = 1 << lgC;
+  const int U = kSmWarps >> lgW;                    // units per CTA
+  uint32_t cta_rank = 0;
+  if constexpr (kCluster) cta_rank = cluster_cta_rank();
+  const int n_units = p.B * p.Hkv;
+  const int unit0 = (int)(blockIdx.x >> lgC) * U;   // first unit of this CTA (of this cluster)
+  const int unit = unit0 + (warp >> lgW);
+  const bool has_unit = unit < n_units;
+  const int b = has_unit ? unit / p.Hkv : 0, head = has_unit ? unit % p.Hkv : 0;
+  const int len = !has_unit ? 0 : p.seq_lens ? min(max(__ldg(p.seq_lens + b), 0), p.n_seq) : p.n_seq;
 
-  // this warp's tiles: tiles are dealt in contiguous runs
+  // this warp's tiles: the unit's tiles are dealt in contiguous runs to its C * W warps
   const int n_tiles = (len + kTile - 1) / kTile;
-  const int t_begin = (int)((long long)warp * n_tiles / kSmWarps), t_end = (int)((long long)(warp + 1) * n_tiles / kSmWarps);
+  const int part = (int)cta_rank * W + (warp & (W - 1)), parts = C * W;
+  const int t_each = n_tiles >> (lgW + lgC), t_more = n_tiles - t_each * parts;  // the first t_more parts get one more
+  const int t_begin = part * t_each + min(part, t_more), t_end = t_begin + t_each + (part < t_more ? 1 : 0);
   const __nv_bfloat16* kbase = p.k + (long long)b * p.k_sb + (long long)head * p.k_sh;
   const __nv_bfloat16* vbase = p.v + (long long)b * p.v_sb + (long long)head * p.v_sh;
   const uint32_t buf0 = smem_u32(smem) + warp * kSmSlots * kTileBytes;
@@ -210,19 +245,74 @@ flash_decode_small_kernel(const SmallParams p) {
   }
   __syncthreads();
 
-  // ---- merge of the eight states: one thread per output element ----
-  for (int e = threadIdx.x; e < R * D; e += 32 * kSmWarps) {
-    const int row = e / D, col = e - row * D;
+  // ---- first level: the W states of each of this CTA's units.  Every thread folds them for its output elements
+  //      (weights recomputed per element: a table built by a few threads first was slower by 0.5 us) ----
+  float* cstate = states + kSmWarps * kStateFloats;  // [R * D] unnormalised sums, then m[8], l[8] (used with C > 1)
+  const int RD = R * D;
+  for (int u = 0; u < U; ++u) {
+    const bool live = unit0 + u < n_units;
+    const int ub = live ? (unit0 + u) / p.Hkv : 0, uh = live ? (unit0 + u) - ub * p.Hkv : 0;
+    const float* s0 = states + (u * W) * kStateFloats;
+    for (int r = threadIdx.x; r < RD && live; r += 32 * kSmWarps) {
+      const int row = r / D, col = r - row * D;
+      float m_w[kSmWarps];
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kSmWarps; ++w) {
+        m_w[w] = w < W ? s0[w * kStateFloats + 8 * D + row] : -INFINITY;
+        M = fmaxf(M, m_w[w]);
+      }
+      const float Mu = M == -INFINITY ? 0.f : M;
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSmWarps; ++w)
+        if (w < W) {
+          const float wgt = fast_exp2(m_w[w] - Mu);
+          L = fmaf(s0[w * kStateFloats + 8 * D + 8 + row], wgt, L);
+          acc = fmaf(s0[w * kStateFloats + row * D + col], wgt, acc);
+        }
+      if (kCluster) {
+        cstate[r] = acc;
+        if (col == 0) { cstate[8 * D + row] = M; cstate[8 * D + 8 + row] = L; }
+      } else {
+        const float val = L > 0.f ? acc / L : 0.f;
+        const long long hq = (long long)uh * R + row;
+        if (p.out) p.out[(long long)ub * p.o_sb + hq * p.o_sh + col] = __float2bfloat16(val);
+        if (p.o_partial) {
+          p.o_partial[((long long)ub * p.Hq + hq) * D + col] = val;
+          if (col == 0) p.lse[(long long)ub * p.Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+        }
+      }
+    }
+  }
+  if constexpr (!kCluster) return;
+
+  if constexpr (kCluster) {
+  // ---- second level: the C per-CTA states of the unit, read through distributed shared memory; this CTA
+  //      finishes its 1/C of the unit's output elements ----
+  cluster_sync();
+  const uint32_t cs = smem_u32(cstate);
+  const int share = RD >> lgC;  // D is a multiple of 64 and C at most 8
+  for (int r = (int)cta_rank * share + (int)threadIdx.x; r < ((int)cta_rank + 1) * share && has_unit; r += 32 * kSmWarps) {
+    const int row = r / D, col = r - row * D;
+    float m_c[8], l_c[8], a_c[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const bool on = c < C;
+      m_c[c] = on ? ld_cluster_f32(cs + (8 * D + row) * 4, c) : -INFINITY;
+      l_c[c] = on ? ld_cluster_f32(cs + (8 * D + 8 + row) * 4, c) : 0.f;
+      a_c[c] = on ? ld_cluster_f32(cs + r * 4, c) : 0.f;
+    }
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kSmWarps; ++w) M = fmaxf(M, states[w * kStateFloats + 8 * D + row]);
+    for (int c = 0; c < 8; ++c) M = fmaxf(M, m_c[c]);
     const float Mu = M == -INFINITY ? 0.f : M;
     float L = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSmWarps; ++w) {
-      const float wgt = fast_exp2(states[w * kStateFloats + 8 * D + row] - Mu);
-      L = fmaf(states[w * kStateFloats + 8 * D + 8 + row], wgt, L);
-      acc = fmaf(states[w * kStateFloats + row * D + col], wgt, acc);
+    for (int c = 0; c < 8; ++c) {
+      const float wgt = fast_exp2(m_c[c] - Mu);
+      L = fmaf(l_c[c], wgt, L);
+      acc = fmaf(a_c[c], wgt, acc);
     }
     const float val = L > 0.f ? acc / L : 0.f;
     const long long hq = (long long)head * R + row;
@@ -232,19 +322,137 @@ flash_decode_small_kernel(const SmallParams p) {
       if (col == 0) p.lse[(long long)b * p.Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
     }
   }
+  cluster_sync();  // no CTA leaves while a peer may still read its shared memory
+  }
 }
 
 }  // namespace
 
-// True when the call is one for the small kernel (decided from host-side sizes only).
-bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq) {
-  const int R = Hq / Hkv;
-  const long long tiles = (long long)(n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
-  return R <= 8 && tiles <= 4 * kSmWarps && (long long)B * Hkv <= 32 && (long long)B * Hkv * tiles <= 512;
+constexpr size_t kSmallSmemBytes = 1024 + (size_t)kSmWarps * kSmSlots * 8192;  // the merge states reuse the slots
+
+// Opt-in to the shared memory size, once per device and head size.
+int configure_small_kernel(int D) {
+  static bool configured[2][64] = {{false}};
+  int dev = 0;
+  L3CI_CUDA_TRY(cudaGetDevice(&dev));
+  const int di = D == 64 ? 0 : 1;
+  if (dev >= 0 && dev < 64 && configured[di][dev]) return L3CI_OK;
+  const int bytes = (int)kSmallSmemBytes;
+  if (D == 64) {
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  } else {
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  }
+  if (dev >= 0 && dev < 64) configured[di][dev] = true;
+  return L3CI_OK;
 }
 
-int flash_decode_small_launch(const l3ci_flash_decode_args* a) {
+// Clusters of C CTAs of this kernel that the current device runs at once (cached; 0 when the query fails).  The
+// SMs of a cluster lie in one GPC, so this is less than SMs / C.
+int max_active_clusters(int D, int C) {
+  static int cached[2][4][64];  // 0 = not asked yet, else answer + 1
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  const int di = D == 64 ? 0 : 1, ci = C == 2 ? 1 : C == 4 ? 2 : 3;
+  if (cached[di][ci][dev]) return cached[di][ci][dev] - 1;
+  int n = 0;
+  if (configure_small_kernel(D) == L3CI_OK) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(C * 64));
+    cfg.blockDim = dim3(32 * kSmWarps);
+    cfg.dynamicSmemBytes = kSmallSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = D == 64 ? cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<64, true, true>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<128, true, true>, &cfg);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+  }
+  cached[di][ci][dev] = n + 1;
+  return n;
+}
+
+// How a call is dealt to this kernel: W warps per unit, C CTAs per unit, and the resulting grid.
+struct UnitSplit {
+  int W, C, ctas;
+};
+
+// The split for `units` units of `tiles` tiles on `sms` SMs.  Few units of at least 32 tiles are spread over
+// clusters while every warp still gets a tile and all clusters run at once; more units than SMs share CTAs.
+// ctas == 0: no split keeps the grid within one wave.
+UnitSplit unit_split(long long units, long long tiles, int sms, int D) {
+  UnitSplit s{kSmWarps, 1, 0};
+  if (units <= 0) return s;
+  if (units <= sms) {
+    while (s.C < 8 && tiles >= 32 && tiles >= (long long)kSmWarps * s.C * 2 && units * s.C * 2 <= sms &&
+           units <= max_active_clusters(D, s.C * 2))
+      s.C *= 2;
+    s.ctas = (int)(units * s.C);
+    return s;
+  }
+  for (int U = 2; U <= kSmWarps; U *= 2)
+    if ((units + U - 1) / U <= sms) {
+      s.W = kSmWarps / U;
+      s.ctas = (int)((units + U - 1) / U);
+      return s;
+    }
+  return s;
+}
+
+// True when l3ci_flash_decode hands the call to this kernel, decided from host-side sizes only.  Measured on a
+// B200 against the persistent kernel over B = 1..64, 128..131072 tokens, both head sizes: this kernel starts in
+// 3.3 us instead of about 10 and an SM takes in up to 96 GB/s, so it is ahead (by up to 2x) wherever one wave
+// covers the units and a CTA's share stays within about 4 MB; past that both stream at the rate of the memory
+// and the persistent kernel, which balances, is level or ahead.  The lengths of a ragged batch are on the
+// device: one long sequence among short ones keeps a single CTA busy here, while the persistent kernel would
+// spread it.  With seq_lens the share that a CTA could get (from the cache length) is therefore held to 1.25 MB,
+// about 13 us: what the other kernel's start costs.
+bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged) {
+  if (Hq / Hkv > 8) return false;
+  const long long units = (long long)B * Hkv;
+  const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
+  const int sms = sm_count();
+  if (sms <= 0) return false;
+  const UnitSplit s = unit_split(units, tiles, sms, D);
+  if (s.ctas == 0) return false;
+  const double cta_bytes = (double)n_seq * 4.0 * D * (kSmWarps / s.W) / s.C;
+  return cta_bytes <= (ragged ? 1.25e6 : 4.5e6);
+}
+
+// split_code: 0 = unit_split's choice, else 16 * C + W (tuning).
+int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
+  const long long units = (long long)a->B * a->Hkv;
+  const long long tiles = ((long long)a->n_seq + fd_tile_tokens(a->D) - 1) / fd_tile_tokens(a->D);
+  if (int st = configure_small_kernel(a->D)) return st;
+  UnitSplit s = unit_split(units, tiles, sm_count(), a->D);
+  if (split_code > 0) {
+    s.C = split_code / 16;
+    s.W = split_code % 16;
+    const bool pow2 = (s.C & (s.C - 1)) == 0 && (s.W & (s.W - 1)) == 0;
+    if (!pow2 || s.C < 1 || s.C > 8 || s.W < 1 || s.W > kSmWarps || (s.C > 1 && s.W != kSmWarps))
+      return fail(L3CI_ERR_INVALID, "flash_decode: split code %d (16 * CTAs per unit + warps per unit)", split_code);
+    s.ctas = 0;
+  }
+  if (s.ctas == 0) {  // forced, or more units than one wave holds: several waves
+    const int U = kSmWarps / s.W;
+    const long long ctas = (units + U - 1) / U * s.C;
+    if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "flash_decode: too many units (%lld)", units);
+    s.ctas = (int)ctas;
+  }
   SmallParams p;
+  p.lgW = s.W == 8 ? 3 : s.W == 4 ? 2 : s.W == 2 ? 1 : 0;
+  p.lgC = s.C == 8 ? 3 : s.C == 4 ? 2 : s.C == 2 ? 1 : 0;
   p.q = static_cast<const __nv_bfloat16*>(a->q);
   p.k = static_cast<const __nv_bfloat16*>(a->k);
   p.v = static_cast<const __nv_bfloat16*>(a->v);
@@ -257,21 +465,35 @@ int flash_decode_small_launch(const l3ci_flash_decode_args* a) {
   p.v_sb = a->v_sb; p.v_sh = a->v_sh; p.v_st = a->v_st; p.o_sb = a->o_sb; p.o_sh = a->o_sh;
   const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2e = scale * 1.4426950408889634f;
-  const size_t smem = 1024 + (size_t)kSmWarps * kSmSlots * 8192;  // the merge states (33 KB at most) reuse the slots
+  const size_t smem = kSmallSmemBytes;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  static bool configured[2][64] = {{false}};
-  int dev = 0;
-  L3CI_CUDA_TRY(cudaGetDevice(&dev));
-  const int di = a->D == 64 ? 0 : 1;
-  if (dev < 0 || dev >= 64 || !configured[di][dev]) {
-    if (a->D == 64) L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    else L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev >= 0 && dev < 64) configured[di][dev] = true;
+  if (s.C == 1) {  // (the instance without cluster instructions, launched the plain way)
+    const unsigned grid = (unsigned)s.ctas, block = 32 * kSmWarps;
+    if (s.W == kSmWarps) {
+      if (a->D == 64) flash_decode_small_kernel<64, false, true><<<grid, block, smem, stream>>>(p);
+      else flash_decode_small_kernel<128, false, true><<<grid, block, smem, stream>>>(p);
+    } else {
+      if (a->D == 64) flash_decode_small_kernel<64, false, false><<<grid, block, smem, stream>>>(p);
+      else flash_decode_small_kernel<128, false, false><<<grid, block, smem, stream>>>(p);
+    }
+    L3CI_CHECK_LAUNCH("flash_decode_small_kernel");
+    return L3CI_OK;
   }
-  const unsigned grid = (unsigned)(a->B * a->Hkv);
-  if (a->D == 64) flash_decode_small_kernel<64><<<grid, 32 * kSmWarps, smem, stream>>>(p);
-  else flash_decode_small_kernel<128><<<grid, 32 * kSmWarps, smem, stream>>>(p);
-  L3CI_CHECK_LAUNCH("flash_decode_small_kernel");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)s.ctas);
+  cfg.blockDim = dim3(32 * kSmWarps);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)s.C;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true>, p)
+                                   : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true>, p);
+  if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));
   return L3CI_OK;
 }
 

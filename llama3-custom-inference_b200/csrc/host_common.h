@@ -20,10 +20,11 @@ int sm_count();
 // Largest opt-in dynamic shared memory per block of the current device (cached).
 int max_smem_optin();
 
-// Decode attention for short caches (flash_decode_small.cu): whether l3ci_flash_decode hands a call of these
-// sizes to it, and its launch (arguments already validated by the caller).
-bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq);
-int flash_decode_small_launch(const l3ci_flash_decode_args* a);
+// Decode attention with units dealt statically to warps, CTAs or clusters (flash_decode_small.cu): whether
+// l3ci_flash_decode hands a call of these sizes to it, and its launch (arguments already validated by the
+// caller; split_code 0 = its own choice, else 16 * CTAs per unit + warps per unit).
+bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged);
+int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

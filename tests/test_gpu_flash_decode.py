@@ -51,8 +51,9 @@ def test_config3_long_context(capi, device):
 
 # ---- shapes: head sizes, group ratios, lengths around the tile sizes -------------------------------
 
-# Short caches take the one-CTA-per-unit kernel unless max_ctas asks for the persistent grid: both are checked.
-KERNELS = pytest.mark.parametrize("max_ctas", [0, 148], ids=["auto", "persistent"])
+# max_ctas 0 lets the library choose between its two kernels; a positive value asks for the persistent grid,
+# -1 for the kernel that deals units statically to warps, CTAs or clusters (with its own choice of split).
+KERNELS = pytest.mark.parametrize("max_ctas", [0, 148, -1], ids=["auto", "persistent", "static"])
 HEADS = [(4, 4), (4, 2), (6, 2), (32, 8), (8, 1), (12, 1), (16, 1), (24, 3), (32, 32), (10, 5)]
 LENGTHS = [1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 255, 300, 1000]
 
@@ -72,15 +73,30 @@ def test_lengths_around_tile_boundaries(capi, device, D, S, max_ctas):
     _check(capi, inputs.decode_case(3, 8, 2, D, S, seed=S), device, max_ctas=max_ctas)
 
 
+# -(16 * C + W): C CTAs (a cluster) per unit, W of a CTA's 8 warps per unit
+SPLITS = {"w1": -17, "w2": -18, "w4": -20, "w8": -24, "c2": -40, "c4": -72, "c8": -136}
+
+
+@pytest.mark.parametrize("split", list(SPLITS))
 @pytest.mark.parametrize("D", [64, 128])
-def test_short_cache_kernel_agrees_with_the_persistent_one(capi, device, D):
-    # largest sizes the short-cache kernel takes: 32 units of 32 tiles would exceed its tile budget, so 16 units
-    S = 32 * (16 if D == 128 else 32)
-    for B, Hq, Hkv in ((1, 32, 8), (2, 64, 8), (4, 16, 4), (16, 8, 1)):
-        case = inputs.decode_case(B, Hq, Hkv, D, S, seed=60 + B, ragged=True, min_len=1)
-        a = _check(capi, case, device, max_ctas=0).float()
+def test_every_static_split_agrees_with_the_oracle(capi, device, D, split):
+    shapes = [(1, 32, 8, 700, False), (3, 9, 3, 333, True), (5, 8, 1, 40, True), (2, 16, 2, 2100, True), (11, 14, 7, 90, False)]
+    for i, (B, Hq, Hkv, S, ragged) in enumerate(shapes):   # 9, 5 and 77 units: partly filled CTAs for W < 8
+        case = inputs.decode_case(B, Hq, Hkv, D, S, seed=60 + i, ragged=ragged, min_len=0)
+        a = _check(capi, case, device, max_ctas=SPLITS[split]).float()
         b = _run(capi, case, device, max_ctas=148).float()
         assert (a - b).abs().max().item() <= 2e-2
+
+
+def test_static_kernel_refuses_a_malformed_split(capi, device):
+    case = inputs.decode_case(1, 8, 2, 64, 50, seed=3).to(device)
+    for code in (-(16 * 3 + 8), -(16 * 2 + 4), -(16 * 16 + 8), -(16 + 3)):
+        with pytest.raises(capi.L3ciError, match="split code"):
+            capi.flash_attention_decode(case.q, case.k, case.v, max_ctas=code)
+
+
+def test_more_than_eight_query_heads_per_kv_head_take_the_persistent_kernel(capi, device):
+    _check(capi, inputs.decode_case(2, 32, 2, 64, 100, seed=4), device, max_ctas=-1)
 
 
 @pytest.mark.parametrize("name,shape", [("d128_r4_s300", (2, 8, 2, 128, 300, 7)), ("d64_r1_s65", (2, 4, 4, 64, 65, 8)),
