@@ -43,9 +43,9 @@ from __graft_entry__ import load_package  # noqa: E402
 
 N_ROTATE = 8
 FALLBACK_PEAK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_kernel launch on the C2 workload (seed 42),
-# from the ncu capture summarised in profiles/flash_decode_c2_full.md: 102.63 MB read + 5.49 MB written.
-C2_TRAFFIC_BYTES = 115_620_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_small_kernel launch on the C2 workload (seed 42),
+# from the ncu capture summarised in profiles/flash_decode_c2_full.md: 102.10 MB read + 4.05 MB written.
+C2_TRAFFIC_BYTES = 106_150_000
 C3_TRAFFIC_BYTES = 548_590_000  # profiles/flash_decode_c3_full.md: 537.00 MB read + 6.83 MB written
 
 
@@ -375,10 +375,24 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     peak, peak_kind = hbm_peak()
     launch_ms = ms_total / args.steps
     achieved = my_bytes / (launch_ms * 1e-3) / 1e9
+    # which of the library's two decode kernels these sizes run (0 = persistent grid, else the static deal's split)
+    if args.max_ctas > 0:
+        choice = 0
+    elif args.max_ctas < 0:
+        choice = -args.max_ctas
+    else:
+        choice = pkg.capi.load().l3ci_flash_decode_kernel_choice(q.shape[0], q.shape[1], ks[0].shape[1], q.shape[-1],
+                                                                 ks[0].shape[2], int(lens is not None))
+    kernel = "flash_decode_kernel" if choice == 0 else "flash_decode_small_kernel"
+    traffic = None
+    if world == 1 and args.workload == "c2" and kernel == "flash_decode_small_kernel":
+        traffic = C2_TRAFFIC_BYTES
+    if world == 1 and args.workload == "c3" and kernel == "flash_decode_kernel":
+        traffic = C3_TRAFFIC_BYTES
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (C2_TRAFFIC_BYTES if args.workload == "c2" and world == 1 else
-                            C3_TRAFFIC_BYTES if args.workload == "c3" and world == 1 else None), "peak_kind": peak_kind,
-                "kernel": "flash_decode_kernel", "algorithmic_bytes_per_launch": my_bytes,
+                "traffic": traffic, "peak_kind": peak_kind,
+                "kernel": kernel, "kernel_split": (None if choice in (0, 1) else {"ctas_per_unit": choice // 16, "warps_per_unit": choice % 16}),
+                "algorithmic_bytes_per_launch": my_bytes,
                 "frac_of_8TBs_nominal": achieved / 8000.0}
     if sharded_seq:
         roofline["note"] = "per-rank shard; the step also holds the exchange of shard results and their merge"

@@ -173,6 +173,12 @@ typedef struct l3ci_flash_decode_args {
 /* Bytes of scratch one call needs on the current device (depends on its SM count). */
 L3CI_API size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D);
 
+/* Which kernel l3ci_flash_decode runs on the current device for a call of these sizes with max_ctas = 0
+ * (ragged: seq_lens given): 0 = the persistent grid, else 16*C + W of the static deal (C CTAs per unit, W warps
+ * per unit), the code that max_ctas = -(16*C + W) asks for.  -1 for sizes the call would refuse.  For logs and
+ * benchmarks; the choice is a fit to measurements and may change between versions. */
+L3CI_API int l3ci_flash_decode_kernel_choice(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t n_seq, int32_t ragged);
+
 L3CI_API int l3ci_flash_decode(const l3ci_flash_decode_args* args);
 
 /* ------------------------------------------------------------------------------------------

@@ -21,6 +21,7 @@ EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version",
     "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
+    "l3ci_flash_decode_kernel_choice",
     "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge", "l3ci_prefill_attention",
 )
 
@@ -98,6 +99,8 @@ def load() -> C.CDLL:
     lib.l3ci_rot_embed_kv_cache_at.argtypes = [vp, vp, i64, vp, vp, vp, vp] + [i64] * 10 + [vp]
     lib.l3ci_flash_decode_scratch_bytes.restype = C.c_size_t
     lib.l3ci_flash_decode_scratch_bytes.argtypes = [i32, i32, i32, i32]
+    lib.l3ci_flash_decode_kernel_choice.restype = C.c_int
+    lib.l3ci_flash_decode_kernel_choice.argtypes = [i32, i32, i32, i32, i32, i32]
     lib.l3ci_flash_decode.restype = C.c_int
     lib.l3ci_flash_decode.argtypes = [C.POINTER(FlashDecodeArgs)]
     lib.l3ci_flash_decode_static.restype = C.c_int

@@ -992,6 +992,13 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
 
 extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) { return l3ci::flash_decode_launch(a); }
 
+extern "C" int l3ci_flash_decode_kernel_choice(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t n_seq, int32_t ragged) {
+  using namespace l3ci;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || (D != 64 && D != 128) || n_seq <= 0) return -1;
+  if (!flash_decode_small_applies(B, Hq, Hkv, D, n_seq, ragged != 0)) return 0;
+  return flash_decode_small_split_code(B, Hkv, D, n_seq);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant: the scratch lives in this library's own device image.
 // ---------------------------------------------------------------------------------------------

@@ -430,6 +430,12 @@ bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool r
   return cta_bytes <= (ragged ? 1.25e6 : 4.5e6);
 }
 
+int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {
+  const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
+  const UnitSplit s = unit_split((long long)B * Hkv, tiles, sm_count(), D);
+  return 16 * s.C + s.W;
+}
+
 // split_code: 0 = unit_split's choice, else 16 * C + W (tuning).
 int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
   const long long units = (long long)a->B * a->Hkv;

@@ -25,6 +25,8 @@ int max_smem_optin();
 // caller; split_code 0 = its own choice, else 16 * CTAs per unit + warps per unit).
 bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged);
 int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code);
+// 16 * C + W of the split the static kernel would take for these sizes on the current device.
+int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

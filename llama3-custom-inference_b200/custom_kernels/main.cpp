@@ -427,6 +427,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lse_exchange_merge", torch::wrap_pybind_function(lse_exchange_merge), "lse_exchange_merge", py::arg("bufs"),
         py::arg("rank"), py::arg("epoch"), py::arg("B"), py::arg("Hq"), py::arg("D"), py::kw_only(),
         py::arg("status") = py::none());
+  // which decode kernel a call of these sizes takes on `device` (0 = persistent grid, else 16*C + W of the static deal)
+  m.def("flash_decode_kernel_choice", [](int64_t device, int64_t B, int64_t Hq, int64_t Hkv, int64_t D, int64_t n_seq, bool ragged) {
+    c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+    return (int64_t)l3ci_flash_decode_kernel_choice((int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)D, (int32_t)n_seq,
+                                                    ragged ? 1 : 0);
+  }, py::arg("device"), py::arg("B"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("n_seq"), py::arg("ragged") = false);
   m.def("lse_exchange_bytes", [](int64_t ranks, int64_t B, int64_t Hq, int64_t D) {
     return (int64_t)l3ci_lse_exchange_bytes((int32_t)ranks, (int32_t)B, (int32_t)Hq, (int32_t)D);
   });

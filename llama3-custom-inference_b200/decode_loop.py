@@ -69,6 +69,23 @@ class Llama3Decoder:
                                                      scale_factor=cfg.rope_scale_factor).to(self.device)
         assert self.w["h0.attn"].shape == (qkv_rows, E) and self.w["h0.gate_up"].shape == (2 * F_, E)
         self._graph = None
+        self._kernel_for_batch = {}
+        self.equal_lengths = True   # all sequences of a step have the same number of cached tokens (`generate`)
+
+    def _decode_kernel(self, B: int) -> int:
+        """`max_ctas` for the decode attention of a batch of B.  `generate` keeps all sequences at one length, which
+        the library cannot see in device-side lengths: its own rule must assume a lopsided batch and keeps the
+        persistent kernel for long caches.  With units known to be equal, the static deal is asked for (-1)
+        wherever the library would take it for a batch of full-length caches."""
+        if not self.equal_lengths:
+            return 0
+        if B in self._kernel_for_batch:
+            return self._kernel_for_batch[B]
+        cfg = self.cfg
+        dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        choice = self.ext.flash_decode_kernel_choice(dev, B, cfg.n_head, cfg.n_kv_head, cfg.head_dim, self.max_len, False)
+        self._kernel_for_batch[B] = -1 if choice > 0 else 0
+        return self._kernel_for_batch[B]
 
     # ---- one forward pass over T new tokens per sequence ------------------------------------------------
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor) -> torch.Tensor:
@@ -92,7 +109,8 @@ class Llama3Decoder:
                 y = ext.prefill_attention(q.transpose(1, 2), k, v)                     # causal, GQA
             else:
                 y = ext.flash_attention_decode(q.transpose(1, 2), self.cache_k[l][:B].transpose(1, 2),
-                                               self.cache_v[l][:B].transpose(1, 2), seq_lens=seq_lens)  # model.py:118
+                                               self.cache_v[l][:B].transpose(1, 2), seq_lens=seq_lens,
+                                               max_ctas=self._decode_kernel(B))     # model.py:118
             y = y.transpose(1, 2).reshape(B, T, E)                                     # model.py:120
             x, h = ext.add_rms_norm(F.linear(y, w[p + "proj"]), x, w[p + "ln_2"], cfg.norm_eps)  # :121, 147-148
             gu = F.linear(h, w[p + "gate_up"])                                         # c_fc2 | c_fc, model.py:134

@@ -65,6 +65,9 @@ def test_argument_validation_happens_before_cuda(capi):
     assert lib.l3ci_flash_decode(C.byref(a)) == capi.OK  # empty batch
     assert lib.l3ci_flash_decode(None) == capi.ERR_INVALID
     assert lib.l3ci_flash_decode_scratch_bytes(1, 32, 5, 128) == 0
+    # sizes the call would refuse: no kernel is chosen
+    for bad in ((1, 32, 5, 128, 16, 0), (1, 32, 8, 96, 16, 0), (0, 32, 8, 128, 16, 0), (1, 32, 8, 128, 0, 1)):
+        assert lib.l3ci_flash_decode_kernel_choice(*bad) == -1
 
 
 def test_extension_module_mirrors_reference_binding(ext):

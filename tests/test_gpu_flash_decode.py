@@ -88,6 +88,26 @@ def test_every_static_split_agrees_with_the_oracle(capi, device, D, split):
         assert (a - b).abs().max().item() <= 2e-2
 
 
+def test_kernel_choice_names_the_split_the_call_takes(capi, device):
+    lib = capi.load()
+    with torch.cuda.device(device):
+        # the reference's own example and a batched step of 2048-token caches: static deal, one CTA per unit
+        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 64, 256, 0) == 16 + 8
+        assert lib.l3ci_flash_decode_kernel_choice(16, 32, 8, 128, 2048, 1) == 16 + 8
+        # few long units: clusters; very long or possibly lopsided ones, or 16 query heads per KV head: persistent grid
+        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 16384, 0) == 16 * 8 + 8
+        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 131072, 0) == 0
+        assert lib.l3ci_flash_decode_kernel_choice(16, 32, 8, 128, 8192, 1) == 0
+        assert lib.l3ci_flash_decode_kernel_choice(2, 32, 2, 128, 512, 0) == 0
+        # many short units share CTAs
+        assert lib.l3ci_flash_decode_kernel_choice(64, 32, 8, 64, 256, 0) == 16 + 2
+    # the split it names, asked for explicitly, gives the same bits as the default call
+    case = inputs.decode_case(1, 32, 8, 128, 16384, seed=5)
+    a = _run(capi, case, device)
+    b = _run(capi, case, device, max_ctas=-(16 * 8 + 8))
+    assert torch.equal(a, b)
+
+
 def test_static_kernel_refuses_a_malformed_split(capi, device):
     case = inputs.decode_case(1, 8, 2, 64, 50, seed=3).to(device)
     for code in (-(16 * 3 + 8), -(16 * 2 + 4), -(16 * 16 + 8), -(16 + 3)):
