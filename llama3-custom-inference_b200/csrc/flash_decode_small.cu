@@ -412,12 +412,15 @@ UnitSplit unit_split(long long units, long long tiles, int sms, int D) {
 
 // True when l3ci_flash_decode hands the call to this kernel, decided from host-side sizes only.  Measured on a
 // B200 against the persistent kernel over B = 1..64, 128..131072 tokens, both head sizes: this kernel starts in
-// 3.3 us instead of about 10 and an SM takes in up to 96 GB/s, so it is ahead (by up to 2x) wherever one wave
-// covers the units and a CTA's share stays within about 4 MB; past that both stream at the rate of the memory
-// and the persistent kernel, which balances, is level or ahead.  The lengths of a ragged batch are on the
-// device: one long sequence among short ones keeps a single CTA busy here, while the persistent kernel would
-// spread it.  With seq_lens the share that a CTA could get (from the cache length) is therefore held to 1.25 MB,
-// about 13 us: what the other kernel's start costs.
+// 3.3 us (4 with a cluster) instead of about 10, and an SM takes in up to 96 GB/s of 256-byte rows (head size 128)
+// or 73 GB/s of 128-byte rows (head size 64), all SMs together 6.9 TB/s.  So it is ahead (by up to 2x) wherever one
+// wave covers the units and a CTA's share stays small; for large shares both stream at the rate of the memory, or
+// this one at the rate of its few SMs, and the persistent kernel (14.8 us + bytes at 7.3 TB/s when large), which
+// balances and reads whole token rows, is level or ahead.  Shares up to 1 MB always come here, shares up to 4.5 MB
+// if the two estimates say so.  The lengths of a ragged batch are on the device: one long sequence among short
+// ones keeps a single CTA busy here, while the persistent kernel would spread it.  With seq_lens the share that a
+// CTA could get (from the cache length) is therefore held to 1.25 MB, about 13 us: what the other kernel's start
+// costs.
 bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged) {
   if (Hq / Hkv > 8) return false;
   const long long units = (long long)B * Hkv;
@@ -426,8 +429,14 @@ bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool r
   if (sms <= 0) return false;
   const UnitSplit s = unit_split(units, tiles, sms, D);
   if (s.ctas == 0) return false;
-  const double cta_bytes = (double)n_seq * 4.0 * D * (kSmWarps / s.W) / s.C;
-  return cta_bytes <= (ragged ? 1.25e6 : 4.5e6);
+  const double unit_bytes = (double)n_seq * 4.0 * D;
+  const double cta_bytes = unit_bytes * (kSmWarps / s.W) / s.C;
+  if (cta_bytes > (ragged ? 1.25e6 : 4.5e6)) return false;
+  if (cta_bytes <= 1.0e6) return true;
+  const double per_sm = fmin(D == 64 ? 73e3 : 96e3, 6.9e6 / s.ctas);  // bytes per microsecond
+  const double t_static = 4.0 + cta_bytes / per_sm;
+  const double t_persistent = 14.8 + unit_bytes * (double)units / 7.3e6;
+  return t_static <= t_persistent;
 }
 
 int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {
