@@ -136,6 +136,59 @@ struct FdWalker {
   L3CI_HD int unit_begin(const FdCursor& c) const { return pref_of(c.b) + c.g * c.tc; }
 };
 
+// ---------------------------------------------------------------------------------------------
+// Static deal (flash_decode_small.cu): units handed to warps, CTAs or clusters on the host.
+// ---------------------------------------------------------------------------------------------
+constexpr int kFdStaticWarps = 8;  // warps of a CTA of the static kernel
+
+// W warps per unit, C CTAs per unit, and the resulting grid; ctas == 0: no split keeps the grid within one wave.
+struct FdStaticSplit {
+  int W, C, ctas;
+};
+
+// The split for `units` units of `tiles` tiles on `sms` SMs.  Few units of at least 32 tiles are spread over
+// clusters while every warp still gets a tile and all clusters run at once (max_clusters[i]: clusters of 2 << i
+// CTAs the device holds at once); more units than SMs share CTAs.
+inline FdStaticSplit fd_static_split(long long units, long long tiles, int sms, const int max_clusters[3]) {
+  FdStaticSplit s{kFdStaticWarps, 1, 0};
+  if (units <= 0 || sms <= 0) return s;
+  if (units <= sms) {
+    for (int i = 0; i < 3; ++i) {
+      const int c2 = s.C * 2;
+      if (tiles < 32 || tiles < (long long)kFdStaticWarps * c2 || units * c2 > sms || units > max_clusters[i]) break;
+      s.C = c2;
+    }
+    s.ctas = (int)(units * s.C);
+    return s;
+  }
+  for (int U = 2; U <= kFdStaticWarps; U *= 2)
+    if ((units + U - 1) / U <= sms) {
+      s.W = kFdStaticWarps / U;
+      s.ctas = (int)((units + U - 1) / U);
+      return s;
+    }
+  return s;
+}
+
+// Whether a call goes to the static kernel, from host-side sizes only.  Fits to measurements on a B200, bytes per
+// microsecond: the static kernel starts in about 4 us, an SM takes in up to 96e3 (256-byte rows, head size 128) or
+// 73e3 (128-byte rows, head size 64), all SMs together 6.9e6; the persistent kernel, when large, takes 14.8 us plus
+// the bytes at 7.3e6.  Shares (bytes of cache per CTA, from the cache length) up to 1 MB always go static, up to
+// 4.5 MB if the estimates say so; with device-side lengths (ragged) the share is held to 1.25 MB, because one
+// long sequence among short ones would keep a single CTA busy.
+inline bool fd_static_applies(const FdStaticSplit& s, long long units, int head_size, int n_seq, int ratio, bool ragged) {
+  if (ratio > 8 || s.ctas == 0) return false;
+  const double unit_bytes = (double)n_seq * 4.0 * head_size;
+  const double cta_bytes = unit_bytes * (kFdStaticWarps / s.W) / s.C;
+  if (cta_bytes > (ragged ? 1.25e6 : 4.5e6)) return false;
+  if (cta_bytes <= 1.0e6) return true;
+  const double all = 6.9e6 / s.ctas;
+  const double one = head_size == 64 ? 73e3 : 96e3;
+  const double t_static = 4.0 + cta_bytes / (one < all ? one : all);
+  const double t_persistent = 14.8 + unit_bytes * (double)units / 7.3e6;
+  return t_static <= t_persistent;
+}
+
 // True when the cursor stands on the last column its CTA sees of the current unit.
 L3CI_HD bool fd_unit_ends(const FdCursor& c, int range_end) { return c.j == c.tc - 1 || c.col == range_end - 1; }
 

@@ -383,60 +383,24 @@ int max_active_clusters(int D, int C) {
   return n;
 }
 
-// How a call is dealt to this kernel: W warps per unit, C CTAs per unit, and the resulting grid.
-struct UnitSplit {
-  int W, C, ctas;
-};
+using UnitSplit = FdStaticSplit;
+static_assert(kSmWarps == kFdStaticWarps, "the plan header deals to this kernel's warps");
 
-// The split for `units` units of `tiles` tiles on `sms` SMs.  Few units of at least 32 tiles are spread over
-// clusters while every warp still gets a tile and all clusters run at once; more units than SMs share CTAs.
-// ctas == 0: no split keeps the grid within one wave.
+// The split of fd_static_split with this device's answers for the clusters it holds at once.
 UnitSplit unit_split(long long units, long long tiles, int sms, int D) {
-  UnitSplit s{kSmWarps, 1, 0};
-  if (units <= 0) return s;
-  if (units <= sms) {
-    while (s.C < 8 && tiles >= 32 && tiles >= (long long)kSmWarps * s.C * 2 && units * s.C * 2 <= sms &&
-           units <= max_active_clusters(D, s.C * 2))
-      s.C *= 2;
-    s.ctas = (int)(units * s.C);
-    return s;
-  }
-  for (int U = 2; U <= kSmWarps; U *= 2)
-    if ((units + U - 1) / U <= sms) {
-      s.W = kSmWarps / U;
-      s.ctas = (int)((units + U - 1) / U);
-      return s;
-    }
-  return s;
+  int max_clusters[3] = {0, 0, 0};
+  if (units <= sms && tiles >= 32)
+    for (int i = 0; i < 3; ++i) max_clusters[i] = max_active_clusters(D, 2 << i);
+  return fd_static_split(units, tiles, sms, max_clusters);
 }
 
-// True when l3ci_flash_decode hands the call to this kernel, decided from host-side sizes only.  Measured on a
-// B200 against the persistent kernel over B = 1..64, 128..131072 tokens, both head sizes: this kernel starts in
-// 3.3 us (4 with a cluster) instead of about 10, and an SM takes in up to 96 GB/s of 256-byte rows (head size 128)
-// or 73 GB/s of 128-byte rows (head size 64), all SMs together 6.9 TB/s.  So it is ahead (by up to 2x) wherever one
-// wave covers the units and a CTA's share stays small; for large shares both stream at the rate of the memory, or
-// this one at the rate of its few SMs, and the persistent kernel (14.8 us + bytes at 7.3 TB/s when large), which
-// balances and reads whole token rows, is level or ahead.  Shares up to 1 MB always come here, shares up to 4.5 MB
-// if the two estimates say so.  The lengths of a ragged batch are on the device: one long sequence among short
-// ones keeps a single CTA busy here, while the persistent kernel would spread it.  With seq_lens the share that a
-// CTA could get (from the cache length) is therefore held to 1.25 MB, about 13 us: what the other kernel's start
-// costs.
+// True when l3ci_flash_decode hands the call to this kernel (fd_static_applies has the rule and its reasons).
 bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged) {
-  if (Hq / Hkv > 8) return false;
   const long long units = (long long)B * Hkv;
   const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
   const int sms = sm_count();
-  if (sms <= 0) return false;
-  const UnitSplit s = unit_split(units, tiles, sms, D);
-  if (s.ctas == 0) return false;
-  const double unit_bytes = (double)n_seq * 4.0 * D;
-  const double cta_bytes = unit_bytes * (kSmWarps / s.W) / s.C;
-  if (cta_bytes > (ragged ? 1.25e6 : 4.5e6)) return false;
-  if (cta_bytes <= 1.0e6) return true;
-  const double per_sm = fmin(D == 64 ? 73e3 : 96e3, 6.9e6 / s.ctas);  // bytes per microsecond
-  const double t_static = 4.0 + cta_bytes / per_sm;
-  const double t_persistent = 14.8 + unit_bytes * (double)units / 7.3e6;
-  return t_static <= t_persistent;
+  if (sms <= 0 || Hq / Hkv > 8) return false;
+  return fd_static_applies(unit_split(units, tiles, sms, D), units, D, n_seq, Hq / Hkv, ragged);
 }
 
 int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {

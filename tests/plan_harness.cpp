@@ -22,6 +22,15 @@ int plan_max_ctas(int sms, int hg) { return fd_max_ctas(sms, hg); }
 int plan_range_begin(int cta, int total, int ctas) { return fd_range_begin(cta, total, ctas); }
 int plan_cta_of(int col, int total, int ctas) { return fd_cta_of(col, total, ctas); }
 
+// Static deal: out = {W, C, ctas}; returns whether the call goes to the static kernel.
+int plan_static(int B, int Hq, int Hkv, int D, int n_seq, int ragged, int sms, const int* max_clusters, int* out) {
+  const long long units = (long long)B * Hkv;
+  const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
+  const FdStaticSplit s = fd_static_split(units, tiles, sms, max_clusters);
+  out[0] = s.W; out[1] = s.C; out[2] = s.ctas;
+  return fd_static_applies(s, units, D, n_seq, Hq / Hkv, ragged != 0) ? 1 : 0;
+}
+
 // Returns 0 if all invariants hold, else a positive code; info[0..3] receive details.
 // stats[0] = units finished directly, stats[1] = units merged, stats[2] = records written,
 // stats[3] = max columns of a CTA, stats[4] = min columns of a non-empty CTA, stats[5] = total columns,

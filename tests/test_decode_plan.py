@@ -18,7 +18,16 @@ def plan(tmp_path_factory):
                     str(REPO / "tests" / "plan_harness.cpp"), "-o", str(so)], check=True)
     lib = C.CDLL(str(so))
     lib.plan_simulate.argtypes = [C.c_int] * 4 + [C.POINTER(C.c_int)] + [C.c_int] * 2 + [C.POINTER(C.c_int), C.POINTER(C.c_longlong)]
+    lib.plan_static.argtypes = [C.c_int] * 7 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]
     return lib
+
+
+def static_deal(plan, B, Hq, Hkv, D, n_seq, ragged=False, sms=148, max_clusters=(72, 34, 14)):
+    """(goes to the static kernel, W warps per unit, C CTAs per unit, CTAs) on a device with `sms` SMs that holds
+    `max_clusters` clusters of 2, 4, 8 CTAs at once."""
+    out = (C.c_int * 3)()
+    takes = plan.plan_static(B, Hq, Hkv, D, n_seq, int(ragged), sms, (C.c_int * 3)(*max_clusters), out)
+    return bool(takes), out[0], out[1], out[2]
 
 
 def simulate(plan, B, Hkv, D, n_seq, lens, G, stages=3):
@@ -94,3 +103,42 @@ def test_short_sequences_are_not_cut(plan):
     assert stats[6] == 0
     # one long sequence is always cut
     assert simulate(plan, 1, 8, 128, 131072, None, 148)[6] == 0
+
+
+# ---- the static deal (flash_decode_small.cu): split and choice of kernel from host-side sizes ---------------------
+
+def test_static_split_of_the_benchmark_shapes(plan):
+    assert static_deal(plan, 1, 32, 8, 64, 256) == (True, 8, 1, 8)              # config 1: 8 tiles, no cluster
+    assert static_deal(plan, 16, 32, 8, 128, 2048, ragged=True) == (True, 8, 1, 128)   # config 2
+    assert static_deal(plan, 1, 32, 8, 128, 131072)[0] is False                 # config 3: persistent kernel
+    assert static_deal(plan, 64, 32, 8, 64, 2176) == (True, 2, 1, 128)          # decode batch: 4 units per CTA
+    assert static_deal(plan, 64, 32, 8, 64, 2176, ragged=True)[0] is False      # ... unless the lengths may differ
+    assert static_deal(plan, 1, 32, 8, 128, 16384) == (True, 8, 8, 64)          # few long units: clusters of 8
+    assert static_deal(plan, 2, 32, 8, 128, 2048) == (True, 8, 4, 64)           # 16 clusters of 8 would not fit
+    assert static_deal(plan, 2, 32, 2, 128, 512)[0] is False                    # 16 query heads per KV head
+    assert static_deal(plan, 1, 32, 8, 64, 131072)[0] is False                  # 64 CTAs of 128-byte rows: too slow
+    assert static_deal(plan, 200, 8, 8, 64, 128)[0] is False                    # 1600 units: more than one wave
+
+
+def test_static_split_invariants(plan):
+    rnd = random.Random(7)
+    for _ in range(3000):
+        B, Hkv = rnd.choice([1, 2, 3, 5, 8, 16, 40, 64, 150]), rnd.choice([1, 2, 3, 4, 8])
+        D, n_seq = rnd.choice([64, 128]), rnd.choice([1, 31, 32, 100, 511, 512, 513, 2048, 5000, 40000, 131072])
+        sms = rnd.choice([148, 132, 20])
+        mc = (rnd.choice([0, sms // 2 - 2]), rnd.choice([0, sms // 4 - 3]), rnd.choice([0, 3, sms // 8 - 4]))
+        takes, W, Cc, ctas = static_deal(plan, B, Hkv * rnd.choice([1, 4, 8]), Hkv, D, n_seq, rnd.random() < 0.5, sms, mc)
+        units, tiles = B * Hkv, -(-n_seq // (16 if D == 128 else 32))
+        assert W in (1, 2, 4, 8) and Cc in (1, 2, 4, 8) and (Cc == 1 or W == 8)
+        if ctas == 0:
+            assert not takes and units > 8 * sms
+            continue
+        assert ctas <= sms and ctas == -(-units // (8 // W)) * Cc          # one wave, every unit placed
+        if Cc > 1:
+            assert tiles >= 8 * Cc and tiles >= 32                           # every warp of the cluster has a tile
+            assert units <= mc[{2: 0, 4: 1, 8: 2}[Cc]]                       # all clusters resident at once
+        if W < 8:
+            assert -(-units // (8 // W // 2)) > sms                          # half as many units per CTA would not fit
+        if takes:
+            share = n_seq * 4 * D * (8 // W) / Cc
+            assert share <= 4.5e6
