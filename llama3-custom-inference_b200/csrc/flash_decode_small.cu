@@ -10,8 +10,9 @@
 // distributed shared memory.  K and V rows go from global to shared memory with 16-byte asynchronous copies
 // (written in the 128-byte-swizzled layout that ldmatrix expects), three tiles in flight per warp; the tile
 // arithmetic is the one of the persistent kernel (S^T = K Q^T and O^T = V^T P^T on mma.sync.m16n8k16, tokens on
-// the rows of a tile, the group's query heads on its 8 columns).  Taken by l3ci_flash_decode where the cost model
-// below expects it to be faster, for at most 8 query heads per KV head; results agree within rounding.
+// the rows of a tile, the group's query heads on its 8 columns).  Taken by l3ci_flash_decode where
+// fd_static_applies (flash_decode_plan.h) expects it to be faster, for at most 8 query heads per KV head; results
+// agree with the persistent kernel's within rounding.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
