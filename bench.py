@@ -141,7 +141,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------
-def make_decode_workload(name: str, rank: int, world: int):
+def make_decode_workload(name: str, rank: int, world: int, seq_len: int = 131072):
     """Returns (case on CPU, description).  Values are seeded N(0,1) in bf16 (synthetic data)."""
     from oracle import inputs
 
@@ -152,8 +152,8 @@ def make_decode_workload(name: str, rank: int, world: int):
         case = inputs.config1(seed=42 + rank)
         desc = "C1 single decode step: B=1, Hq=32, Hkv=8, D=64, S=256, bf16"
     elif name == "c3":
-        case = inputs.config3(seed=42)
-        desc = "C3 long-context decode: B=1, Hq=32, Hkv=8, D=128, S=131072, bf16, KV sequence sharded over the GPUs"
+        case = inputs.config3(seed=42, S=seq_len)
+        desc = f"C3 long-context decode: B=1, Hq=32, Hkv=8, D=128, S={seq_len}, bf16, KV sequence sharded over the GPUs"
     else:
         raise ValueError(name)
     return case, desc
@@ -190,7 +190,7 @@ def run_reference_arm(args, rank, world):
     """The reference's own CPU implementation of the path, timed on the host cores (rank 0 only)."""
     if rank != 0:
         return
-    case, desc = make_decode_workload(args.workload if args.workload in ("c1", "c2", "c3") else "c2", 0, 1)
+    case, desc = make_decode_workload(args.workload if args.workload in ("c1", "c2", "c3") else "c2", 0, 1, args.seq_len)
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_attention_pass(case)
     steps = max(1, min(args.steps, 10))
@@ -230,6 +230,7 @@ def main():
     ap.add_argument("--no-comparator", action="store_true", help="c1-c3: skip the torch SDPA timing on the GPU")
     ap.add_argument("--no-graph", action="store_true", help="c1-c3: launch every step through the extension call "
                     "instead of replaying a captured launch")
+    ap.add_argument("--seq-len", type=int, default=131072, help="c3: cached tokens (a shard of C3 on one GPU: 131072 / N)")
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--nccl-merge", action="store_true", help="c3 on >1 GPU: all_gather + merge kernel instead of the fused exchange")
     args = ap.parse_args()
@@ -298,7 +299,7 @@ def sum_over_ranks(x: float, world: int, dev) -> float:
 
 
 def bench_decode(args, ext, pkg, dev, rank, world):
-    case, desc = make_decode_workload(args.workload, rank, world)
+    case, desc = make_decode_workload(args.workload, rank, world, args.seq_len)
     sharded_seq = args.workload == "c3" and world > 1
     if sharded_seq:
         lo, hi = pkg.sharding.kv_shard_bounds(case.k.shape[2], world)[rank]
@@ -387,7 +388,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     traffic = None
     if world == 1 and args.workload == "c2" and kernel == "flash_decode_small_kernel":
         traffic = C2_TRAFFIC_BYTES
-    if world == 1 and args.workload == "c3" and kernel == "flash_decode_kernel":
+    if world == 1 and args.workload == "c3" and kernel == "flash_decode_kernel" and args.seq_len == 131072:
         traffic = C3_TRAFFIC_BYTES
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_kind": peak_kind,

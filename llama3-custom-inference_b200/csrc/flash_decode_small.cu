@@ -107,22 +107,49 @@ flash_decode_small_kernel(const SmallParams p) {
   const __nv_bfloat16* vbase = p.v + (long long)b * p.v_sb + (long long)head * p.v_sh;
   const uint32_t buf0 = smem_u32(smem) + warp * kSmSlots * kTileBytes;
 
-  // copy of one tile: 16-byte chunk c (0..7) of 128-byte row r of half h goes to chunk position c ^ (r & 7)
-  // (always one commit group per call, empty past the warp's last tile, so that "all but the newest
-  // kSmSlots - 1 groups" is the tile about to be used)
+  // Copy of one tile: 16-byte chunk c (0..7) of 128-byte row r of half h goes to chunk position c ^ (r & 7).  A
+  // pass of the warp covers 4 rows x 8 chunks; lane (r0, c) keeps one pointer per tensor and steps it by 4 rows
+  // (the copies are a third of the instructions of a tile otherwise).  Always one commit group per call, empty
+  // past the warp's last tile, so that "all but the newest kSmSlots - 1 groups" is the tile about to be used.
   const uint64_t policy = l2_evict_first_policy();
+  const int r0 = lane >> 3, c8 = lane & 7;
+  const __nv_bfloat16* klane = kbase + (long long)r0 * p.k_st + c8 * 8;
+  const __nv_bfloat16* vlane = vbase + (long long)r0 * p.v_st + c8 * 8;
+  const long long k4 = 4 * p.k_st, v4 = 4 * p.v_st;
+  // row r0 + 4 j sits at (r0 + 4 j) * 128, its chunk at c ^ r0 ^ (4 * (j & 1)) since r0 < 4
+  const uint32_t d_even = r0 * 128 + ((c8 ^ r0) << 4), d_odd = r0 * 128 + ((c8 ^ r0 ^ 4) << 4);
   auto fetch = [&](int tile, int slot) {
-    const uint32_t dst = buf0 + slot * kTileBytes;
-    constexpr int kChunks = kHalves * kTile * 8;  // per tensor
+    if (tile < t_end) {
+      const uint32_t dst = buf0 + slot * kTileBytes;
+      const long long t0 = (long long)tile * kTile;
+      const __nv_bfloat16* kp = klane + t0 * p.k_st;
+      const __nv_bfloat16* vp = vlane + t0 * p.v_st;
+      if (tile * kTile + kTile <= len) {
 #pragma unroll
-    for (int i = lane; i < (tile < t_end ? kChunks : 0); i += 32) {
-      const int c = i & 7, r = (i >> 3) % kTile, h = i / (8 * kTile);
-      const int tok = tile * kTile + r;
-      const bool ok = tok < len;
-      const long long off = (long long)(ok ? tok : 0);
-      const uint32_t d = h * kBoxBytes + r * 128 + ((c ^ (r & 7)) << 4);
-      cp_async16(dst + d, kbase + off * p.k_st + h * 64 + c * 8, ok, policy);
-      cp_async16(dst + kHalves * kBoxBytes + d, vbase + off * p.v_st + h * 64 + c * 8, ok, policy);
+        for (int j = 0; j < kTile / 4; ++j) {
+          const uint32_t d = dst + j * 512 + ((j & 1) ? d_odd : d_even);
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h) {
+            cp_async16(d + h * kBoxBytes, kp + h * 64, true, policy);
+            cp_async16(d + (kHalves + h) * kBoxBytes, vp + h * 64, true, policy);
+          }
+          kp += k4;
+          vp += v4;
+        }
+      } else {  // the sequence ends inside this tile: rows past its end are zero-filled, nothing is read for them
+#pragma unroll
+        for (int j = 0; j < kTile / 4; ++j) {
+          const uint32_t d = dst + j * 512 + ((j & 1) ? d_odd : d_even);
+          const bool ok = tile * kTile + r0 + 4 * j < len;
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h) {
+            cp_async16(d + h * kBoxBytes, ok ? kp + h * 64 : kbase, ok, policy);
+            cp_async16(d + (kHalves + h) * kBoxBytes, ok ? vp + h * 64 : vbase, ok, policy);
+          }
+          kp += k4;
+          vp += v4;
+        }
+      }
     }
     cp_async_commit();
   };
@@ -154,16 +181,30 @@ flash_decode_small_kernel(const SmallParams p) {
     __syncwarp();
     const uint32_t kb = buf0 + slot * kTileBytes, vb = kb + kHalves * kBoxBytes;
     // S^T = K Q^T
-    float s[MB][4];
+    // (the k-steps go to kAcc accumulator sets summed at the end: a chain of KS dependent MMAs is 20 cycles each)
+    constexpr int kAcc = MB == 1 ? 4 : 2;
+    float sp[kAcc][MB][4];
 #pragma unroll
-    for (int mb = 0; mb < MB; ++mb) s[mb][0] = s[mb][1] = s[mb][2] = s[mb][3] = 0.f;
+    for (int a = 0; a < kAcc; ++a)
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) sp[a][mb][0] = sp[a][mb][1] = sp[a][mb][2] = sp[a][mb][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
 #pragma unroll
       for (int mb = 0; mb < MB; ++mb) {
         uint32_t a0, a1, a2, a3;
         ldsm_x4(kb + (ks >> 2) * kBoxBytes + mb * 2048 + k_row_off + (((2u * (ks & 3)) ^ k_x) << 4), a0, a1, a2, a3);
-        mma_bf16(s[mb], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+        mma_bf16(sp[ks % kAcc][mb], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+      }
+    float s[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float acc = sp[0][mb][e];
+#pragma unroll
+        for (int a = 1; a < kAcc; ++a) acc += sp[a][mb][e];
+        s[mb][e] = acc;
       }
     // mask the end of the sequence (rows beyond len were zero-filled: finite scores, masked here)
     const int tok0 = t * kTile;
