@@ -46,7 +46,7 @@ FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_small_kernel launch on the C2 workload (seed 42),
 # from the ncu capture summarised in profiles/flash_decode_c2_full.md: 102.10 MB read + 4.05 MB written.
 C2_TRAFFIC_BYTES = 106_150_000
-C3_TRAFFIC_BYTES = 548_590_000  # profiles/flash_decode_c3_full.md: 537.00 MB read + 6.83 MB written
+C3_TRAFFIC_BYTES = 540_310_000  # flash_decode_small_kernel, profiles/flash_decode_c3_full.md: 536.91 MB read + 3.40 MB written
 
 
 def hbm_peak():
@@ -388,7 +388,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     traffic = None
     if world == 1 and args.workload == "c2" and kernel == "flash_decode_small_kernel":
         traffic = C2_TRAFFIC_BYTES
-    if world == 1 and args.workload == "c3" and kernel == "flash_decode_kernel" and args.seq_len == 131072:
+    if world == 1 and args.workload == "c3" and kernel == "flash_decode_small_kernel" and args.seq_len == 131072:
         traffic = C3_TRAFFIC_BYTES
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": traffic, "peak_kind": peak_kind,

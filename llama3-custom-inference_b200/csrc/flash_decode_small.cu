@@ -28,6 +28,12 @@ namespace {
 
 constexpr int kSmWarps = 8;
 constexpr int kSmSlots = 3;  // tiles in flight per warp
+// Few CTAs with long runs of tiles each have an SM's intake to themselves: there the warps wait on their own
+// instructions, not on memory, and 12 warps with 2 tiles in flight each (the same shared memory) issue more
+// (131072 tokens of one sequence: 84 us instead of 91; short runs lose a little to the finer deal).
+constexpr int kClWarps = 12;
+constexpr int kClSlots = 2;
+static_assert(kClWarps * kClSlots == kSmWarps * kSmSlots, "both shapes of a CTA fill the same shared memory");
 
 struct SmallParams {
   const __nv_bfloat16 *q, *k, *v;
@@ -71,9 +77,14 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t cta) {
 // kCluster: launched as clusters of CTAs per unit (the instances without hold no cluster instruction and are
 // launched the plain way, which starts sooner).  kWholeCta: all eight warps on one unit, known at compile time
 // (the merge loops then unroll without predicates: 0.5 us on a call of a few microseconds).
-template <int D, bool kCluster, bool kWholeCta>
-__global__ void __launch_bounds__(32 * kSmWarps)
+// kWide: 12 warps x 2 tiles in flight instead of 8 x 3 (cluster instances on long runs of tiles).
+template <int D, bool kCluster, bool kWholeCta, bool kWide = false>
+__global__ void __launch_bounds__(32 * (kWide ? kClWarps : kSmWarps))
 flash_decode_small_kernel(const SmallParams p) {
+  static_assert(kWholeCta || !kCluster, "a cluster works on one unit with all warps of its CTAs");
+  static_assert(kCluster || !kWide, "the wide shape is built for cluster instances only");
+  constexpr int NW = kWide ? kClWarps : kSmWarps;  // warps of the CTA
+  constexpr int NS = kWide ? kClSlots : kSmSlots;  // tiles in flight per warp
   constexpr int kTile = fd_tile_tokens(D);   // tokens per tile: 4 KB of K and 4 KB of V
   constexpr int kHalves = D / 64;
   constexpr int kBoxBytes = kTile * 128;     // one 64-column half of a tile
@@ -82,35 +93,36 @@ flash_decode_small_kernel(const SmallParams p) {
   constexpr int kStateFloats = 8 * D + 16;   // o[8 rows][D], m[8], l[8]
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* states = reinterpret_cast<float*>(smem);  // [kSmWarps][kStateFloats], over the tile slots once all warps are done
+  float* states = reinterpret_cast<float*>(smem);  // [NW][kStateFloats], over the tile slots once all warps are done
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   // (shifts, not divisions: they sit on the path to the first copy)
-  const int R = p.R, lgW = kWholeCta ? 3 : p.lgW, lgC = kCluster ? p.lgC : 0;
-  const int W = 1 << lgW, C = 1 << lgC;
-  const int U = kSmWarps >> lgW;                    // units per CTA
+  const int R = p.R, lgW = kWholeCta ? 0 : p.lgW, lgC = kCluster ? p.lgC : 0;
+  const int W = kWholeCta ? NW : 1 << lgW, C = 1 << lgC;
+  const int U = kWholeCta ? 1 : NW >> lgW;          // units per CTA
   uint32_t cta_rank = 0;
   if constexpr (kCluster) cta_rank = cluster_cta_rank();
   const int n_units = p.B * p.Hkv;
   const int unit0 = (int)(blockIdx.x >> lgC) * U;   // first unit of this CTA (of this cluster)
-  const int unit = unit0 + (warp >> lgW);
+  const int unit = unit0 + (kWholeCta ? 0 : warp >> lgW);
   const bool has_unit = unit < n_units;
   const int b = has_unit ? unit / p.Hkv : 0, head = has_unit ? unit % p.Hkv : 0;
   const int len = !has_unit ? 0 : p.seq_lens ? min(max(__ldg(p.seq_lens + b), 0), p.n_seq) : p.n_seq;
 
   // this warp's tiles: the unit's tiles are dealt in contiguous runs to its C * W warps
   const int n_tiles = (len + kTile - 1) / kTile;
-  const int part = (int)cta_rank * W + (warp & (W - 1)), parts = C * W;
-  const int t_each = n_tiles >> (lgW + lgC), t_more = n_tiles - t_each * parts;  // the first t_more parts get one more
+  const int part = (int)cta_rank * W + (kWholeCta ? warp : warp & (W - 1)), parts = C * W;
+  const int t_each = kWholeCta ? (n_tiles >> lgC) / NW : n_tiles >> (lgW + lgC);
+  const int t_more = n_tiles - t_each * parts;  // the first t_more parts get one more
   const int t_begin = part * t_each + min(part, t_more), t_end = t_begin + t_each + (part < t_more ? 1 : 0);
   const __nv_bfloat16* kbase = p.k + (long long)b * p.k_sb + (long long)head * p.k_sh;
   const __nv_bfloat16* vbase = p.v + (long long)b * p.v_sb + (long long)head * p.v_sh;
-  const uint32_t buf0 = smem_u32(smem) + warp * kSmSlots * kTileBytes;
+  const uint32_t buf0 = smem_u32(smem) + warp * NS * kTileBytes;
 
   // Copy of one tile: 16-byte chunk c (0..7) of 128-byte row r of half h goes to chunk position c ^ (r & 7).  A
   // pass of the warp covers 4 rows x 8 chunks; lane (r0, c) keeps one pointer per tensor and steps it by 4 rows
   // (the copies are a third of the instructions of a tile otherwise).  Always one commit group per call, empty
-  // past the warp's last tile, so that "all but the newest kSmSlots - 1 groups" is the tile about to be used.
+  // past the warp's last tile, so that "all but the newest NS - 1 groups" is the tile about to be used.
   const uint64_t policy = l2_evict_first_policy();
   const int r0 = lane >> 3, c8 = lane & 7;
   const __nv_bfloat16* klane = kbase + (long long)r0 * p.k_st + c8 * 8;
@@ -154,7 +166,7 @@ flash_decode_small_kernel(const SmallParams p) {
     cp_async_commit();
   };
 #pragma unroll
-  for (int i = 0; i < kSmSlots; ++i) fetch(t_begin + i, i);
+  for (int i = 0; i < NS; ++i) fetch(t_begin + i, i);
 
   // Q^T fragments of the group's query heads (rows >= R are zero)
   uint32_t qb[KS][2];
@@ -176,8 +188,8 @@ flash_decode_small_kernel(const SmallParams p) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // this thread's query rows 2 tig, 2 tig + 1
 
   for (int t = t_begin; t < t_end; ++t) {
-    const int slot = (t - t_begin) % kSmSlots;
-    cp_async_wait<kSmSlots - 1>();
+    const int slot = (t - t_begin) % NS;
+    cp_async_wait<NS - 1>();
     __syncwarp();
     const uint32_t kb = buf0 + slot * kTileBytes, vb = kb + kHalves * kBoxBytes;
     // S^T = K Q^T
@@ -260,7 +272,7 @@ flash_decode_small_kernel(const SmallParams p) {
         mma_bf16(o[mt], a0, a1, a2, a3, pb[kk][0], pb[kk][1]);
       }
     __syncwarp();
-    fetch(t + kSmSlots, slot);
+    fetch(t + NS, slot);
   }
   cp_async_wait<0>();
   __syncthreads();  // every warp is done with its slots: the states go over them
@@ -292,25 +304,25 @@ flash_decode_small_kernel(const SmallParams p) {
 
   // ---- first level: the W states of each of this CTA's units.  Every thread folds them for its output elements
   //      (weights recomputed per element: a table built by a few threads first was slower by 0.5 us) ----
-  float* cstate = states + kSmWarps * kStateFloats;  // [R * D] unnormalised sums, then m[8], l[8] (used with C > 1)
+  float* cstate = states + NW * kStateFloats;  // [R * D] unnormalised sums, then m[8], l[8] (used with C > 1)
   const int RD = R * D;
   for (int u = 0; u < U; ++u) {
     const bool live = unit0 + u < n_units;
     const int ub = live ? (unit0 + u) / p.Hkv : 0, uh = live ? (unit0 + u) - ub * p.Hkv : 0;
     const float* s0 = states + (u * W) * kStateFloats;
-    for (int r = threadIdx.x; r < RD && live; r += 32 * kSmWarps) {
+    for (int r = threadIdx.x; r < RD && live; r += 32 * NW) {
       const int row = r / D, col = r - row * D;
-      float m_w[kSmWarps];
+      float m_w[NW];
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < kSmWarps; ++w) {
+      for (int w = 0; w < NW; ++w) {
         m_w[w] = w < W ? s0[w * kStateFloats + 8 * D + row] : -INFINITY;
         M = fmaxf(M, m_w[w]);
       }
       const float Mu = M == -INFINITY ? 0.f : M;
       float L = 0.f, acc = 0.f;
 #pragma unroll
-      for (int w = 0; w < kSmWarps; ++w)
+      for (int w = 0; w < NW; ++w)
         if (w < W) {
           const float wgt = fast_exp2(m_w[w] - Mu);
           L = fmaf(s0[w * kStateFloats + 8 * D + 8 + row], wgt, L);
@@ -338,7 +350,7 @@ flash_decode_small_kernel(const SmallParams p) {
   cluster_sync();
   const uint32_t cs = smem_u32(cstate);
   const int share = RD >> lgC;  // D is a multiple of 64 and C at most 8
-  for (int r = (int)cta_rank * share + (int)threadIdx.x; r < ((int)cta_rank + 1) * share && has_unit; r += 32 * kSmWarps) {
+  for (int r = (int)cta_rank * share + (int)threadIdx.x; r < ((int)cta_rank + 1) * share && has_unit; r += 32 * NW) {
     const int row = r / D, col = r - row * D;
     float m_c[8], l_c[8], a_c[8];
 #pragma unroll
@@ -387,10 +399,12 @@ int configure_small_kernel(int D) {
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   } else {
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
     L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   }
   if (dev >= 0 && dev < 64) configured[di][dev] = true;
   return L3CI_OK;
@@ -408,7 +422,7 @@ int max_active_clusters(int D, int C) {
   if (configure_small_kernel(D) == L3CI_OK) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(C * 64));
-    cfg.blockDim = dim3(32 * kSmWarps);
+    cfg.blockDim = dim3(32 * kClWarps);
     cfg.dynamicSmemBytes = kSmallSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -417,8 +431,8 @@ int max_active_clusters(int D, int C) {
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = D == 64 ? cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<64, true, true>, &cfg)
-                                  : cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<128, true, true>, &cfg);
+    const cudaError_t e = D == 64 ? cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<64, true, true, true>, &cfg)
+                                  : cudaOccupancyMaxActiveClusters(&n, flash_decode_small_kernel<128, true, true, true>, &cfg);
     if (e != cudaSuccess) {
       (void)cudaGetLastError();
       n = 0;
@@ -445,7 +459,7 @@ bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool r
   const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
   const int sms = sm_count();
   if (sms <= 0 || Hq / Hkv > 8) return false;
-  return fd_static_applies(unit_split(units, tiles, sms, D), units, D, n_seq, Hq / Hkv, ragged);
+  return fd_static_applies(unit_split(units, tiles, sms, D), units, tiles, D, n_seq, Hq / Hkv, ragged);
 }
 
 int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {
@@ -505,7 +519,8 @@ int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)s.ctas);
-  cfg.blockDim = dim3(32 * kSmWarps);
+  const bool wide = fd_static_wide(s, tiles);
+  cfg.blockDim = dim3(32 * (wide ? kClWarps : kSmWarps));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -515,8 +530,10 @@ int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true>, p)
-                                   : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true>, p);
+  const cudaError_t e = wide ? (a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true, true>, p)
+                                          : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true, true>, p))
+                             : (a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true, false>, p)
+                                           : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true, false>, p));
   if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));
   return L3CI_OK;
 }

@@ -28,7 +28,7 @@ int plan_static(int B, int Hq, int Hkv, int D, int n_seq, int ragged, int sms, c
   const long long tiles = ((long long)n_seq + fd_tile_tokens(D) - 1) / fd_tile_tokens(D);
   const FdStaticSplit s = fd_static_split(units, tiles, sms, max_clusters);
   out[0] = s.W; out[1] = s.C; out[2] = s.ctas;
-  return fd_static_applies(s, units, D, n_seq, Hq / Hkv, ragged != 0) ? 1 : 0;
+  return fd_static_applies(s, units, tiles, D, n_seq, Hq / Hkv, ragged != 0) ? 1 : 0;
 }
 
 // Returns 0 if all invariants hold, else a positive code; info[0..3] receive details.

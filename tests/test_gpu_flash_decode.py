@@ -94,9 +94,10 @@ def test_kernel_choice_names_the_split_the_call_takes(capi, device):
         # the reference's own example and a batched step of 2048-token caches: static deal, one CTA per unit
         assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 64, 256, 0) == 16 + 8
         assert lib.l3ci_flash_decode_kernel_choice(16, 32, 8, 128, 2048, 1) == 16 + 8
-        # few long units: clusters; very long or possibly lopsided ones, or 16 query heads per KV head: persistent grid
+        # few long units: clusters; longer still or possibly lopsided ones, or 16 query heads per KV head: persistent grid
         assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 16384, 0) == 16 * 8 + 8
-        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 131072, 0) == 0
+        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 131072, 0) == 16 * 8 + 8
+        assert lib.l3ci_flash_decode_kernel_choice(1, 32, 8, 128, 262144, 0) == 0
         assert lib.l3ci_flash_decode_kernel_choice(16, 32, 8, 128, 8192, 1) == 0
         assert lib.l3ci_flash_decode_kernel_choice(2, 32, 2, 128, 512, 0) == 0
         # many short units share CTAs
