@@ -176,7 +176,7 @@ inline bool fd_static_wide(const FdStaticSplit& s, long long tiles) { return s.C
 
 // Whether a call goes to the static kernel, from host-side sizes only.  Fits to measurements on a B200, bytes per
 // microsecond: the static kernel starts in about 4 us, an SM takes in up to 96e3 (256-byte rows, head size 128) or
-// 73e3 (128-byte rows, head size 64), 105e3 / 100e3 in the 12-warp shape, all SMs together 6.9e6; the persistent
+// 73e3 (128-byte rows, head size 64), 105e3 / 100e3 in the 12-warp shape, all SMs together 6.5e6; the persistent
 // kernel, when large, takes 14.8 us plus the bytes at 7.3e6.  Shares (bytes of cache per CTA, from the cache
 // length) up to 1 MB always go static, up to 9 MB if the estimates say so; with device-side lengths (ragged)
 // the share is held to 1.25 MB, because one long sequence among short ones would keep a single CTA busy.
@@ -187,7 +187,7 @@ inline bool fd_static_applies(const FdStaticSplit& s, long long units, long long
   const double cta_bytes = unit_bytes * (kFdStaticWarps / s.W) / s.C;
   if (cta_bytes > (ragged ? 1.25e6 : 9.0e6)) return false;
   if (cta_bytes <= 1.0e6) return true;
-  const double all = 6.9e6 / s.ctas;
+  const double all = 6.5e6 / s.ctas;
   const double one = fd_static_wide(s, tiles) ? (head_size == 64 ? 100e3 : 105e3) : (head_size == 64 ? 73e3 : 96e3);
   const double t_static = 4.0 + cta_bytes / (one < all ? one : all);
   const double t_persistent = 14.8 + unit_bytes * (double)units / 7.3e6;

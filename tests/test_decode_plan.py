@@ -119,6 +119,8 @@ def test_static_split_of_the_benchmark_shapes(plan):
     assert static_deal(plan, 2, 32, 2, 128, 512)[0] is False                    # 16 query heads per KV head
     assert static_deal(plan, 1, 32, 8, 64, 131072)[0] is True                   # long runs: the 12-warp shape keeps up
     assert static_deal(plan, 200, 8, 8, 64, 128)[0] is False                    # 1600 units: more than one wave
+    assert static_deal(plan, 16, 32, 8, 128, 8192) == (True, 8, 1, 128)         # 4 MB per CTA: level with the persistent kernel
+    assert static_deal(plan, 16, 32, 8, 128, 16384)[0] is False                 # 8 MB per CTA at the shared memory rate
 
 
 def test_static_split_invariants(plan):
