@@ -24,9 +24,13 @@ constexpr int kRopeBlock = 256;   // pair kernel: one thread per rotation pair
 constexpr int kTokenBlock = 128;  // token kernels: threads stride over one token's vectors
 constexpr int kTokenBatch = 4;    // 16-byte loads a thread has in flight
 
+// One rotation, rounded exactly as the reference's compiled kernel rounds it: nvcc contracts each of
+// `x*c - y*s` and `x*s + y*c` (custom_kernels/custom_kernels.cu:408,410) into a rounded product of the second
+// term and a fused multiply-add of the first.  Written with explicit intrinsics so that the form does not depend
+// on this file's compiler flags; outputs are bit-identical to the reference kernel's on the same inputs.
 __device__ __forceinline__ void rotate_pair(float x, float y, float c, float s, float& xo, float& yo) {
-  xo = __fsub_rn(__fmul_rn(x, c), __fmul_rn(y, s));
-  yo = __fadd_rn(__fmul_rn(x, s), __fmul_rn(y, c));
+  xo = __fmaf_rn(x, c, -__fmul_rn(y, s));
+  yo = __fmaf_rn(x, s, __fmul_rn(y, c));
 }
 
 // Rotates the 8 bf16 of `v` with the table entries freq8[0..7] = (c0,s0,c1,s1,c2,s2,c3,s3).

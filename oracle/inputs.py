@@ -76,3 +76,30 @@ def prefill_case(B: int, Hq: int, Hkv: int, D: int, T: int, seed: int = 42):
     k = torch.randn(B, T, Hkv, D, generator=g).bfloat16().transpose(1, 2)
     v = torch.randn(B, T, Hkv, D, generator=g).bfloat16().transpose(1, 2)
     return q, k, v
+
+
+def rms_case(B: int, S: int, E: int, seed: int):
+    """x [B,S,E] ~ N(0,1) and weight [E] ~ N(1,0.02) in bf16: the operands of `rms_norm(input, weight, eps)`
+    (custom_kernels/custom_kernels.cu:369-373) for a shape other than config 4's."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, S, E, generator=g).bfloat16()
+    w = (1.0 + 0.02 * torch.randn(E, generator=g)).bfloat16()
+    return x, w
+
+
+def rope_case(B: int, S: int, H: int, D: int, seed: int, extra_heads: int = 0):
+    """x [B,S,H,D] ~ N(0,1) in bf16, the operand of `rot_embed(input, freq)` (custom_kernels.cu:418-427).  With
+    `extra_heads` the tensor is a strided view of a wider [B,S,(H+extra_heads)*D] buffer, as q and k are views
+    of the fused projection output (model.py:95-97)."""
+    g = torch.Generator().manual_seed(seed)
+    buf = torch.randn(B, S, (H + extra_heads) * D, generator=g).bfloat16()
+    return buf[..., : H * D].view(B, S, H, D)
+
+
+# name -> (B, S, E, seed) of rms_case / (B, S, H, D, seed, extra_heads) of rope_case: the small shapes whose
+# reference-CUDA outputs are held whole in tests/golden/reference_cuda_vectors.pt
+RMS_GOLDEN_CASES = {"e64": (1, 3, 64, 31), "e512": (2, 5, 512, 32), "e2048_decode": (4, 1, 2048, 33),
+                    "e4096": (3, 7, 4096, 34), "e8192": (1, 2, 8192, 35)}
+ROPE_GOLDEN_CASES = {"d64": (1, 5, 3, 64, 41, 0), "d128_strided": (2, 17, 4, 128, 42, 2), "d64_decode": (8, 1, 32, 64, 43, 16)}
+# rows of config 4 whose reference-CUDA outputs are held (the whole outputs are 17 MB each)
+C4_GOLDEN_ROW_STEP = 64

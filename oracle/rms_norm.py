@@ -16,6 +16,17 @@ def rms_norm_reference(x: torch.Tensor, weight: torch.Tensor, eps: float) -> tor
     return ((xf * inv) * wf).to(torch.bfloat16)
 
 
+def rms_norm_reference_rounding(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm with the rounding order of the reference's kernel: the sum of squares in fp32
+    (custom_kernels/custom_kernels.cu:354-360), then `inv = bf16(rsqrt(ss / E + eps))` (:362) and
+    `out = bf16(bf16(inv * w) * x)` (:365, two bf16 multiplications evaluated left to right).  Three roundings
+    where `rms_norm_reference` has one; the two differ by at most 2 bf16 ulp."""
+    xf = x.detach().cpu().float()
+    inv = torch.rsqrt(xf.pow(2).sum(dim=-1, keepdim=True) / x.shape[-1] + eps).to(torch.bfloat16)
+    iw = (inv.float() * weight.detach().cpu().float()).to(torch.bfloat16)
+    return (iw.float() * xf).to(torch.bfloat16)
+
+
 def add_rms_norm_reference(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
     """(s, rmsnorm(s)) with s = x + residual as a bf16 tensor add gives it: Block.forward's residual add
     followed by the next norm (model.py:147-148), the two steps kept separate as the reference runs them."""

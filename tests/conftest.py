@@ -56,6 +56,14 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def ref_cuda():
+    """Outputs of the reference's own CUDA kernels (tests/golden/make_reference_cuda_golden.py)."""
+    import torch
+
+    return torch.load(REPO / "tests" / "golden" / "reference_cuda_vectors.pt")
+
+
+@pytest.fixture(scope="session")
 def device():
     import torch
 

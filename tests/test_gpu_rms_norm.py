@@ -1,4 +1,5 @@
-"""RMSNorm kernel through the C ABI against the fp32 oracle: at most 1 bf16 ulp."""
+"""RMSNorm kernel through the C ABI against the fp32 oracle: at most 1 bf16 ulp; and against the outputs of the
+reference's own CUDA kernel, which rounds three times in bf16: at most 2 bf16 ulp."""
 import pytest
 import torch
 
@@ -105,3 +106,19 @@ def test_fused_errors(capi, device):
     assert lib.l3ci_add_rms_norm(p, p + 2, p, p, p, 1, 8, 1e-5, None) == capi.ERR_ALIGNMENT
     assert lib.l3ci_silu_mul(p, p, p, 1, 12, 12, 12, None) == capi.ERR_ALIGNMENT
     assert lib.l3ci_silu_mul(p, p, p, 0, 8, 8, 8, None) == capi.OK
+
+
+@pytest.mark.parametrize("name", sorted(inputs.RMS_GOLDEN_CASES) + ["c4_rows"])
+def test_within_two_ulp_of_the_reference_kernels_output(capi, device, ref_cuda, name):
+    """The reference kernel rounds the inverse RMS, its product with the weight and the final product to bf16
+    (custom_kernels/custom_kernels.cu:362,365); this kernel rounds once.  Measured on the held vectors: the two
+    differ by at most 2 ulp, in under 1 % of the elements by more than 1."""
+    if name == "c4_rows":
+        x, w, eps, _ = inputs.config4(seed=42)
+        got = capi.rms_norm(x.to(device), w.to(device), eps).view(-1, x.shape[-1])[:: inputs.C4_GOLDEN_ROW_STEP].contiguous()
+    else:
+        x, w = inputs.rms_case(*inputs.RMS_GOLDEN_CASES[name])
+        got = capi.rms_norm(x.to(device), w.to(device), 1e-5)
+    torch.cuda.synchronize()
+    d = compare.bf16_ulp_distance(got.cpu(), ref_cuda["rms/" + name])
+    assert int(d.max()) <= 2 and float((d > 1).float().mean()) < 0.01

@@ -1,5 +1,6 @@
-"""Rotary-embedding kernels through the C ABI against the unfused-fp32 oracle.  The stated tolerance is
-1 bf16 ulp; the kernel evaluates the same unfused fp32 formula, so the results are expected identical."""
+"""Rotary-embedding kernels through the C ABI against the oracle, which is bit-equal to the reference's compiled
+kernel (tests/test_oracle_reference_cuda.py).  The stated tolerance is 1 bf16 ulp; the kernel evaluates the same
+fp32 expression with the same roundings, so the results are expected identical."""
 import pytest
 import torch
 
@@ -109,3 +110,24 @@ def test_errors(capi, device):
     f = torch.zeros(64, device=device)
     assert lib.l3ci_rot_embed(x.data_ptr() + 2, f.data_ptr(), x.data_ptr(), 1, 1, 1, 8, 8, 8, 8, None) == capi.ERR_ALIGNMENT
     assert lib.l3ci_rot_embed(x.data_ptr(), f.data_ptr(), x.data_ptr(), 1, 1, 1, 7, 7, 7, 7, None) == capi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("which", ["q", "k"])
+def test_config4_is_bit_equal_to_the_reference_kernels_output(capi, device, ref_cuda, which):
+    """Directly against what the reference's own CUDA kernel wrote for configuration 4 on a B200 (every element)."""
+    from test_oracle_reference_cuda import c4_rope_full
+
+    t, freq, full = c4_rope_full(ref_cuda, which)
+    got = capi.rot_embed(t.to(device), freq.to(device))
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), full)
+
+
+@pytest.mark.parametrize("name", sorted(inputs.ROPE_GOLDEN_CASES))
+def test_small_shapes_are_bit_equal_to_the_reference_kernels_output(capi, device, ref_cuda, name):
+    B, S, H, D, seed, extra = inputs.ROPE_GOLDEN_CASES[name]
+    x = inputs.rope_case(B, S, H, D, seed, extra)
+    freq = freqs_cis_reference(D, S, theta=500000.0, use_scaled=True, scale_factor=8)
+    got = capi.rot_embed(x.to(device), freq.to(device))
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), ref_cuda["rope/" + name])
