@@ -46,6 +46,15 @@ L3CI_API const char* l3ci_last_error(void);
 /* Library version, "major.minor.patch". */
 L3CI_API const char* l3ci_version(void);
 
+/* Bound of the device-side waits on OTHER CTAs or OTHER GPUs (the arrival counters of l3ci_flash_decode's
+ * persistent kernel, default 2 s; the peers' flags of l3ci_lse_exchange_merge, default 1 s), in nanoseconds,
+ * for the launches made after this call by any thread of the process; 0 restores the defaults.  Returns the
+ * previous setting.  A wait that runs out makes the kernel give up in order: it records
+ * L3CI_ERR_DEVICE_WAIT (scratch header / status word), skips the rows it could not finish and returns,
+ * so the context stays usable.  A host that watches for a lost peer sets a limit near its step time; the
+ * tests use it to let a wait run out in milliseconds.  No counterpart in the reference (one GPU, no waits). */
+L3CI_API uint64_t l3ci_set_device_wait_limit_ns(uint64_t ns);
+
 /* ------------------------------------------------------------------------------------------
  * RMSNorm.   out[r, :] = bf16( (float(x[r, :]) * rsqrt(mean(x[r, :]^2) + eps)) * float(w) )
  * fp32 arithmetic, one rounding.  Replaces `rms_norm(input, weight, eps)` and

@@ -18,7 +18,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 
 # Every symbol include/l3ci_b200.h declares.
 EXPORTS = (
-    "l3ci_status_string", "l3ci_last_error", "l3ci_version",
+    "l3ci_status_string", "l3ci_last_error", "l3ci_version", "l3ci_set_device_wait_limit_ns",
     "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_flash_decode_kernel_choice",
@@ -81,6 +81,8 @@ def load() -> C.CDLL:
     lib.l3ci_last_error.argtypes = []
     lib.l3ci_version.restype = C.c_char_p
     lib.l3ci_version.argtypes = []
+    lib.l3ci_set_device_wait_limit_ns.restype = C.c_uint64
+    lib.l3ci_set_device_wait_limit_ns.argtypes = [C.c_uint64]
     lib.l3ci_rms_norm.restype = C.c_int
     lib.l3ci_rms_norm.argtypes = [vp, vp, vp, i64, i64, i64, i64, f32, vp]
     lib.l3ci_add_rms_norm.restype = C.c_int
@@ -345,7 +347,7 @@ def lse_merge(o_parts, lse_parts):
 STATIC_SCRATCH_BYTES = 12 << 20  # L3CI_STATIC_SCRATCH_BYTES
 
 
-def flash_attention_decode_static(q, k, v, seq_lens=None, scale: float = 0.0):
+def flash_attention_decode_static(q, k, v, seq_lens=None, scale: float = 0.0, max_ctas: int = 0):
     """`flash_attention_decode` for callers that cannot allocate device memory: the merge scratch is the
     library's built-in array (one per GPU, shared by every call on it; do not overlap calls).  The output
     tensor is still created here because this helper mirrors the reference call form; a caller that owns
@@ -353,7 +355,34 @@ def flash_attention_decode_static(q, k, v, seq_lens=None, scale: float = 0.0):
     import torch
 
     out = torch.empty_like(q)
-    a = flash_decode_args(q, k, v, out=out, seq_lens=seq_lens, scale=scale)
+    a = flash_decode_args(q, k, v, out=out, seq_lens=seq_lens, scale=scale, max_ctas=max_ctas)
     with _on(q):
         _check(load().l3ci_flash_decode_static(C.byref(a)), "l3ci_flash_decode_static")
+    return out
+
+
+class device_wait_limit:
+    """Context manager: device-side waits on other CTAs / GPUs of launches made inside give up after `ns`
+    nanoseconds (l3ci_set_device_wait_limit_ns); the previous setting comes back on exit."""
+
+    def __init__(self, ns: int):
+        self.ns = ns
+
+    def __enter__(self):
+        self.prev = load().l3ci_set_device_wait_limit_ns(self.ns)
+        return self
+
+    def __exit__(self, *exc):
+        load().l3ci_set_device_wait_limit_ns(self.prev)
+        return False
+
+
+def lse_exchange_merge(bufs, rank: int, ranks: int, epoch: int, out, B: int, Hq: int, D: int, status=None):
+    """`l3ci_lse_exchange_merge` over a device int64 tensor of `ranks` buffer addresses; `out` is bf16 [B,Hq,1,D]
+    (any strides over b and h), `status` an optional int32 device word."""
+    with _on(out):
+        _check(load().l3ci_lse_exchange_merge(bufs.data_ptr(), rank, ranks, epoch, out.data_ptr(), B, Hq, D,
+                                              out.stride(0), out.stride(1),
+                                              status.data_ptr() if status is not None else None, _stream(out)),
+               "l3ci_lse_exchange_merge")
     return out

@@ -68,25 +68,6 @@ struct FdCfg {
   static constexpr int KS_PV = kTile / 16; // k-steps of P.V
 };
 
-// Build with -DL3CI_FD_TRACE to record, per warp, %globaltimer at five points of the kernel into a
-// buffer registered with l3ci_debug_set_trace (development aid; absent from normal builds).
-#ifdef L3CI_FD_TRACE
-__device__ unsigned long long* g_fd_trace = nullptr;
-#define FD_TRACE(slot)                                                                       \
-  do {                                                                                       \
-    if (g_fd_trace && lane == 0 && warp < 8) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 32 + (slot)] = global_ns(); \
-  } while (0)
-#define FD_TRACE_VAL(slot, v)                                                                 \
-  do {                                                                                       \
-    if (g_fd_trace && lane == 0 && warp < 8) g_fd_trace[((size_t)blockIdx.x * 8 + warp) * 32 + (slot)] = (v); \
-  } while (0)
-#define FD_TRACE_ONLY(...) __VA_ARGS__
-#else
-#define FD_TRACE(slot) do { } while (0)
-#define FD_TRACE_VAL(slot, v) do { } while (0)
-#define FD_TRACE_ONLY(...)
-#endif
-
 struct FdParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* out;   // may be null
@@ -100,6 +81,7 @@ struct FdParams {
   long long q_sb, q_sh, o_sb, o_sh;
   float scale_log2e;
   int rec_floats;       // floats per record: R * D / 4 chunks of 8
+  unsigned long long wait_ns;  // bound of a wait on other CTAs' arrival counters
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -214,7 +196,6 @@ struct SliceJob {
   }
   // The general form: as many passes over chunks and rounds over records as the job needs.
   __device__ __forceinline__ void run(const FdParams& p, int lane) const {
-    FD_TRACE_ONLY(const int warp = threadIdx.x >> 5; FD_TRACE(7);)
     for (int base = 0; base < q1 - q0; base += per_pass) {
       Chunk4 acc;
       acc.clear();
@@ -223,7 +204,6 @@ struct SliceJob {
         load(ld, base, k0, lane);
         fold(acc, ld);
       }
-      FD_TRACE_ONLY(if (__any_sync(kFullMask, acc.l > 0.f)) FD_TRACE(11);)
       finish(acc, p, base, lane);
     }
   }
@@ -245,7 +225,7 @@ __device__ __forceinline__ bool wait_for_records(const FdParams& p, const int* c
   for (uint32_t it = 0;; ++it) {
     __nanosleep(32);
     if (__all_sync(kFullMask, poll())) return true;
-    if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > kWaitLimitNs)) {
+    if ((it & 15u) == 15u && __any_sync(kFullMask, global_ns() - t0 > p.wait_ns)) {
       if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
       return false;
     }
@@ -267,7 +247,6 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
   const bool on[2] = {def_n[0] > 1, def_n[1] > 1};
   int* const counter[2] = {p.counters + def_b[0] * p.Hkv + def_head[0], p.counters + def_b[1] * p.Hkv + def_head[1]};
   if (!wait_for_records(p, counter, def_n, on, lane)) return;
-  FD_TRACE(14);
   int left[2] = {0, 0};
   if (lane == 0) {
 #pragma unroll
@@ -292,8 +271,6 @@ __device__ __noinline__ void merge_shared_units(const FdParams& p, const int* de
     if (on[0]) job[0].run(p, lane);
     if (on[1]) job[1].run(p, lane);
   }
-  FD_TRACE(15);
-  FD_TRACE_ONLY(if (on[0] && !on[1]) { FD_TRACE(16); job[0].run(p, lane); FD_TRACE(17); })
   if (lane == 0) {
 #pragma unroll
     for (int w = 0; w < 2; ++w)
@@ -322,7 +299,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   const int HG = (blockDim.x >> 5) - 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  FD_TRACE(0);
   const int gid = lane >> 2;  // MMA row within the 8-row half
   const int tig = lane & 3;   // MMA column pair
 
@@ -468,7 +444,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     return;
   }
 
-  FD_TRACE(1);
   FdCursor cons = wk.seek(c0);
 
   // ---- lane constants of the ldmatrix addresses ----
@@ -499,7 +474,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   bool ok = true;
   int def_b[2] = {0, 0}, def_head[2] = {0, 0}, def_first[2] = {0, 0}, def_n[2] = {0, 0};  // shared units to merge at the end
 
-  FD_TRACE_ONLY(long long trace_wait = 0, trace_c0 = 0, tr_qk = 0, tr_sm = 0, tr_pv = 0, tr_t = 0;)
   // S^T = K Q^T for the kTile tokens of the tile at kb.  The k-steps are dealt to kChains accumulator sets that
   // are added at the end, so that no tensor-core instruction waits on more than one predecessor.
   auto qk_scores = [&](uint32_t kb, float (&sc)[NB][MB][4]) {
@@ -593,10 +567,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     const uint32_t kb = stage0 + stage * cta_stage_bytes + warp * C::kBoxBytes;
     const uint32_t vb = kb + HG * C::kKBytes;
     if (!have_s) {
-      FD_TRACE_ONLY(const long long tw0 = clock64();)
       if (!mbar_wait_bounded(full0 + stage * 8, (k_iter / kStages) & 1)) { ok = false; break; }
-      FD_TRACE_ONLY(trace_wait += clock64() - tw0; if (k_iter == 0) trace_c0 = clock64();)
-      if (k_iter == 0) FD_TRACE(2);
       qk_scores(kb, s);
     }
     // Scores of the next tile, when it continues this unit: its K is normally in shared memory already, and its
@@ -607,14 +578,9 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     float s_next[NB][MB][4];
     if (ahead) {
       const int st2 = (k_iter + 1) % kStages;
-      FD_TRACE_ONLY(const long long tw0 = clock64();)
       if (!mbar_wait_bounded(full0 + st2 * 8, ((k_iter + 1) / kStages) & 1)) { ok = false; break; }
-      FD_TRACE_ONLY(trace_wait += clock64() - tw0;)
-      FD_TRACE_ONLY(tr_t = clock64();)
       qk_scores(stage0 + st2 * cta_stage_bytes + warp * C::kBoxBytes, s_next);
-      FD_TRACE_ONLY(tr_qk += clock64() - tr_t;)
     }
-    FD_TRACE_ONLY(tr_t = clock64();)
 
     // ---- mask the tail of the sequence, online softmax (log2 domain) ----
     const int tok0 = cons.j * C::kTile;
@@ -675,7 +641,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
         }
     }
 
-    FD_TRACE_ONLY(tr_sm += clock64() - tr_t; tr_t = clock64();)
     // ---- O^T += V^T P^T ----
 #pragma unroll
     for (int kk = 0; kk < MB; ++kk) {
@@ -689,7 +654,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       }
     }
 
-    FD_TRACE_ONLY(tr_pv += clock64() - tr_t;)
     // ---- release the stage to the producer ----
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + stage * 8);
@@ -773,13 +737,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
     if (lane == 0) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
     return;
   }
-  FD_TRACE(3);
-  FD_TRACE_VAL(8, (unsigned long long)trace_wait);
-  FD_TRACE_VAL(9, (unsigned long long)(clock64() - trace_c0));
-  FD_TRACE_VAL(10, (unsigned long long)k_iter);
-  FD_TRACE_VAL(11, (unsigned long long)tr_qk);
-  FD_TRACE_VAL(12, (unsigned long long)tr_sm);
-  FD_TRACE_VAL(13, (unsigned long long)tr_pv);
   // ---- shared units ----
   // Announce this warp's records (one fence for both), then merge this CTA's slice of each unit once every
   // participant has announced.
@@ -791,11 +748,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       for (int w = 0; w < 2; ++w)
         if (def_n[w] > 1) atomicAdd(p.counters + def_b[w] * p.Hkv + def_head[w], 1);
     }
-    FD_TRACE(5);
     merge_shared_units<D>(p, def_b, def_head, def_first, def_n, cta, HG, warp, lane);
-    FD_TRACE(6);
   }
-  FD_TRACE(4);
 }
 
 // Writes zeros for a call without any cached token.
@@ -880,12 +834,6 @@ int launch_fd(const CUtensorMap& kmap, const CUtensorMap& vmap, const FdParams& 
 }  // namespace
 }  // namespace l3ci
 
-#ifdef L3CI_FD_TRACE
-extern "C" __attribute__((visibility("default"))) int l3ci_debug_set_trace(unsigned long long* buf) {
-  return (int)cudaMemcpyToSymbol(l3ci::g_fd_trace, &buf, sizeof(buf));
-}
-#endif
-
 extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t Hkv, int32_t D) {
   using namespace l3ci;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || Hq % Hkv) return 0;
@@ -899,6 +847,15 @@ extern "C" size_t l3ci_flash_decode_scratch_bytes(int32_t B, int32_t Hq, int32_t
 
 namespace l3ci {
 namespace {
+// Whether a call with valid sizes goes to the static-deal kernel, which uses no scratch (the one rule for
+// l3ci_flash_decode and l3ci_flash_decode_static).
+bool takes_static_deal(const l3ci_flash_decode_args* a) {
+  if (a->B <= 0 || a->Hkv <= 0 || a->Hq <= 0 || a->Hq % a->Hkv || a->n_seq <= 0 || (a->D != 64 && a->D != 128)) return false;
+  const int R = a->Hq / a->Hkv;
+  if (a->max_ctas < 0) return R <= 8;
+  return a->max_ctas == 0 && flash_decode_small_applies(a->B, a->Hq, a->Hkv, a->D, a->n_seq, a->seq_lens != nullptr);
+}
+
 // Validates the arguments and launches; `a->scratch` must already be what the call may use.
 int flash_decode_launch(const l3ci_flash_decode_args* a) {
   clear_error();
@@ -946,16 +903,15 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if (max_cols < grid) grid = (int)max_cols;
 
+  // Where the static deal of units to warps, CTAs or clusters is expected to be faster (flash_decode_small.cu),
+  // nothing goes through global memory and the scratch is neither needed nor touched.  A positive max_ctas asks
+  // for the persistent kernel.
+  if (takes_static_deal(a)) return flash_decode_small_launch(a, a->max_ctas < -1 ? -a->max_ctas : 0);
+
   const size_t need = l3ci_flash_decode_scratch_bytes(B, Hq, Hkv, D);
   if (!a->scratch || a->scratch_bytes < need)
     return fail(L3CI_ERR_SCRATCH, "flash_decode: scratch has %zu bytes, needs %zu", a->scratch_bytes, need);
   if (reinterpret_cast<uintptr_t>(a->scratch) & 255) return fail(L3CI_ERR_ALIGNMENT, "flash_decode: scratch must be 256-byte aligned");
-
-  // Where the static deal of units to warps, CTAs or clusters is expected to be faster (flash_decode_small.cu),
-  // nothing goes through global memory and the scratch stays untouched.  A positive max_ctas asks for the
-  // persistent kernel.
-  if ((a->max_ctas == 0 && flash_decode_small_applies(B, Hq, Hkv, D, n_seq, ragged)) || (a->max_ctas < 0 && R <= 8))
-    return flash_decode_small_launch(a, a->max_ctas < -1 ? -a->max_ctas : 0);
 
   const size_t smem = smem_bytes(HG, B, ragged);
   if ((long long)smem > max_smem_optin()) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode: needs %zu bytes of shared memory", smem);
@@ -979,6 +935,7 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
   const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)D);
   p.scale_log2e = scale * 1.4426950408889634f;
   p.rec_floats = record_floats(R, D);
+  p.wait_ns = device_wait_limit_ns(kWaitLimitNs);
 
   if (D == 64) {
     return R > 8 ? launch_fd<64, true>(kmap, vmap, p, grid, HG, smem, stream)
@@ -1009,8 +966,10 @@ static __device__ __align__(256) unsigned char g_fd_static_scratch[L3CI_STATIC_S
 namespace l3ci {
 namespace {
 // Device address of g_fd_static_scratch on the current device, looked up once per device (with that
-// device current) and remembered.
-int static_scratch_address(void** out) {
+// device current) and remembered.  The first look-up on a device may make the runtime load this library's
+// device image, array included; inside a stream capture that is refused here with a clear message rather
+// than left to fail in the driver.
+int static_scratch_address(void** out, cudaStream_t stream) {
   static void* address[64] = {nullptr};
   static std::mutex mu;
   int dev = 0;
@@ -1018,6 +977,11 @@ int static_scratch_address(void** out) {
   if (dev < 0 || dev >= 64) return fail(L3CI_ERR_UNSUPPORTED, "flash_decode_static: device index %d", dev);
   std::lock_guard<std::mutex> lock(mu);
   if (!address[dev]) {
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) (void)cudaGetLastError();
+    if (capturing != cudaStreamCaptureStatusNone)
+      return fail(L3CI_ERR_INVALID, "flash_decode_static: the first call on a device looks up the built-in scratch "
+                                    "and must be made outside a stream capture");
     void* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&ptr, g_fd_static_scratch);
     if (e != cudaSuccess || !ptr)
@@ -1035,24 +999,24 @@ extern "C" int l3ci_flash_decode_static(const l3ci_flash_decode_args* a) {
   clear_error();
   if (!a) return fail(L3CI_ERR_INVALID, "flash_decode_static: null args");
   if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv) return flash_decode_launch(a);  // reports the bad size
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+  void* area = nullptr;
+  if (int st = static_scratch_address(&area, stream)) return st;
+  l3ci_flash_decode_args b = *a;
+  b.scratch = area;
+  b.scratch_bytes = (size_t)L3CI_STATIC_SCRATCH_BYTES;
+  // A call that the static-deal kernel takes needs no scratch at all: no size limit applies, nothing is cleared.
+  if (takes_static_deal(a)) return flash_decode_launch(&b);
   const size_t need = l3ci_flash_decode_scratch_bytes(a->B, a->Hq, a->Hkv, a->D);
   if (need == 0 || need > (size_t)L3CI_STATIC_SCRATCH_BYTES || (size_t)a->B * a->Hkv > kFixedCounters)
     return fail(L3CI_ERR_SCRATCH,
                 "flash_decode_static: this shape needs %zu bytes of scratch (B*Hkv = %lld units), the built-in area holds "
                 "%zu bytes and %zu units; use l3ci_flash_decode with caller-provided scratch",
                 need, (long long)a->B * a->Hkv, (size_t)L3CI_STATIC_SCRATCH_BYTES, kFixedCounters);
-  void* area = nullptr;
-  if (int st = static_scratch_address(&area)) return st;
   // The area keeps whatever the previous call (of any shape) left.  Records are written before they are read;
   // the status word and the arrival counters of this call's units must start at zero.
-  // (The kernel for short caches uses no scratch.)
-  const bool small = a->max_ctas == 0 && a->n_seq > 0 && (a->D == 64 || a->D == 128) &&
-                     flash_decode_small_applies(a->B, a->Hq, a->Hkv, a->D, a->n_seq, a->seq_lens != nullptr);
   const size_t clear = kHeaderBytes + (((size_t)a->B * a->Hkv * sizeof(int) + 255) & ~(size_t)255);
-  if (!small) L3CI_CUDA_TRY(cudaMemsetAsync(area, 0, clear, reinterpret_cast<cudaStream_t>(a->stream)));
-  l3ci_flash_decode_args b = *a;
-  b.scratch = area;
-  b.scratch_bytes = (size_t)L3CI_STATIC_SCRATCH_BYTES;
+  L3CI_CUDA_TRY(cudaMemsetAsync(area, 0, clear, stream));
   return flash_decode_launch(&b);
 }
 

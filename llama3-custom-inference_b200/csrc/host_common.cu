@@ -3,6 +3,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
+
 namespace l3ci {
 
 namespace {
@@ -10,7 +12,13 @@ thread_local char g_err[512] = {0};
 constexpr int kMaxDev = 64;
 int g_sms[kMaxDev] = {0};
 int g_smem[kMaxDev] = {0};
+std::atomic<unsigned long long> g_wait_limit_ns{0};  // 0: every kernel's own default
 }  // namespace
+
+unsigned long long device_wait_limit_ns(unsigned long long default_ns) {
+  const unsigned long long v = g_wait_limit_ns.load(std::memory_order_relaxed);
+  return v ? v : default_ns;
+}
 
 int fail(int status, const char* fmt, ...) {
   va_list ap;
@@ -67,6 +75,10 @@ const char* l3ci_status_string(int status) {
 
 const char* l3ci_last_error(void) { return l3ci::g_err; }
 
-const char* l3ci_version(void) { return "0.1.0"; }
+const char* l3ci_version(void) { return "0.2.0"; }
+
+uint64_t l3ci_set_device_wait_limit_ns(uint64_t ns) {
+  return l3ci::g_wait_limit_ns.exchange(ns, std::memory_order_relaxed);
+}
 
 }  // extern "C"

@@ -28,6 +28,10 @@ int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code);
 // 16 * C + W of the split the static kernel would take for these sizes on the current device.
 int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq);
 
+// Bound, in nanoseconds, of a device-side wait on other CTAs or other GPUs: the value set through
+// l3ci_set_device_wait_limit_ns, else `default_ns`.
+unsigned long long device_wait_limit_ns(unsigned long long default_ns);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 #define L3CI_CUDA_TRY(expr)                                                              \

@@ -67,7 +67,7 @@ lse_merge_kernel(const float* __restrict__ o, const float* __restrict__ lse, __n
 // back (control word 1 counts the finished warps).  A launch sequence without any host-side state can be
 // captured in a CUDA graph and replayed.
 // ---------------------------------------------------------------------------------------------
-constexpr unsigned long long kXchgWaitNs = 1000000000ull;  // bound of the wait for the peers' rows
+constexpr unsigned long long kXchgWaitNs = 1000000000ull;  // default bound of the wait for the peers' rows
 
 __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   unsigned v;
@@ -85,7 +85,8 @@ __device__ __forceinline__ unsigned long long xchg_ns() {
 
 __global__ void __launch_bounds__(kMergeBlock)
 lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsigned epoch_arg, long long rows, int Hq,
-                          int D, __nv_bfloat16* __restrict__ out, long long o_sb, long long o_sh, int* status) {
+                          int D, __nv_bfloat16* __restrict__ out, long long o_sb, long long o_sh, int* status,
+                          unsigned long long wait_ns) {
   const long long row = (long long)blockIdx.x * (kMergeBlock / kWarp) + threadIdx.x / kWarp;
   const int lane = threadIdx.x % kWarp;
   if (row >= rows) return;
@@ -138,7 +139,7 @@ lse_exchange_merge_kernel(float* const* __restrict__ bufs, int rank, int W, unsi
         if (s != rank && ld_acquire_sys_u32(flag(local, s)) != epoch) there = false;
       if (__all_sync(kFullMask, there)) break;
       __nanosleep(64);
-      if ((it & 15u) == 15u && __any_sync(kFullMask, xchg_ns() - t0 > kXchgWaitNs)) { late = true; break; }
+      if ((it & 15u) == 15u && __any_sync(kFullMask, xchg_ns() - t0 > wait_ns)) { late = true; break; }
     }
     if (late) {
       if (lane == 0 && status) atomicExch(status, (int)L3CI_ERR_DEVICE_WAIT);
@@ -200,7 +201,7 @@ extern "C" int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t 
   const long long ctas = (rows + kMergeBlock / kWarp - 1) / (kMergeBlock / kWarp);
   lse_exchange_merge_kernel<<<(unsigned)ctas, kMergeBlock, 0, stream>>>(
       reinterpret_cast<float* const*>(bufs), rank, ranks, epoch, rows, Hq, D, static_cast<__nv_bfloat16*>(out), o_sb,
-      o_sh, status);
+      o_sh, status, device_wait_limit_ns(kXchgWaitNs));
   L3CI_CHECK_LAUNCH("lse_exchange_merge_kernel");
   return L3CI_OK;
 }

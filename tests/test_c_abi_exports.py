@@ -78,7 +78,7 @@ def test_extension_module_mirrors_reference_binding(ext):
         assert callable(getattr(ext, name))
     for name in ("rot_embed_kv_cache", "flash_attention_decode_partial", "lse_merge", "flash_decode_status"):
         assert callable(getattr(ext, name))
-    assert ext.c_abi_version() == "0.1.0"
+    assert ext.c_abi_version() == "0.2.0"
     x = torch.zeros(1, 2, 8, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="CUDA tensor"):  # no CPU fallback: CPU tensors are refused
         ext.rms_norm(x, torch.ones(8, dtype=torch.bfloat16), 1e-5)
@@ -87,3 +87,10 @@ def test_extension_module_mirrors_reference_binding(ext):
         ext.flash_attention_decode(q, q, q)
     with pytest.raises(RuntimeError):
         ext.rot_embed(torch.zeros(1, 1, 1, 64, dtype=torch.bfloat16), torch.zeros(1, 64))
+
+
+def test_device_wait_limit_setter_round_trips(capi):
+    lib = capi.load()
+    prev = lib.l3ci_set_device_wait_limit_ns(123)
+    assert lib.l3ci_set_device_wait_limit_ns(prev) == 123
+    assert lib.l3ci_set_device_wait_limit_ns(prev) == prev

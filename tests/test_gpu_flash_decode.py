@@ -258,9 +258,11 @@ def test_error_statuses(capi, device):
     case = inputs.decode_case(1, 8, 2, 128, 64, seed=19).to(device)
     out = torch.empty_like(case.q)
     scratch = capi.DecodeScratch(1, 8, 2, 128, device)
-    a = capi.flash_decode_args(case.q, case.k, case.v, out=out, scratch=scratch)
-    a.scratch_bytes = 128
+    a = capi.flash_decode_args(case.q, case.k, case.v, out=out, scratch=scratch, max_ctas=148)
+    a.scratch_bytes = 128     # the persistent kernel needs its scratch ...
     assert lib.l3ci_flash_decode(C.byref(a)) == capi.ERR_SCRATCH
+    a = capi.flash_decode_args(case.q, case.k, case.v, out=out, max_ctas=-1)
+    assert lib.l3ci_flash_decode(C.byref(a)) == capi.OK   # ... the static-deal kernel none at all
     a = capi.flash_decode_args(case.q, case.k[..., 8:], case.v, out=out, scratch=scratch)
     a.D = 128
     a.k = case.k.data_ptr() + 2
