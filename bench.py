@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|rmsnorm|rope] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|rmsnorm|rope|c5|prefill]
+                    [--impl ours|reference]
 
 One "step" is one pass of the hot path over one batch of synthetic input: for the default workload (C2) one
 `flash_attention_decode` call over a ragged batch of 16 sequences (32 q / 8 kv heads, head size 128, lengths
@@ -11,19 +12,29 @@ in decimal GB/s.
 
 Printed JSON line (rank 0):
   value          GB/s over all GPUs with inputs resident in HBM; K steps timed as one region with CUDA events
-                 on the launching stream, barrier + synchronize on both sides, max over ranks
+                 on the launching stream, barrier + synchronize on both sides, max over ranks.  A region
+                 shorter than 50 ms is repeated (each repeat bracketed the same way) and the median region is
+                 reported, with the minimum and maximum beside it (`regions`)
   e2e            the same metric through the extension module with HOST inputs: every step copies q, k, v
                  (and seq_lens) from pinned host memory, runs the kernel and reads the output back
   roofline       achieved algorithmic GB/s of the flash-decode kernel against the measured HBM copy bandwidth
   cpu_baseline   the reference's PyTorch attention path (scaled_dot_product_attention, bf16, on the CPU tensors)
-                 timed on this box's host cores over a bounded number of passes
+                 timed on this box's host cores over a bounded number of passes (rank 0)
   clocks         SM clock and throttle reasons sampled through NVML while the GPU was busy
+  c3             (default workload only, every N) the long-context step: 131072 cached tokens of one sequence,
+                 KV sequence sharded over the N ranks, per-rank decode kernel + fused NVLink exchange/merge;
+                 rank 0's merged output is checked against the CPU oracle BEFORE timing and the process
+                 exits non-zero on a mismatch; strong scaling
+  c1, c4_rmsnorm, c4_rope, c5
+                 (default workload, N = 1) the other configurations, each with its own roofline
+  comparators    torch's SDPA on the same GPU tensors; and, at N = 1, the reference's own CUDA kernels rebuilt
+                 for sm_100 (oracle/_ref, when present), timed beside this library's calls
 
 L2 hygiene: every step reads a different one of 8 KV caches (1.07 GB in total, L2 is 126 MB), so a cache is
 cold again when its turn comes.  With --impl reference the CPU baseline alone is run and reported.
 Multi-GPU (launched by torch.distributed.run, one rank per GPU): C2 is weak-scaled, every rank owns a batch
-of 16 sequences and no data crosses GPUs; C3 (--workload c3) shards the KV sequence across ranks and merges
-the per-rank (o, lse) pairs after one all-gather.
+of 16 sequences and no data crosses GPUs; C3 shards the KV sequence across ranks and merges the per-rank
+(o, lse) pairs over NVLink.
 """
 from __future__ import annotations
 
@@ -43,10 +54,14 @@ from __graft_entry__ import load_package  # noqa: E402
 
 N_ROTATE = 8
 FALLBACK_PEAK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one flash_decode_small_kernel launch on the C2 workload (seed 42),
-# from the ncu capture summarised in profiles/flash_decode_c2_full.md: 102.10 MB read + 4.05 MB written.
-C2_TRAFFIC_BYTES = 106_150_000
-C3_TRAFFIC_BYTES = 540_310_000  # flash_decode_small_kernel, profiles/flash_decode_c3_full.md: 536.91 MB read + 3.40 MB written
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from ncu captures of these kernels on these workloads
+# (seed 42); reported only when the kernel and the shape of the run are the captured ones.
+TRAFFIC = {
+    ("c2", "flash_decode_small_kernel"): (106_150_000, "ncu capture of flash_decode_small_kernel on C2: 102.10 MB read + 4.05 MB written"),
+    ("c3", "flash_decode_small_kernel"): (540_310_000, "ncu capture of flash_decode_small_kernel on C3: 536.91 MB read + 3.40 MB written"),
+}
+MIN_REGION_MS = 50.0   # a K-step region shorter than this is repeated until this much has been timed
+MAX_REGIONS = 400
 
 
 def hbm_peak():
@@ -172,8 +187,18 @@ def cpu_attention_pass(case):
     return attention.sdpa_reference(case.q, case.k, case.v, case.seq_lens, dtype=torch.bfloat16)
 
 
+def use_all_host_cores() -> int:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; the CPU baseline is meant to use the host
+    cores the box has, as a plain `python bench.py` run does."""
+    n = os.cpu_count() or 1
+    if torch.get_num_threads() < n:
+        torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def time_cpu_baseline(case, budget_s: float = 12.0, max_passes: int = 20):
     """Times the reference's CPU attention call on a bounded number of passes over the same batch."""
+    use_all_host_cores()
     cpu_attention_pass(case)  # warm-up (thread pool, allocator)
     times = []
     t_end = time.perf_counter() + budget_s
@@ -187,27 +212,39 @@ def time_cpu_baseline(case, budget_s: float = 12.0, max_passes: int = 20):
 
 # ------------------------------------------------------------------------------------------------
 def run_reference_arm(args, rank, world):
-    """The reference's own CPU implementation of the path, timed on the host cores (rank 0 only)."""
+    """The reference's own CPU implementation of the path, timed on the host cores (rank 0 only): the same
+    workload, metric and unit as the GPU arm at this N.  A step is one pass of
+    F.scaled_dot_product_attention over the global batch (the N per-GPU batches of the GPU arm, one after the
+    other); W warm-up steps, then K timed steps, as asked for."""
     if rank != 0:
         return
-    case, desc = make_decode_workload(args.workload if args.workload in ("c1", "c2", "c3") else "c2", 0, 1, args.seq_len)
-    for _ in range(max(1, min(args.warmup, 2))):
-        cpu_attention_pass(case)
-    steps = max(1, min(args.steps, 10))
+    cores = use_all_host_cores()
+    name = args.workload if args.workload in ("c1", "c2", "c3") else "c2"
+    n_batches = world if name != "c3" else 1   # C3 is one sequence whatever N is (strong scaling)
+    cases, desc = [], None
+    for r in range(n_batches):
+        case, desc = make_decode_workload(name, r, world, args.seq_len)
+        cases.append(case)
+    total_bytes = sum(kv_bytes(c) for c in cases)
+    for _ in range(args.warmup):
+        for c in cases:
+            cpu_attention_pass(c)
     t = time.perf_counter()
-    for _ in range(steps):
-        cpu_attention_pass(case)
-    dt = (time.perf_counter() - t) / steps
-    val = kv_bytes(case) / dt / 1e9
-    cores = torch.get_num_threads()
+    for _ in range(args.steps):
+        for c in cases:
+            cpu_attention_pass(c)
+    dt = (time.perf_counter() - t) / args.steps
+    val = total_bytes / dt / 1e9
     line = {
         "impl": "reference", "metric": "flash-decode HBM GB/s", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": desc.replace("/GPU", ""), "note": "F.scaled_dot_product_attention(enable_gqa=True) with a "
-                   "length mask on the bf16 CPU tensors: the reference's PyTorch attention path (model.py:115-116)"},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if name == "c3" else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "global_batch": sum(c.k.shape[0] for c in cases), "kv_bytes_per_step": int(total_bytes),
+                   "note": "F.scaled_dot_product_attention(enable_gqa=True) with a length mask on the bf16 CPU tensors: the "
+                           "reference's PyTorch attention path (model.py:115-116), no GPU involved"},
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "reference",
-                         "sample": f"mean of {steps} full passes over one batch; os.cpu_count()={os.cpu_count()}"},
+                         "sample": f"mean of {args.steps} passes over the global batch of {n_batches} x the per-GPU batch; "
+                                   f"os.cpu_count()={os.cpu_count()}"},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -220,14 +257,16 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=100)
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "rmsnorm", "rope", "c5", "prefill"])
+    ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "rmsnorm", "rope", "c5", "prefill"],
+                    help="default: c2 as the headline plus the sub-records of the other configurations")
     ap.add_argument("--gen-len", type=int, default=2048, help="c5: tokens generated per sequence")
     ap.add_argument("--batch", type=int, default=64, help="c5: sequences per GPU")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128], help="prefill: head size")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-comparator", action="store_true", help="c1-c3: skip the torch SDPA timing on the GPU")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the torch SDPA and reference-CUDA timings on the GPU")
+    ap.add_argument("--no-subrecords", action="store_true", help="default workload: only the C2 headline")
     ap.add_argument("--no-graph", action="store_true", help="c1-c3: launch every step through the extension call "
                     "instead of replaying a captured launch")
     ap.add_argument("--seq-len", type=int, default=131072, help="c3: cached tokens (a shard of C3 on one GPU: 131072 / N)")
@@ -235,6 +274,10 @@ def main():
     ap.add_argument("--nccl-merge", action="store_true", help="c3 on >1 GPU: all_gather + merge kernel instead of the fused exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.steps = max(args.steps, 1)
+    full_line = args.workload is None and not args.no_subrecords
+    if args.workload is None:
+        args.workload = "c2"
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -250,6 +293,7 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=dev)
 
     pkg = load_package()
@@ -260,14 +304,48 @@ def main():
     elif args.workload == "prefill":
         line = bench_prefill(args, ext, pkg, dev, rank, world)
     elif args.workload in ("rmsnorm", "rope"):
-        line = bench_pre_attention(args, ext, pkg, dev, rank, world)
+        line = bench_pre_attention(args, ext, pkg, dev, rank, world, args.workload)
     else:
-        line = bench_decode(args, ext, pkg, dev, rank, world)
+        line = bench_decode(args, ext, pkg, dev, rank, world, args.workload)
+    if full_line:
+        add_sub_records(line, args, ext, pkg, dev, rank, world)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def add_sub_records(line, args, ext, pkg, dev, rank, world):
+    """The configurations beside the headline, measured in the same process: C3 at every N (sharded over the
+    ranks, checked against the oracle before it is timed), and at N = 1 also C1, the two C4 kernels, C5 and the
+    reference's own CUDA kernels as a comparator."""
+    def brief(rec, keep=("metric", "value", "unit", "ms_per_step", "steps", "regions", "scaling", "config", "roofline",
+                         "parity", "comparators", "gpu_launches", "e2e", "clocks")):
+        return {k: rec[k] for k in keep if k in rec}
+
+    torch.cuda.empty_cache()
+    line["c3"] = brief(bench_decode(args, ext, pkg, dev, rank, world, "c3", lean=True))
+    if world > 1:
+        return
+    torch.cuda.empty_cache()
+    line["c1"] = brief(bench_decode(args, ext, pkg, dev, rank, world, "c1", lean=True))
+    torch.cuda.empty_cache()
+    line["c4_rmsnorm"] = brief(bench_pre_attention(args, ext, pkg, dev, rank, world, "rmsnorm"))
+    torch.cuda.empty_cache()
+    line["c4_rope"] = brief(bench_pre_attention(args, ext, pkg, dev, rank, world, "rope"))
+    torch.cuda.empty_cache()
+    if not args.no_comparator:
+        try:
+            line.setdefault("comparators", {})["reference_cuda_sm100"] = time_reference_cuda(ext, pkg, dev)
+        except Exception as exc:   # optional evidence, never a reason to lose the bench line
+            line.setdefault("comparators", {})["reference_cuda_sm100"] = {"error": str(exc)[:300]}
+        torch.cuda.empty_cache()
+    c5_args = argparse.Namespace(**vars(args))
+    c5_args.no_cpu_baseline = True
+    c5_args.steps = 1
+    line["c5"] = brief(bench_end_to_end(c5_args, ext, pkg, dev, rank, world))
+    torch.cuda.empty_cache()
 
 
 def sync_all(world):
@@ -298,21 +376,83 @@ def sum_over_ranks(x: float, world: int, dev) -> float:
     return float(t.item())
 
 
-def bench_decode(args, ext, pkg, dev, rank, world):
-    case, desc = make_decode_workload(args.workload, rank, world, args.seq_len)
-    sharded_seq = args.workload == "c3" and world > 1
+def timed_regions(run_steps, steps: int, world: int, dev, sampler=None):
+    """Times `steps` steps as ONE region (CUDA events on the launching stream, barrier + synchronize on both
+    sides) and repeats the region while less than MIN_REGION_MS has been timed in total.  Returns
+    (this rank's ms of the median region, max-over-ranks ms of the median region, summary dict).  The repeat
+    decision uses the max over ranks, so every rank makes the same number of repeats."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    regions, total = [], 0.0
+    if sampler is not None:
+        sampler.mark("t0")
+    while True:
+        sync_all(world)
+        start.record()
+        run_steps(steps)
+        end.record()
+        torch.cuda.synchronize()
+        sync_all(world)
+        mine = start.elapsed_time(end)
+        worst = max_over_ranks(mine, world, dev)
+        regions.append((worst, mine))
+        total += worst
+        if total >= MIN_REGION_MS or len(regions) >= MAX_REGIONS:
+            break
+    if sampler is not None:
+        sampler.mark("t1")
+    regions.sort()
+    worst, mine = regions[len(regions) // 2]
+    summary = {"n": len(regions), "steps_each": steps, "ms_median": worst, "ms_min": regions[0][0], "ms_max": regions[-1][0],
+               "reported": "median region"}
+    return mine, worst, summary
+
+
+def attention_parity(out, case_full, rank, world, dev, what):
+    """Rank 0 compares `out` (bf16 [B,Hq,1,D] on the device) with the CPU oracle under the attention tolerance
+    (2e-2 absolute + 1e-2 relative against fp32) and a relative-L2 bound of 1e-2; every rank learns the verdict
+    and the process group leaves with a non-zero exit code on a mismatch."""
+    import torch.distributed as dist
+
+    rec = {"checked": what, "oracle": "F.scaled_dot_product_attention in fp32 on the CPU (oracle.attention.sdpa_reference)",
+           "tolerance": "|err| <= 2e-2 + 1e-2*|ref| and relative L2 <= 1e-2"}
+    ok = torch.ones(1, dtype=torch.int32, device=dev)
+    if rank == 0:
+        from oracle import attention
+
+        use_all_host_cores()
+        want = attention.sdpa_reference(case_full.q, case_full.k, case_full.v, case_full.seq_lens)
+        got = out.detach().float().cpu()
+        err = (got - want).abs()
+        rel_l2 = float((got - want).norm() / want.norm().clamp_min(1e-30))
+        fine = bool(torch.isfinite(got).all()) and bool((err <= 2e-2 + 1e-2 * want.abs()).all()) and rel_l2 <= 1e-2
+        rec.update({"ok": fine, "max_abs_err": float(err.max()), "rel_l2_err": rel_l2, "max_abs_ref": float(want.abs().max())})
+        ok[0] = 1 if fine else 0
+    if world > 1:
+        dist.broadcast(ok, 0)
+    if int(ok.item()) != 1:
+        if rank == 0:
+            print(json.dumps({"error": "parity check failed before timing", "parity": rec}), flush=True)
+        raise SystemExit(3)
+    return rec
+
+
+def bench_decode(args, ext, pkg, dev, rank, world, workload, lean=False):
+    """C1 / C2 / C3.  `lean`: a sub-record (no end-to-end leg, no CPU baseline)."""
+    case, desc = make_decode_workload(workload, rank, world, args.seq_len)
+    sharded_seq = workload == "c3" and world > 1
+    case_full = case
+    full_bytes = kv_bytes(case)
     if sharded_seq:
         lo, hi = pkg.sharding.kv_shard_bounds(case.k.shape[2], world)[rank]
         from oracle.inputs import DecodeCase
 
-        full_bytes = kv_bytes(case)
         case = DecodeCase(case.q, case.k[:, :, lo:hi], case.v[:, :, lo:hi], None)
     my_bytes = kv_bytes(case)
 
     # ---- device-resident inputs: N_ROTATE distinct KV caches so that each step finds L2 cold ----
     q = case.q.to(dev)
     lens = case.seq_lens.to(dev) if case.seq_lens is not None else None
-    n_rot = N_ROTATE if args.workload != "c3" else 2
+    n_rot = N_ROTATE if workload != "c3" else 2
     ks, vs = [], []
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     for i in range(n_rot):
@@ -328,7 +468,6 @@ def bench_decode(args, ext, pkg, dev, rank, world):
 
     xchg = None
     if sharded_seq and not args.nccl_merge:
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         xchg = pkg.sharding.KvShardExchange(ext, q.shape[0], q.shape[1], q.shape[3], dev)
 
     def step(i):
@@ -339,10 +478,18 @@ def bench_decode(args, ext, pkg, dev, rank, world):
             return pkg.sharding.decode_kv_sharded(ext, q, ks[j], vs[j], None)
         return ext.flash_attention_decode(q, ks[j], vs[j], seq_lens=lens, out=out, max_ctas=args.max_ctas)
 
+    # ---- parity before timing: the step on the seeded inputs (cache 0) against the CPU oracle ----
+    parity = None
+    if workload == "c3" or lean:
+        got = step(0)
+        torch.cuda.synchronize()
+        parity = attention_parity(got, case_full, rank, world, dev,
+                                  f"{workload} step output of rank 0" + (f" (KV sharded over {world} ranks, merged)" if sharded_seq else ""))
+
     # The launches of the rotating caches are captured back to back in one CUDA graph: the timed loop then
     # costs the host one graph launch per n_rot steps instead of the extension's argument checks and
     # tensor-map encoding per step, which take as long as a short kernel.  (The fused exchange numbers its
-    # calls on the device, so its two launches per step are captured too; the NCCL variant stays eager.)
+    # calls on the device, so its launches are captured too; the NCCL variant stays eager.)
     use_graph = not args.no_graph and (not sharded_seq or xchg is not None)
     n_graph = max(n_rot, 8)  # launches per graph: a graph launch costs the host about as much as an eager call
     run_steps = graph_runner(step, n_graph, dev) if use_graph else eager_runner(step)
@@ -353,18 +500,8 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     sampler.start()
     sampler.mark("w0")
     run_steps(args.warmup)
-    sync_all(world)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.mark("t0")
-    start.record()
-    run_steps(args.steps)
-    end.record()
-    torch.cuda.synchronize()
-    sampler.mark("t1")
-    sync_all(world)
+    ms_total, ms_max, regions = timed_regions(run_steps, args.steps, world, dev, sampler)
     sampler.stop()
-    ms_total = start.elapsed_time(end)
-    ms_max = max_over_ranks(ms_total, world, dev)
     status = ext.flash_decode_status(q)
     if status != 0:
         raise RuntimeError(f"device-side wait ran out (status {status})")
@@ -376,7 +513,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     peak, peak_kind = hbm_peak()
     launch_ms = ms_total / args.steps
     achieved = my_bytes / (launch_ms * 1e-3) / 1e9
-    # which of the library's two decode kernels these sizes run (0 = persistent grid, else the static deal's split)
+    # which of the library's decode kernels these sizes run (0 = persistent grid, else the static deal's split)
     if args.max_ctas > 0:
         choice = 0
     elif args.max_ctas < 0:
@@ -385,18 +522,17 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         choice = pkg.capi.load().l3ci_flash_decode_kernel_choice(q.shape[0], q.shape[1], ks[0].shape[1], q.shape[-1],
                                                                  ks[0].shape[2], int(lens is not None))
     kernel = "flash_decode_kernel" if choice == 0 else "flash_decode_small_kernel"
-    traffic = None
-    if world == 1 and args.workload == "c2" and kernel == "flash_decode_small_kernel":
-        traffic = C2_TRAFFIC_BYTES
-    if world == 1 and args.workload == "c3" and kernel == "flash_decode_small_kernel" and args.seq_len == 131072:
-        traffic = C3_TRAFFIC_BYTES
+    traffic, traffic_source = None, None
+    if world == 1 and (workload != "c3" or args.seq_len == 131072) and (workload, kernel) in TRAFFIC:
+        traffic, traffic_source = TRAFFIC[(workload, kernel)]
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_kind": peak_kind,
+                "traffic": traffic, "traffic_source": traffic_source, "peak_kind": peak_kind,
                 "kernel": kernel, "kernel_split": (None if choice in (0, 1) else {"ctas_per_unit": choice // 16, "warps_per_unit": choice % 16}),
                 "algorithmic_bytes_per_launch": my_bytes,
                 "frac_of_8TBs_nominal": achieved / 8000.0}
     if sharded_seq:
-        roofline["note"] = "per-rank shard; the step also holds the exchange of shard results and their merge"
+        roofline["note"] = ("per-rank shard of %d tokens; the step also holds the exchange of shard results and their merge, so this "
+                            "is the whole step against the HBM time of the shard" % case.k.shape[2])
     if xchg is not None and xchg.check() != 0:
         raise RuntimeError("exchange wait ran out")
 
@@ -418,16 +554,37 @@ def bench_decode(args, ext, pkg, dev, rank, world):
             sd_run.prepare(n_graph)
             sd_run(n_graph)
             torch.cuda.synchronize()
-            start.record()
-            sd_run(n_sd)
-            end.record()
-            torch.cuda.synchronize()
-            sd_ms = start.elapsed_time(end) / n_sd
+            _, sd_total, _ = timed_regions(sd_run, n_sd, 1, dev)
+            sd_ms = sd_total / n_sd
             comparators = {"torch_sdpa_gpu": {"ms_per_step": sd_ms, "GB/s": my_bytes / (sd_ms * 1e-3) / 1e9, "steps": n_sd,
                                               "call": "F.scaled_dot_product_attention(q, k, v, enable_gqa=True" +
                                                       (", attn_mask=lengths)" if mask is not None else ")")}}
         except Exception as exc:  # the comparator is optional evidence, never a reason to lose the bench line
             comparators = {"torch_sdpa_gpu": {"error": str(exc)[:200]}}
+
+    B, Hkv, S, D = case.k.shape
+    line = {
+        "metric": "flash-decode HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if workload == "c3" else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
+                   "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
+                   "launch": f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
+                             else "each step is an eager extension call",
+                   "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
+                                                                  "fused NVLink exchange/merge kernel (peer stores, no collective)")) if sharded_seq else
+                                  ("data-parallel x%d, no collective" % world),
+                   "pct_of_8TBs_nominal_per_gpu": 100.0 * achieved / 8000.0},
+        "regions": regions, "roofline": roofline,
+        "gpu_launches": args.steps * (2 if sharded_seq else 1),
+        "clocks": sampler.summary(),
+    }
+    if parity is not None:
+        line["parity"] = parity
+    if comparators is not None:
+        line["comparators"] = comparators
+    if lean:
+        return line
 
     # ---- end to end through the extension with host buffers (pinned), copies inside the timed region ----
     # Host side: q [B,1,Hq,D], K and V as the cache holds them, [B,S,Hkv,D], all pinned.  Only the cached tokens
@@ -463,6 +620,7 @@ def bench_decode(args, ext, pkg, dev, rank, world):
         e2e_step()
     sync_all(world)
     e_steps = max(1, args.e2e_steps)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(e_steps):
         e2e_step()
@@ -471,38 +629,114 @@ def bench_decode(args, ext, pkg, dev, rank, world):
     sync_all(world)
     e_ms = max_over_ranks(start.elapsed_time(end), world, dev)
     e2e_val = total_bytes * e_steps / (e_ms * 1e-3) / 1e9
-    e2e = {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "steps": e_steps, "ms_per_step": e_ms / e_steps}
+    line["e2e"] = {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                   "steps": e_steps, "ms_per_step": e_ms / e_steps}
 
-    # ---- CPU baseline on this box's host cores (rank 0, N=1 only) ----
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, passes, sec = time_cpu_baseline(case)
-        cpu = {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "reference",
-               "sample": f"median of {passes} full passes of F.scaled_dot_product_attention (bf16, enable_gqa, length "
-                         f"mask) over the same batch, {sec * 1e3:.1f} ms each; os.cpu_count()={os.cpu_count()}"}
-
-    B, Hkv, S, D = case.k.shape
-    line = {
-        "metric": "flash-decode HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if sharded_seq else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
-                   "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
-                   "launch": f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
-                             else "each step is an eager extension call",
-                   "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
-                                                                  "fused NVLink exchange/merge kernel")) if sharded_seq else
-                                  ("data-parallel x%d, no collective" % world),
-                   "pct_of_8TBs_nominal_per_gpu": 100.0 * achieved / 8000.0},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * (2 if sharded_seq else 1),
-        "clocks": sampler.summary(),
-    }
-    if cpu is not None:
-        line["cpu_baseline"] = cpu
-    if comparators is not None:
-        line["comparators"] = comparators
+    # ---- CPU baseline on this box's host cores (rank 0, at every N; the other ranks wait at the next barrier) ----
+    if rank == 0 and not args.no_cpu_baseline:
+        v, passes, sec = time_cpu_baseline(case_full if workload == "c3" else case)
+        line["cpu_baseline"] = {
+            "value": v, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "reference",
+            "sample": f"median of {passes} full passes of F.scaled_dot_product_attention (bf16, enable_gqa, length "
+                      f"mask) over one GPU's batch, {sec * 1e3:.1f} ms each; os.cpu_count()={os.cpu_count()}"}
+    sync_all(world)
     return line
+
+
+def time_reference_cuda(ext, pkg, dev):
+    """The reference's own CUDA kernels (custom_kernels/custom_kernels.cu, unmodified, rebuilt for sm_100 into
+    oracle/_ref) beside this library's calls on the same GPU and tensors: its three functions on C1, on a
+    uniform-length C2 (its interface has one length for the batch) and on C4.  Both sides are timed the same way:
+    eager calls back to back with CUDA events (the reference launches on the legacy default stream and allocates
+    its outputs and scratch inside every call, so it cannot be captured in a graph), and the device time of the
+    kernels alone from the profiler's kernel records.  Its attention output is not a correctness reference."""
+    from oracle import build_ref, inputs
+
+    ref = build_ref.load()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/reference_kernels_sm100.so is not built (needs the reference checkout at build time)"}
+
+    def timed(fn, n_inputs, calls=48):
+        for i in range(4):
+            fn(i % n_inputs)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(calls):
+            fn(i % n_inputs)
+        end.record()
+        torch.cuda.synchronize()
+        eager_us = start.elapsed_time(end) * 1e3 / calls
+        kernel_us = None
+        try:
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for i in range(n_inputs):
+                    fn(i)
+                torch.cuda.synchronize()
+            total = sum(e.device_time_total for e in prof.key_averages() if e.device_type.name == "CUDA" or e.device_time_total > 0)
+            kernel_us = total / n_inputs
+        except Exception:
+            pass
+        return eager_us, kernel_us
+
+    res = {"source": "the reference's custom_kernels.cu + main.cpp, unmodified, compiled for sm_100 (oracle/build_ref.py)",
+           "timing": "eager_us: CUDA events around 48 back-to-back calls on rotating inputs larger than L2; kernel_us: device "
+                     "time of the kernels of one call (profiler kernel records), mean over the rotating inputs"}
+
+    def pair(name, nbytes, ref_fn, our_fn, n_inputs):
+        r_eager, r_kernel = timed(ref_fn, n_inputs)
+        o_eager, o_kernel = timed(our_fn, n_inputs)
+        rec = {"bytes": nbytes, "reference": {"eager_us": r_eager, "kernel_us": r_kernel},
+               "this_library": {"eager_us": o_eager, "kernel_us": o_kernel}}
+        if r_kernel and o_kernel:
+            rec["kernel_time_ratio"] = r_kernel / o_kernel
+            rec["reference"]["GB/s"] = nbytes / r_kernel / 1e3
+            rec["this_library"]["GB/s"] = nbytes / o_kernel / 1e3
+        res[name] = rec
+
+    g = torch.Generator(device=dev).manual_seed(7)
+
+    def caches(B, S, Hkv, D, n):
+        return [torch.randn(B, S, Hkv, D, generator=g, device=dev).bfloat16().transpose(1, 2) for _ in range(n)]
+
+    # C1 (the cache is 0.5 MB: 8 caches do not leave L2; reported as it is, the call is latency-bound)
+    c1 = inputs.config1()
+    q1 = c1.q.to(dev)
+    k1, v1 = caches(1, 256, 8, 64, 8), caches(1, 256, 8, 64, 8)
+    pair("c1_attention", kv_bytes(c1), lambda i: ref.flash_attention_decode(q1, k1[i], v1[i]),
+         lambda i: ext.flash_attention_decode(q1, k1[i], v1[i]), 8)
+    # C2 with one length for the whole batch: B=16, 2048 cached tokens each
+    q2 = torch.randn(16, 1, 32, 128, generator=g, device=dev).bfloat16().transpose(1, 2)
+    k2, v2 = caches(16, 2048, 8, 128, 4), caches(16, 2048, 8, 128, 4)
+    pair("c2_uniform_attention", 2 * 2 * 8 * 128 * 16 * 2048, lambda i: ref.flash_attention_decode(q2, k2[i], v2[i]),
+         lambda i: ext.flash_attention_decode(q2, k2[i], v2[i]), 4)
+    del k2, v2
+    # C4: RMSNorm and the rotation of q and k (two calls, as model.py:100-101 makes them)
+    x, w, eps, qkv = inputs.config4(seed=42)
+    xs = [x.to(dev)] + [torch.randn(x.shape, generator=g, device=dev).bfloat16() for _ in range(7)]
+    dw = w.to(dev)
+    pair("c4_rms_norm", 2 * x.numel() * 2 + w.numel() * 2, lambda i: ref.rms_norm(xs[i], dw, eps), lambda i: ext.rms_norm(xs[i], dw, eps), 8)
+    del xs
+    Hq, Hkv, D = 32, 8, 64
+    B, S = qkv.shape[:2]
+    freq = pkg.rope_table.precompute_freqs_cis(D, S, **inputs.ROPE_CONFIG4).to(dev)
+    qs = [qkv.to(dev)] + [torch.randn(qkv.shape, generator=g, device=dev).bfloat16() for _ in range(5)]
+
+    def views(t):
+        return t[..., : Hq * D].view(B, S, Hq, D), t[..., Hq * D: (Hq + Hkv) * D].view(B, S, Hkv, D)
+
+    def rope_ref(i):
+        a, b = views(qs[i])
+        return ref.rot_embed(a, freq), ref.rot_embed(b, freq)
+
+    def rope_ours(i):
+        a, b = views(qs[i])
+        return ext.rot_embed(a, freq), ext.rot_embed(b, freq)
+
+    pair("c4_rot_embed_q_and_k", 2 * B * S * (Hq + Hkv) * D * 2 + freq.numel() * 4, rope_ref, rope_ours, 6)
+    return res
 
 
 def graph_runner(step, n_rot, dev):
@@ -612,7 +846,7 @@ def bench_prefill(args, ext, pkg, dev, rank, world):
     }
 
 
-def bench_pre_attention(args, ext, pkg, dev, rank, world):
+def bench_pre_attention(args, ext, pkg, dev, rank, world, workload):
     """C4: RMSNorm over [4096, 2048] tokens, or fused RoPE + KV-cache write of q (32x64) and k, v (8x64)."""
     from oracle import inputs
 
@@ -620,7 +854,7 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world):
     Hq, Hkv, D, B, S = 32, 8, 64, 2, 2048
     freq = pkg.rope_table.precompute_freqs_cis(D, S, **{k: v for k, v in inputs.ROPE_CONFIG4.items()}).to(dev)
     n_rot = 12  # 12 x (33.5 | 50 MB) > 126 MB L2
-    if args.workload == "rmsnorm":
+    if workload == "rmsnorm":
         xs = [x.to(dev) if i == 0 else torch.randn_like(x.float(), device=dev).bfloat16() for i in range(n_rot)]
         dw = w.to(dev)
         nbytes = 2 * x.numel() * 2 + w.numel() * 2
@@ -642,18 +876,8 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world):
     sampler.start()
     sampler.mark("w0")
     run_steps(args.warmup)
-    sync_all(world)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.mark("t0")
-    start.record()
-    run_steps(args.steps)
-    end.record()
-    torch.cuda.synchronize()
-    sampler.mark("t1")
-    sync_all(world)
+    ms_total, ms_max, regions = timed_regions(run_steps, args.steps, world, dev, sampler)
     sampler.stop()
-    ms_total = start.elapsed_time(end)
-    ms_max = max_over_ranks(ms_total, world, dev)
     value = nbytes * world * args.steps / (ms_max * 1e-3) / 1e9
     peak, peak_kind = hbm_peak()
     achieved = nbytes / (ms_total / args.steps * 1e-3) / 1e9
@@ -664,8 +888,10 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world):
         "config": {"workload": desc, "l2": f"{n_rot} rotating inputs and outputs > 126 MB L2", "bytes_per_step": nbytes,
                    "launch": "each step is an eager extension call (with its output allocation)" if args.no_graph else
                              f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back"},
+        "regions": regions,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": kernel},
+                     "traffic": None, "peak_kind": peak_kind, "kernel": kernel, "algorithmic_bytes_per_launch": nbytes,
+                     "frac_of_8TBs_nominal": achieved / 8000.0},
         "gpu_launches": args.steps, "clocks": sampler.summary(),
     }
 
@@ -717,6 +943,15 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_end_to_end(cfg, dl, B, P, G)
     decode_steps = (G - 1) * steps
+    # HBM bytes a generation cannot avoid: every decode step streams the weights once (16 layers + the tied head)
+    # and the cached K and V of all sequences and layers; prefill, activations and the logits are left out
+    D = cfg.head_dim
+    weight_bytes = 2 * (cfg.n_layer * ((cfg.n_head + 2 * cfg.n_kv_head) * D * cfg.n_embd + cfg.n_embd * cfg.n_embd +
+                                       3 * cfg.hidden_dim * cfg.n_embd) + cfg.vocab_size * cfg.n_embd)
+    kv_bytes_per_token = 2 * 2 * cfg.n_kv_head * D * cfg.n_layer * B
+    gen_bytes = (G - 1) * weight_bytes + kv_bytes_per_token * sum(P + t for t in range(1, G))
+    peak, peak_kind = hbm_peak()
+    achieved = gen_bytes * steps / (ms * 1e-3) / 1e9
     line = {
         "metric": "Llama-3.2-1B decode tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": 1, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
@@ -729,6 +964,13 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
                    "note": "GEMMs are cuBLAS via torch; RMSNorm (+ residual add), SiLU*mul, RoPE + cache write, decode attention and the greedy step are this "
                            "repository's kernels; the decode step is replayed from a CUDA graph",
                    "reference_published_rtx4060_tokens_per_s": 2041.67},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_kind": peak_kind, "kernel": "whole decode step (cuBLAS GEMMs + this library's kernels)",
+                     "algorithmic_bytes_per_launch": gen_bytes // max(1, G - 1),
+                     "note": "weights once per decode step + cached K/V of the step, averaged over the generation; the time "
+                             "includes the prefill pass"},
+        "launches_per_decode_step": {"this_library": 82, "detail": "33 RMSNorm (32 fused with the residual add), 16 SiLU*mul, 16 fused "
+                                     "RoPE + cache write, 16 flash-decode, 1 greedy step; plus 81 cuBLAS GEMMs and the embedding lookup"},
         "e2e": e2e,
         # per decode step: 33 RMSNorm (32 with the residual add) + 16 SiLU*mul + 16 fused RoPE/cache + 16
         # flash-decode + 1 greedy-step launches of this library; the prefill pass has no flash-decode
