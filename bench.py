@@ -942,6 +942,14 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_end_to_end(cfg, dl, B, P, G)
+    ref_loop = None
+    if world == 1 and not args.no_comparator:
+        del model
+        torch.cuda.empty_cache()
+        try:
+            ref_loop = time_reference_model_loop(pkg, dev, B, P, min(G, 512), prompts)
+        except Exception as exc:   # optional evidence, never a reason to lose the bench line
+            ref_loop = {"error": str(exc)[:300]}
     decode_steps = (G - 1) * steps
     # HBM bytes a generation cannot avoid: every decode step streams the weights once (16 layers + the tied head)
     # and the cached K and V of all sequences and layers; prefill, activations and the logits are left out
@@ -978,7 +986,58 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if ref_loop is not None:
+        line["comparators"] = {"reference_model_loop": ref_loop}
     return line
+
+
+def time_reference_model_loop(pkg, dev, B, P, G, prompts):
+    """The reference's own generation loop — its unmodified model.py (`LLaMA3.generate`, model.py:314-396; taken
+    from baseline/_ref/, where build() puts it when the reference checkout is present) — running on THIS build of
+    `custom_kernels_extension`, at the same architecture, batch and prompt length with random-init weights, greedy,
+    ignore_eos.  Same kernels underneath; what differs is the loop around them: eager launches, two rot_embed calls
+    and two cache copies per layer, unfused residual adds and SiLU, a host sync per token.  tokens/s by the
+    reference's formula (benchmark_model.py:82) over a generation of G tokens."""
+    import importlib.util
+    import types
+
+    ref_dir = Path(os.environ.get("L3CI_REFERENCE_DIR", REPO / "baseline" / "_ref"))
+    if not (ref_dir / "model.py").exists():
+        return {"unavailable": f"{ref_dir / 'model.py'} is absent (the reference checkout was not there at build time)"}
+    pkg.extension()
+    saved = sys.modules.get("transformers")
+    stub = types.ModuleType("transformers")
+    stub.AutoModelForCausalLM = stub.AutoTokenizer = None
+    sys.modules["transformers"] = stub   # imported at model.py:21 for the checkpoint loader only
+    try:
+        spec = importlib.util.spec_from_file_location("l3ci_reference_model", ref_dir / "model.py")
+        model_py = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(model_py)
+    finally:
+        if saved is not None:
+            sys.modules["transformers"] = saved
+        else:
+            del sys.modules["transformers"]
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)   # as from_pretrained_llama3_hf builds it (model.py:282, 298-300)
+    try:
+        with torch.device(dev):
+            m = model_py.LLaMA3(model_py.LlamaConfig(max_model_len=P + G, max_gen_batch_size=B)).eval()
+    finally:
+        torch.set_default_dtype(old)
+    m.tokenizer = types.SimpleNamespace(pad_id=-1, stop_tokens=[128001, 128009])
+    plist = prompts.tolist()
+    m.generate(plist, 4, temperature=0, ignore_eos=True)   # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = m.generate(plist, G, temperature=0, ignore_eos=True)
+    torch.cuda.synchronize()
+    sec = time.perf_counter() - t0
+    del m
+    torch.cuda.empty_cache()
+    return {"tokens_per_s": G * B / sec, "seconds": sec, "generated_tokens_per_sequence": G, "batch": B, "prompt": P,
+            "what": "unmodified reference model.py (LLaMA3.generate, temperature 0, ignore_eos) on this build of the extension; "
+                    "shorter generation than the headline (shorter caches on average, which favours it)"}
 
 
 def cpu_baseline_end_to_end(cfg, dl, B, P, G):

@@ -29,6 +29,11 @@ import torch.nn.functional as F
 
 from . import rope_table
 
+# Profiler range names of the reference's loop (model.py:99-109 "rot_embd" / "use_kv", :214-216 "layer", :364-366
+# "forward"), kept so that a timeline of this loop reads like one of the reference's.  The fused RoPE + cache-write
+# call carries both of the first two names.
+_nvtx_push, _nvtx_pop = torch.cuda.nvtx.range_push, torch.cuda.nvtx.range_pop
+
 
 @dataclass
 class DecoderConfig:
@@ -99,9 +104,14 @@ class Llama3Decoder:
         h = ext.rms_norm(x, w["h0.ln_1"], cfg.norm_eps)                                # model.py:147, 71
         for l in range(cfg.n_layer):
             p = f"h{l}."
+            _nvtx_push("layer")
             qkv = F.linear(h, w[p + "attn"])                                           # model.py:95
+            _nvtx_push("rot_embd")
+            _nvtx_push("use_kv")
             q = ext.rot_embed_kv_cache(qkv, self.freqs, self.cache_k[l], self.cache_v[l], 0, Hq, Hkv,
                                        positions=positions)                            # model.py:96-108
+            _nvtx_pop()
+            _nvtx_pop()
             if T > 1:
                 # prefill: all sequences start at position 0 with T tokens (model.py:114-116)
                 k = self.cache_k[l][:B, :T].transpose(1, 2)
@@ -117,6 +127,7 @@ class Llama3Decoder:
             m = F.linear(ext.silu_mul(gu[..., :F_], gu[..., F_:]), w[p + "mlp_proj"])
             nxt = w[f"h{l + 1}.ln_1"] if l + 1 < cfg.n_layer else w["ln_f"]
             x, h = ext.add_rms_norm(m, x, nxt, cfg.norm_eps)                           # model.py:148, next 147 / 217
+            _nvtx_pop()
         # the reference widens the logits to fp32 first (model.py:226); the widening is monotonic, so the argmax
         # of the bf16 values is the same index
         return F.linear(h[:, -1, :], w["wte"])                                         # model.py:225 (tied head)
@@ -141,7 +152,9 @@ class Llama3Decoder:
         steps = torch.ones(B, dtype=torch.int64, device=dev)   # next free column of `out`, per sequence
 
         def step():
+            _nvtx_push("forward")
             logits = self.forward(cur, positions, seq_lens)
+            _nvtx_pop()
             # argmax, out[b, steps[b]] = token, cur[b] = token, steps / positions / seq_lens += 1: one kernel
             self.ext.greedy_step(logits, out, steps, cur.view(B), positions, seq_lens)  # model.py:370-381
 
