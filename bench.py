@@ -505,6 +505,7 @@ def bench_decode(args, ext, pkg, dev, rank, world, workload, lean=False):
     status = ext.flash_decode_status(q)
     if status != 0:
         raise RuntimeError(f"device-side wait ran out (status {status})")
+    one_launch = bool(xchg is not None and xchg.one_launch)
     total_bytes = full_bytes if sharded_seq else sum_over_ranks(float(my_bytes), world, dev)
     value = total_bytes * args.steps / (ms_max * 1e-3) / 1e9
     ms_per_step = ms_max / args.steps
@@ -572,11 +573,13 @@ def bench_decode(args, ext, pkg, dev, rank, world, workload, lean=False):
                    "launch": f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
                              else "each step is an eager extension call",
                    "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
-                                                                  "fused NVLink exchange/merge kernel (peer stores, no collective)")) if sharded_seq else
+                                                                  ("exchange over NVLink (peer stores, no collective) and merge in the decode "
+                                                                   "kernel's tail: one launch per rank and step" if one_launch else
+                                                                   "decode kernel + one exchange/merge kernel over NVLink (peer stores, no collective)"))) if sharded_seq else
                                   ("data-parallel x%d, no collective" % world),
                    "pct_of_8TBs_nominal_per_gpu": 100.0 * achieved / 8000.0},
         "regions": regions, "roofline": roofline,
-        "gpu_launches": args.steps * (2 if sharded_seq else 1),
+        "gpu_launches": args.steps * (2 if sharded_seq and not one_launch else 1),
         "clocks": sampler.summary(),
     }
     if parity is not None:

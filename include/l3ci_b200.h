@@ -293,6 +293,30 @@ L3CI_API int l3ci_lse_exchange_merge(void* const* bufs, int32_t rank, int32_t ra
                                      int64_t o_sb, int64_t o_sh, int32_t* status,
                                      l3ci_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Decode attention over a sequence-sharded cache in ONE launch per GPU and step: l3ci_flash_decode on this GPU's
+ * slice of the cached tokens, with the exchange of the per-GPU results and their log-sum-exp merge done in the
+ * kernel's tail (every thread sends its finished output element to the peers as one 64-bit word {value, call
+ * number} with a plain store over NVLink, polls its own buffer for the peers' words, merges).  No counterpart in
+ * the reference (single GPU); does for GPU shards what its combine kernel intends for 64-token steps
+ * (custom_kernels/custom_kernels.cu:179-223).
+ *
+ * `args` as for l3ci_flash_decode (k, v, n_seq, seq_lens describe THIS rank's slice; `out` receives the merged
+ * attention on every rank; o_partial / lse must be null; scratch is not used).  `bufs` is a DEVICE array of
+ * `ranks` (<= 8) base pointers, as seen from this process, of the ranks' exchange buffers of
+ * l3ci_flash_decode_exchange_bytes(ranks, B, Hq, D) bytes each, zero-filled once, bufs[rank] the local one (CUDA IPC
+ * / torch symmetric memory).  `epoch` numbers the calls (1, 2, 3, ... the same on all ranks); with 0 the number
+ * is kept in the buffer and advanced by the kernel, so a step has no host state and can be captured in a CUDA
+ * graph.  Every rank must make the call once per epoch.  The wait for the peers is bounded (1 s, see
+ * l3ci_set_device_wait_limit_ns): when it runs out, *status (optional device word) becomes L3CI_ERR_DEVICE_WAIT and
+ * the elements concerned stay unwritten.  Sizes that l3ci_flash_decode would hand to its persistent kernel
+ * (Hq/Hkv > 8, very long or lopsided slices) return L3CI_ERR_UNSUPPORTED: use l3ci_flash_decode with o_partial /
+ * lse followed by l3ci_lse_exchange_merge for those.
+ * ------------------------------------------------------------------------------------------ */
+L3CI_API size_t l3ci_flash_decode_exchange_bytes(int32_t ranks, int32_t B, int32_t Hq, int32_t D);
+L3CI_API int l3ci_flash_decode_exchange(const l3ci_flash_decode_args* args, void* const* bufs, int32_t rank,
+                                        int32_t ranks, uint32_t epoch, int32_t* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,6 +23,7 @@ EXPORTS = (
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_flash_decode_kernel_choice",
     "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge", "l3ci_prefill_attention",
+    "l3ci_flash_decode_exchange_bytes", "l3ci_flash_decode_exchange",
 )
 
 
@@ -115,6 +116,10 @@ def load() -> C.CDLL:
     lib.l3ci_lse_exchange_bytes.argtypes = [i32, i32, i32, i32]
     lib.l3ci_lse_exchange_merge.restype = C.c_int
     lib.l3ci_lse_exchange_merge.argtypes = [vp, i32, i32, C.c_uint32, vp, i32, i32, i32, i64, i64, vp, vp]
+    lib.l3ci_flash_decode_exchange_bytes.restype = C.c_size_t
+    lib.l3ci_flash_decode_exchange_bytes.argtypes = [i32, i32, i32, i32]
+    lib.l3ci_flash_decode_exchange.restype = C.c_int
+    lib.l3ci_flash_decode_exchange.argtypes = [C.POINTER(FlashDecodeArgs), vp, i32, i32, C.c_uint32, vp]
     _lib = lib
     return lib
 
@@ -385,4 +390,20 @@ def lse_exchange_merge(bufs, rank: int, ranks: int, epoch: int, out, B: int, Hq:
                                               out.stride(0), out.stride(1),
                                               status.data_ptr() if status is not None else None, _stream(out)),
                "l3ci_lse_exchange_merge")
+    return out
+
+
+def flash_decode_exchange(q, k, v, bufs, rank: int, ranks: int, epoch: int = 0, out=None, seq_lens=None, status=None,
+                          scale: float = 0.0, max_ctas: int = 0):
+    """`l3ci_flash_decode_exchange`: attention of q over this rank's slice k, v of a sequence-sharded cache, merged
+    with the other ranks' results in the same launch.  `bufs`: device int64 tensor of the ranks' exchange buffers."""
+    import torch
+
+    if out is None:
+        out = torch.empty_like(q)
+    a = flash_decode_args(q, k, v, out=out, seq_lens=seq_lens, scale=scale, max_ctas=max_ctas)
+    with _on(q):
+        _check(load().l3ci_flash_decode_exchange(C.byref(a), bufs.data_ptr(), rank, ranks, epoch,
+                                                 status.data_ptr() if status is not None else None),
+               "l3ci_flash_decode_exchange")
     return out

@@ -949,6 +949,41 @@ int flash_decode_launch(const l3ci_flash_decode_args* a) {
 
 extern "C" int l3ci_flash_decode(const l3ci_flash_decode_args* a) { return l3ci::flash_decode_launch(a); }
 
+// ---------------------------------------------------------------------------------------------
+// Sequence-sharded decode with the cross-GPU exchange and merge in the kernel's tail (one launch per step).
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t l3ci_flash_decode_exchange_bytes(int32_t ranks, int32_t B, int32_t Hq, int32_t D) {
+  if (ranks <= 0 || B <= 0 || Hq <= 0 || D <= 0) return 0;
+  // [2 parities][ranks][rows * (D + 1)] 64-bit words, then 2 control words
+  return (2 * (size_t)ranks * (size_t)B * Hq * (D + 1) + 2) * sizeof(unsigned long long);
+}
+
+extern "C" int l3ci_flash_decode_exchange(const l3ci_flash_decode_args* a, void* const* bufs, int32_t rank, int32_t ranks,
+                                          uint32_t epoch, int32_t* status) {
+  using namespace l3ci;
+  clear_error();
+  if (!a) return fail(L3CI_ERR_INVALID, "flash_decode_exchange: null args");
+  if (a->B <= 0 || a->Hq <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv || a->n_seq < 0 || (a->D != 64 && a->D != 128))
+    return fail(L3CI_ERR_INVALID, "flash_decode_exchange: bad size B=%d Hq=%d Hkv=%d D=%d n_seq=%d", a->B, a->Hq, a->Hkv, a->D, a->n_seq);
+  if (!a->q || !a->out || a->o_partial || a->lse)
+    return fail(L3CI_ERR_INVALID, "flash_decode_exchange: needs q and out, and takes no o_partial / lse");
+  if (!bufs || rank < 0 || rank >= ranks) return fail(L3CI_ERR_INVALID, "flash_decode_exchange: bad rank %d of %d or no buffers", rank, ranks);
+  if (a->n_seq > 0 && (!a->k || !a->v)) return fail(L3CI_ERR_INVALID, "flash_decode_exchange: null k or v");
+  if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (a->q_sb & 1) || (a->q_sh & 1) || (reinterpret_cast<uintptr_t>(a->out) & 3) ||
+      (a->o_sb & 1) || (a->o_sh & 1))
+    return fail(L3CI_ERR_ALIGNMENT, "flash_decode_exchange: q/out rows must start on 4 bytes");
+  if (a->n_seq > 0 && (!aligned16(a->k) || !aligned16(a->v) || (a->n_seq > 1 && (a->k_st % 8 || a->v_st % 8 || a->k_st <= 0 || a->v_st <= 0)) ||
+                       (a->Hkv > 1 && (a->k_sh % 8 || a->v_sh % 8)) || (a->B > 1 && (a->k_sb % 8 || a->v_sb % 8))))
+    return fail(L3CI_ERR_ALIGNMENT, "flash_decode_exchange: k/v rows must start on 16 bytes and strides be positive multiples of 8 elements");
+  // Only the static-deal kernel has the exchange in its tail.  An empty shard (n_seq == 0) still takes part: it
+  // sends zeros with a log-sum-exp of -inf.
+  if (a->Hq / a->Hkv > 8 || a->max_ctas > 0 || (a->n_seq > 0 && a->max_ctas == 0 && !takes_static_deal(a)))
+    return fail(L3CI_ERR_UNSUPPORTED, "flash_decode_exchange: these sizes go to the persistent kernel, which has no fused exchange; "
+                                      "use l3ci_flash_decode with o_partial / lse and l3ci_lse_exchange_merge");
+  FdExchange x{bufs, rank, ranks, epoch, status};
+  return flash_decode_small_launch(a, a->max_ctas < -1 ? -a->max_ctas : 0, &x);
+}
+
 extern "C" int l3ci_flash_decode_kernel_choice(int32_t B, int32_t Hq, int32_t Hkv, int32_t D, int32_t n_seq, int32_t ragged) {
   using namespace l3ci;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || (D != 64 && D != 128) || n_seq <= 0) return -1;

@@ -45,7 +45,130 @@ struct SmallParams {
   int lgW, lgC;  // log2 of: warps per unit (1, 2, 4, 8), CTAs per unit (a cluster; > 1 only with 8 warps per unit)
   long long q_sb, q_sh, k_sb, k_sh, k_st, v_sb, v_sh, v_st, o_sb, o_sh;
   float scale_log2e;
+  // kExchange instances: the KV sequence is sharded over `xranks` GPUs and the per-GPU results are merged here
+  unsigned long long* const* xbufs;  // device array of the ranks' exchange buffers (peer-mapped), [xrank] the local one
+  int xrank, xranks;
+  unsigned xepoch;                   // call number, the same on all ranks; 0 = kept in the buffer's control words
+  int* xstatus;                      // optional: receives L3CI_ERR_DEVICE_WAIT when a peer's values do not arrive
+  unsigned long long xwait_ns;
 };
+
+// ---------------------------------------------------------------------------------------------
+// Exchange of shard results across GPUs, folded into the tail of the decode kernel.
+//
+// With the KV sequence of a long context sharded over W GPUs, every GPU runs this kernel on its shard and ends up,
+// per output element (query row, column), with a softmax-normalised value and the row's log-sum-exp.  Instead of
+// writing them out for a second kernel, the thread that holds an element
+//   1. stores (value, call number) as ONE 64-bit word into the same place of every peer's exchange buffer (plain
+//      stores over NVLink; the thread of column 0 also sends the row's log-sum-exp),
+//   2. polls its own buffer until the W - 1 peers' words for that element and that row carry this call's number
+//      (a 64-bit store is single-copy atomic: a word that shows the number holds the value, so there is no fence,
+//      no separate flag and no second round trip),
+//   3. merges the W values by log-sum-exp and writes the bf16 output.
+// Buffer (64-bit words): [2 parities][W source ranks][rows * (D + 1)], word row * (D + 1) + col, col == D for the
+// log-sum-exp; then 2 control words (call number | CTAs finished).  Call e uses parity e & 1: a rank can only
+// start call e + 2 after it finished call e + 1, which needed every peer's words of call e + 1, which a peer sends
+// only at the end of a kernel that runs after its own call e has finished reading.  The wait is bounded: when it
+// runs out the element is left unwritten and the status word set.  Loads of remote memory: none.
+// ---------------------------------------------------------------------------------------------
+constexpr int kXchgMaxRanks = 8;
+
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct XchgView {
+  long long words;   // rows * (D + 1)
+  unsigned epoch;
+  unsigned long long* ctrl;
+};
+template <int D>
+__device__ __forceinline__ XchgView xchg_begin(const SmallParams& p) {
+  XchgView x;
+  x.words = (long long)p.B * p.Hq * (D + 1);
+  x.ctrl = p.xbufs[p.xrank] + 2LL * p.xranks * x.words;
+  // (read before this CTA counts itself finished; the number only moves once every CTA has)
+  x.epoch = p.xepoch ? p.xepoch : (unsigned)__ldcg(reinterpret_cast<const unsigned*>(x.ctrl)) + 1u;
+  return x;
+}
+// Steps 1-3 for the element (row, col) of this GPU's shard result; returns false if the wait ran out.
+template <int D>
+__device__ __forceinline__ bool xchg_element(const SmallParams& p, const XchgView& x, long long row, int col, float val,
+                                             float lse, float& merged) {
+  const int W = p.xranks, me = p.xrank;
+  const long long at = row * (D + 1) + col, at_lse = row * (D + 1) + D;
+  const long long mine = ((long long)(x.epoch & 1u) * W + me) * x.words;
+  const unsigned long long tag = (unsigned long long)x.epoch << 32;
+#pragma unroll
+  for (int s = 0; s < kXchgMaxRanks; ++s)
+    if (s < W && s != me) {
+      unsigned long long* dst = p.xbufs[s] + mine;
+      st_relaxed_sys_u64(dst + at, tag | __float_as_uint(val));
+      if (col == 0) st_relaxed_sys_u64(dst + at_lse, tag | __float_as_uint(lse));
+    }
+  const unsigned long long* loc = p.xbufs[me] + (long long)(x.epoch & 1u) * W * x.words;
+  float v[kXchgMaxRanks], l[kXchgMaxRanks];
+  unsigned got = 0;
+#pragma unroll
+  for (int s = 0; s < kXchgMaxRanks; ++s) {
+    v[s] = 0.f;
+    l[s] = -INFINITY;
+    if (s >= W || s == me) got |= 1u << s;
+  }
+  v[me & (kXchgMaxRanks - 1)] = val;
+  l[me & (kXchgMaxRanks - 1)] = lse;
+  unsigned long long t0 = 0;
+  for (unsigned it = 0; got != (1u << kXchgMaxRanks) - 1u; ++it) {
+#pragma unroll
+    for (int s = 0; s < kXchgMaxRanks; ++s)
+      if (!((got >> s) & 1u)) {
+        const unsigned long long a = ld_relaxed_sys_u64(loc + s * x.words + at);
+        const unsigned long long b = ld_relaxed_sys_u64(loc + s * x.words + at_lse);
+        if ((unsigned)(a >> 32) == x.epoch && (unsigned)(b >> 32) == x.epoch) {
+          v[s] = __uint_as_float((unsigned)a);
+          l[s] = __uint_as_float((unsigned)b);
+          got |= 1u << s;
+        }
+      }
+    if ((it & 31u) == 31u) {
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > p.xwait_ns) {
+        if (p.xstatus) atomicExch(p.xstatus, (int)L3CI_ERR_DEVICE_WAIT);
+        return false;
+      }
+    }
+  }
+  float M = -INFINITY;
+#pragma unroll
+  for (int s = 0; s < kXchgMaxRanks; ++s) M = fmaxf(M, l[s]);
+  const float Mu = M == -INFINITY ? 0.f : M;
+  float L = 0.f, acc = 0.f;
+#pragma unroll
+  for (int s = 0; s < kXchgMaxRanks; ++s) {
+    const float w = __expf(l[s] - Mu);  // exp(-inf) = 0: an empty shard, or a rank beyond W
+    L += w;
+    acc = fmaf(v[s], w, acc);
+  }
+  merged = L > 0.f ? acc / L : 0.f;
+  return true;
+}
+// The last CTA of the launch to finish advances the call number kept in the buffer (xepoch == 0).
+__device__ __forceinline__ void xchg_end(const SmallParams& p, const XchgView& x) {
+  if (p.xepoch == 0u && threadIdx.x == 0) {
+    unsigned* c = reinterpret_cast<unsigned*>(x.ctrl);
+    if (atomicAdd(c + 2, 1u) == gridDim.x - 1u) {
+      c[2] = 0u;
+      __threadfence();
+      c[0] = x.epoch;
+    }
+  }
+}
 
 // (policy: the cache is read once, so its lines are the first to leave L2: 3-4 % on calls of a few clusters)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid, uint64_t policy) {
@@ -78,7 +201,9 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t cta) {
 // launched the plain way, which starts sooner).  kWholeCta: all eight warps on one unit, known at compile time
 // (the merge loops then unroll without predicates: 0.5 us on a call of a few microseconds).
 // kWide: 12 warps x 2 tiles in flight instead of 8 x 3 (cluster instances on long runs of tiles).
-template <int D, bool kCluster, bool kWholeCta, bool kWide = false>
+// kExchange: the results of this launch are one GPU's shard of a sequence-sharded cache; the exchange with the
+// other GPUs and the merge happen in the kernel's tail (above) and `out` receives the merged attention.
+template <int D, bool kCluster, bool kWholeCta, bool kWide = false, bool kExchange = false>
 __global__ void __launch_bounds__(32 * (kWide ? kClWarps : kSmWarps))
 flash_decode_small_kernel(const SmallParams p) {
   static_assert(kWholeCta || !kCluster, "a cluster works on one unit with all warps of its CTAs");
@@ -302,6 +427,8 @@ flash_decode_small_kernel(const SmallParams p) {
   }
   __syncthreads();
 
+  XchgView xv{};
+  if constexpr (kExchange) xv = xchg_begin<D>(p);
   // ---- first level: the W states of each of this CTA's units.  Every thread folds them for its output elements
   //      (weights recomputed per element: a table built by a few threads first was slower by 0.5 us) ----
   float* cstate = states + NW * kStateFloats;  // [R * D] unnormalised sums, then m[8], l[8] (used with C > 1)
@@ -332,17 +459,27 @@ flash_decode_small_kernel(const SmallParams p) {
         cstate[r] = acc;
         if (col == 0) { cstate[8 * D + row] = M; cstate[8 * D + 8 + row] = L; }
       } else {
-        const float val = L > 0.f ? acc / L : 0.f;
+        float val = L > 0.f ? acc / L : 0.f;
+        const float lse = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
         const long long hq = (long long)uh * R + row;
+        if constexpr (kExchange) {
+          if (!xchg_element<D>(p, xv, (long long)ub * p.Hq + hq, col, val, lse, val)) continue;
+        }
         if (p.out) p.out[(long long)ub * p.o_sb + hq * p.o_sh + col] = __float2bfloat16(val);
         if (p.o_partial) {
           p.o_partial[((long long)ub * p.Hq + hq) * D + col] = val;
-          if (col == 0) p.lse[(long long)ub * p.Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+          if (col == 0) p.lse[(long long)ub * p.Hq + hq] = lse;
         }
       }
     }
   }
-  if constexpr (!kCluster) return;
+  if constexpr (!kCluster) {
+    if constexpr (kExchange) {
+      __syncthreads();  // every thread of the CTA has read the call number and is done with its elements
+      xchg_end(p, xv);
+    }
+    return;
+  }
 
   if constexpr (kCluster) {
   // ---- second level: the C per-CTA states of the unit, read through distributed shared memory; this CTA
@@ -371,15 +508,20 @@ flash_decode_small_kernel(const SmallParams p) {
       L = fmaf(l_c[c], wgt, L);
       acc = fmaf(a_c[c], wgt, acc);
     }
-    const float val = L > 0.f ? acc / L : 0.f;
+    float val = L > 0.f ? acc / L : 0.f;
+    const float lse = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
     const long long hq = (long long)head * R + row;
+    if constexpr (kExchange) {
+      if (!xchg_element<D>(p, xv, (long long)b * p.Hq + hq, col, val, lse, val)) continue;
+    }
     if (p.out) p.out[(long long)b * p.o_sb + hq * p.o_sh + col] = __float2bfloat16(val);
     if (p.o_partial) {
       p.o_partial[((long long)b * p.Hq + hq) * D + col] = val;
-      if (col == 0) p.lse[(long long)b * p.Hq + hq] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+      if (col == 0) p.lse[(long long)b * p.Hq + hq] = lse;
     }
   }
   cluster_sync();  // no CTA leaves while a peer may still read its shared memory
+  if constexpr (kExchange) xchg_end(p, xv);
   }
 }
 
@@ -388,24 +530,26 @@ flash_decode_small_kernel(const SmallParams p) {
 constexpr size_t kSmallSmemBytes = 1024 + (size_t)kSmWarps * kSmSlots * 8192;  // the merge states reuse the slots
 
 // Opt-in to the shared memory size, once per device and head size.
+template <int D>
+int configure_instances() {
+  const int bytes = (int)kSmallSmemBytes;
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, true, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<D, true, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return L3CI_OK;
+}
 int configure_small_kernel(int D) {
   static bool configured[2][64] = {{false}};
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
   const int di = D == 64 ? 0 : 1;
   if (dev >= 0 && dev < 64 && configured[di][dev]) return L3CI_OK;
-  const int bytes = (int)kSmallSmemBytes;
-  if (D == 64) {
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<64, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  } else {
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    L3CI_CUDA_TRY(cudaFuncSetAttribute(flash_decode_small_kernel<128, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  }
+  if (int st = D == 64 ? configure_instances<64>() : configure_instances<128>()) return st;
   if (dev >= 0 && dev < 64) configured[di][dev] = true;
   return L3CI_OK;
 }
@@ -468,8 +612,35 @@ int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {
   return 16 * s.C + s.W;
 }
 
-// split_code: 0 = unit_split's choice, else 16 * C + W (tuning).
-int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
+template <int D, bool kExchange>
+int launch_instance(const SmallParams& p, const UnitSplit& s, bool wide, size_t smem, cudaStream_t stream) {
+  if (s.C == 1) {  // (the instances without cluster instructions, launched the plain way)
+    const unsigned grid = (unsigned)s.ctas, block = 32 * kSmWarps;
+    if (s.W == kSmWarps) flash_decode_small_kernel<D, false, true, false, kExchange><<<grid, block, smem, stream>>>(p);
+    else flash_decode_small_kernel<D, false, false, false, kExchange><<<grid, block, smem, stream>>>(p);
+    L3CI_CHECK_LAUNCH("flash_decode_small_kernel");
+    return L3CI_OK;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)s.ctas);
+  cfg.blockDim = dim3(32 * (wide ? kClWarps : kSmWarps));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)s.C;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, true, kExchange>, p)
+                             : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, false, kExchange>, p);
+  if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));
+  return L3CI_OK;
+}
+
+// split_code: 0 = unit_split's choice, else 16 * C + W (tuning).  `x`: the exchange of a sequence-sharded call.
+int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code, const FdExchange* x) {
   const long long units = (long long)a->B * a->Hkv;
   const long long tiles = ((long long)a->n_seq + fd_tile_tokens(a->D) - 1) / fd_tile_tokens(a->D);
   if (int st = configure_small_kernel(a->D)) return st;
@@ -503,39 +674,19 @@ int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code) {
   p.v_sb = a->v_sb; p.v_sh = a->v_sh; p.v_st = a->v_st; p.o_sb = a->o_sb; p.o_sh = a->o_sh;
   const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)a->D);
   p.scale_log2e = scale * 1.4426950408889634f;
+  p.xbufs = nullptr; p.xrank = 0; p.xranks = 1; p.xepoch = 0; p.xstatus = nullptr; p.xwait_ns = 0;
+  if (x) {
+    if (x->ranks < 1 || x->ranks > kXchgMaxRanks || x->rank < 0 || x->rank >= x->ranks || !x->bufs)
+      return fail(L3CI_ERR_UNSUPPORTED, "flash_decode_exchange: %d ranks (1..%d are supported), rank %d", x->ranks, kXchgMaxRanks, x->rank);
+    p.xbufs = reinterpret_cast<unsigned long long* const*>(x->bufs);
+    p.xrank = x->rank; p.xranks = x->ranks; p.xepoch = x->epoch; p.xstatus = x->status;
+    p.xwait_ns = device_wait_limit_ns(1000000000ull);
+  }
   const size_t smem = kSmallSmemBytes;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  if (s.C == 1) {  // (the instance without cluster instructions, launched the plain way)
-    const unsigned grid = (unsigned)s.ctas, block = 32 * kSmWarps;
-    if (s.W == kSmWarps) {
-      if (a->D == 64) flash_decode_small_kernel<64, false, true><<<grid, block, smem, stream>>>(p);
-      else flash_decode_small_kernel<128, false, true><<<grid, block, smem, stream>>>(p);
-    } else {
-      if (a->D == 64) flash_decode_small_kernel<64, false, false><<<grid, block, smem, stream>>>(p);
-      else flash_decode_small_kernel<128, false, false><<<grid, block, smem, stream>>>(p);
-    }
-    L3CI_CHECK_LAUNCH("flash_decode_small_kernel");
-    return L3CI_OK;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)s.ctas);
   const bool wide = fd_static_wide(s, tiles);
-  cfg.blockDim = dim3(32 * (wide ? kClWarps : kSmWarps));
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)s.C;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t e = wide ? (a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true, true>, p)
-                                          : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true, true>, p))
-                             : (a->D == 64 ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<64, true, true, false>, p)
-                                           : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<128, true, true, false>, p));
-  if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));
-  return L3CI_OK;
+  if (a->D == 64) return x ? launch_instance<64, true>(p, s, wide, smem, stream) : launch_instance<64, false>(p, s, wide, smem, stream);
+  return x ? launch_instance<128, true>(p, s, wide, smem, stream) : launch_instance<128, false>(p, s, wide, smem, stream);
 }
 
 }  // namespace l3ci

@@ -23,8 +23,15 @@ int max_smem_optin();
 // Decode attention with units dealt statically to warps, CTAs or clusters (flash_decode_small.cu): whether
 // l3ci_flash_decode hands a call of these sizes to it, and its launch (arguments already validated by the
 // caller; split_code 0 = its own choice, else 16 * CTAs per unit + warps per unit).
+// `FdExchange` (optional): the cross-GPU exchange of a sequence-sharded call, done in the kernel's tail.
+struct FdExchange {
+  void* const* bufs;
+  int rank, ranks;
+  unsigned epoch;
+  int* status;
+};
 bool flash_decode_small_applies(int B, int Hq, int Hkv, int D, int n_seq, bool ragged);
-int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code);
+int flash_decode_small_launch(const l3ci_flash_decode_args* a, int split_code, const FdExchange* x = nullptr);
 // 16 * C + W of the split the static kernel would take for these sizes on the current device.
 int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq);
 

@@ -56,7 +56,13 @@ Tensor& workspace_for(const Tensor& like, size_t bytes) {
   const auto stream = c10::cuda::getCurrentCUDAStream();
   const auto key = std::make_pair((int)like.get_device(), (int64_t)stream.id());
   std::lock_guard<std::mutex> lock(g_ws_mutex);
-  Workspace& ws = workspaces()[key];
+  auto& all = workspaces();
+  if (all.size() >= 16 && all.find(key) == all.end()) {
+    // streams come and go (graph captures, side streams): the buffers of other streams are dropped rather than
+    // kept for the life of the process; a stream that comes back gets a fresh zero-filled one
+    for (auto it = all.begin(); it != all.end();) it = it->first.first == key.first ? all.erase(it) : std::next(it);
+  }
+  Workspace& ws = all[key];
   if (!ws.buf.defined() || (size_t)ws.buf.numel() < bytes) {
     ws.buf = torch::zeros({(int64_t)bytes}, torch::dtype(torch::kUInt8).device(like.device()));
   }
@@ -234,6 +240,46 @@ Tensor lse_exchange_merge(Tensor bufs, int64_t rank, int64_t epoch, int64_t B, i
                                        status ? status->data_ptr<int32_t>() : nullptr, current_stream()),
                "lse_exchange_merge");
   return out;
+}
+
+// Decode attention over this rank's slice of a sequence-sharded cache, merged with the other ranks' results in the
+// same launch (l3ci_flash_decode_exchange).  `bufs`: int64 CUDA tensor [ranks] of the ranks' exchange buffers as this
+// process addresses them.  Returns false-y (None) when the sizes go to the kernel without a fused exchange, so that
+// the caller can take the two-launch path.
+std::optional<Tensor> flash_attention_decode_exchange(Tensor query, Tensor keys, Tensor values, Tensor bufs, int64_t rank,
+                                                      int64_t epoch, std::optional<Tensor> seq_lens, std::optional<Tensor> out,
+                                                      std::optional<Tensor> status, double scale, int64_t max_ctas) {
+  const DecodeShapes s = check_decode_inputs(query, keys, values, seq_lens);
+  TORCH_CHECK(bufs.is_cuda() && bufs.scalar_type() == torch::kInt64 && bufs.dim() == 1 && bufs.is_contiguous() &&
+                  bufs.get_device() == query.get_device(),
+              "bufs must be a contiguous int64 CUDA tensor of buffer addresses on the device of the inputs");
+  if (status)
+    TORCH_CHECK(status->is_cuda() && status->scalar_type() == torch::kInt32 && status->numel() >= 1 &&
+                    status->get_device() == query.get_device(),
+                "status must be an int32 CUDA tensor");
+  const c10::cuda::CUDAGuard guard(query.device());
+  Tensor result = out ? *out : torch::empty_like(query);
+  if (out) {
+    check_bf16_cuda(result, "out");
+    TORCH_CHECK(result.sizes() == query.sizes() && result.stride(3) == 1, "out must be shaped like query");
+  }
+  if (s.B == 0) return result;
+  l3ci_flash_decode_args a{};
+  a.q = query.data_ptr(); a.k = keys.data_ptr(); a.v = values.data_ptr(); a.out = result.data_ptr();
+  a.seq_lens = seq_lens ? seq_lens->data_ptr<int32_t>() : nullptr;
+  a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.D = s.D; a.n_seq = s.n_seq;
+  a.q_sb = query.stride(0); a.q_sh = query.stride(1);
+  a.k_sb = keys.stride(0); a.k_sh = keys.stride(1); a.k_st = keys.stride(2);
+  a.v_sb = values.stride(0); a.v_sh = values.stride(1); a.v_st = values.stride(2);
+  a.o_sb = result.stride(0); a.o_sh = result.stride(1);
+  a.scale = (float)scale;
+  a.max_ctas = (int32_t)max_ctas;
+  a.stream = current_stream();
+  const int st = l3ci_flash_decode_exchange(&a, reinterpret_cast<void* const*>(bufs.data_ptr<int64_t>()), (int32_t)rank,
+                                            (int32_t)bufs.size(0), (uint32_t)epoch, status ? status->data_ptr<int32_t>() : nullptr);
+  if (st == L3CI_ERR_UNSUPPORTED) return std::nullopt;
+  check_status(st, "flash_attention_decode_exchange");
+  return result;
 }
 
 // reference: custom_kernels/custom_kernels.cu:369-389
@@ -433,6 +479,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return (int64_t)l3ci_flash_decode_kernel_choice((int32_t)B, (int32_t)Hq, (int32_t)Hkv, (int32_t)D, (int32_t)n_seq,
                                                     ragged ? 1 : 0);
   }, py::arg("device"), py::arg("B"), py::arg("Hq"), py::arg("Hkv"), py::arg("D"), py::arg("n_seq"), py::arg("ragged") = false);
+  m.def("flash_attention_decode_exchange", torch::wrap_pybind_function(flash_attention_decode_exchange),
+        "flash_attention_decode_exchange", py::arg("query"), py::arg("keys"), py::arg("values"), py::arg("bufs"),
+        py::arg("rank"), py::arg("epoch") = 0, py::kw_only(), py::arg("seq_lens") = py::none(), py::arg("out") = py::none(),
+        py::arg("status") = py::none(), py::arg("scale") = 0.0, py::arg("max_ctas") = 0);
+  m.def("flash_decode_exchange_bytes", [](int64_t ranks, int64_t B, int64_t Hq, int64_t D) {
+    return (int64_t)l3ci_flash_decode_exchange_bytes((int32_t)ranks, (int32_t)B, (int32_t)Hq, (int32_t)D);
+  });
   m.def("lse_exchange_bytes", [](int64_t ranks, int64_t B, int64_t Hq, int64_t D) {
     return (int64_t)l3ci_lse_exchange_bytes((int32_t)ranks, (int32_t)B, (int32_t)Hq, (int32_t)D);
   });

@@ -10,9 +10,11 @@ attention shards:
   ((D + 1) * Hq * 4 bytes per sequence and rank) and merged by log-sum-exp on every rank
   (`kv_shard_bounds`, `local_seq_lens`, `exchange_partials`, `decode_kv_sharded`).
 
-`KvShardExchange` + `decode_kv_sharded_fused` replace the all-gather and the merge kernel by ONE kernel per rank
-that pushes the rank's (o, lse) into its peers' memory over NVLink and merges what the peers pushed
-(`lse_exchange_merge`); the buffers are torch symmetric memory.
+`KvShardExchange` + `decode_kv_sharded_fused` replace the all-gather and the merge kernel by pushes of the rank's
+result into its peers' memory over NVLink and a merge of what the peers pushed; the buffers are torch symmetric
+memory.  Where the shard goes to the static-deal decode kernel (the usual case) all of that happens in the decode
+kernel's own tail, ONE launch per rank and step (`flash_attention_decode_exchange`); otherwise the decode kernel is
+followed by one exchange + merge kernel (`lse_exchange_merge`).
 
 Only `decode_kv_sharded*` touch a GPU; the rest is integer arithmetic and `torch.distributed`
 plumbing that also runs over gloo on CPU.
@@ -114,8 +116,17 @@ class KvShardExchange:
         # behind the data and the flags: a staging slot for this rank's own result, then the control words
         self.staging_base = 2 * self.world * self.slot_floats + ((2 * self.world * self.rows + 3) & ~3)
         self.epoch = 0
+        # second buffer: the exchange done in the decode kernel's own tail (one launch per step), with its own layout
+        nbytes1 = ext.flash_decode_exchange_bytes(self.world, B, Hq, D)
+        self.buf1 = symm_mem.empty(nbytes1 // 8, dtype=torch.int64, device=device)
+        self.buf1.zero_()
+        self.handle1 = symm_mem.rendezvous(self.buf1, self.group.group_name)
+        self.bufs1 = torch.tensor(list(self.handle1.buffer_ptrs), dtype=torch.int64, device=device)
+        self.epoch1 = 0
+        self.one_launch = None         # None: not tried yet; False: these sizes take the two-launch path
         torch.cuda.synchronize(device)
-        self.handle.barrier()          # every rank's buffer is zeroed before anyone may push into it
+        self.handle.barrier()          # every rank's buffers are zeroed before anyone may push into them
+        self.handle1.barrier()
 
     def slot(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Starts the next exchange and returns (o [B,Hq,D], lse [B,Hq]) views of this rank's own slot."""
@@ -152,10 +163,26 @@ class KvShardExchange:
 def decode_kv_sharded_fused(ext, q: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
                             xchg: KvShardExchange, seq_lens_local: Optional[torch.Tensor] = None,
                             device_epoch: bool = False) -> torch.Tensor:
-    """`decode_kv_sharded` with the exchange and the merge in one kernel over peer memory: two launches per step
-    (shard attention into the exchange buffer, then push + wait + merge) and no collective call.  With
-    `device_epoch` the step keeps no host state (fixed addresses, call number in the buffer) and can be captured
-    in a CUDA graph."""
+    """`decode_kv_sharded` with the exchange and the merge over peer memory and no collective call: one launch per
+    step where the shard takes the static-deal decode kernel (exchange in its tail), else two (shard attention into
+    the exchange buffer, then push + wait + merge).  With `device_epoch` the step keeps no host state (fixed
+    addresses, call number in the buffer) and can be captured in a CUDA graph."""
+    if xchg.one_launch is not False and xchg.world <= 8:
+        # the exchange in the decode kernel's tail; the library says when the head layout has no such kernel (more
+        # than 8 query heads per KV head), which is the same answer on every rank
+        epoch = 0
+        if not device_epoch:
+            xchg.epoch1 += 1
+            epoch = xchg.epoch1
+        # (max_ctas = -1: the static-deal kernel whatever the shard's length, so that every rank takes the same
+        # path even when the last shard is shorter than the others)
+        out = ext.flash_attention_decode_exchange(q, k_local, v_local, xchg.bufs1, xchg.rank, epoch,
+                                                  seq_lens=seq_lens_local, status=xchg.status, max_ctas=-1)
+        xchg.one_launch = out is not None
+        if out is not None:
+            return out
+        if not device_epoch:
+            xchg.epoch1 -= 1
     o, lse = xchg.staging() if device_epoch else xchg.slot()
     ext.flash_attention_decode_partial(q, k_local, v_local, seq_lens=seq_lens_local, out_o=o, out_lse=lse)
     return xchg.merge_auto() if device_epoch else xchg.merge()

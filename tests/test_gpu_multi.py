@@ -38,8 +38,8 @@ def _rank_main(rank, world, port, q):
         torch.cuda.synchronize()
         want = attention.sdpa_reference(case.q, case.k, case.v, case.seq_lens)
         compare.assert_close_attention(out, want)
-        # --- the same with the exchange fused into the merge kernel (peer stores over NVLink), three steps in a
-        #     row so that both parities of the exchange buffer and their reuse are exercised
+        # --- the same with the exchange over peer memory (plain stores over NVLink) in the decode kernel's tail,
+        #     three steps in a row so that both parities of the exchange buffer and their reuse are exercised
         xchg = pkg.sharding.KvShardExchange(ext, 2, 32, 128, dev)
         for step in range(3):
             c = inputs.decode_case(2, 32, 8, 128, 6000, seed=70 + step, ragged=True, min_len=100)
@@ -48,7 +48,19 @@ def _rank_main(rank, world, port, q):
             got = pkg.sharding.decode_kv_sharded_fused(ext, d.q, d.k[:, :, lo:hi], d.v[:, :, lo:hi], xchg, ll)
             torch.cuda.synchronize()
             compare.assert_close_attention(got, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
-        assert xchg.check() == 0
+        assert xchg.check() == 0 and xchg.one_launch is True     # exchange in the decode kernel's own tail
+        # --- the two-launch form (decode kernel, then exchange + merge kernel), kept for head layouts and sizes
+        #     that go to the persistent decode kernel
+        x2 = pkg.sharding.KvShardExchange(ext, 2, 32, 128, dev)
+        x2.one_launch = False
+        for step in range(3):
+            c = inputs.decode_case(2, 32, 8, 128, 6000, seed=75 + step, ragged=True, min_len=100)
+            d = c.to(dev)
+            ll = pkg.sharding.local_seq_lens(d.seq_lens, lo, hi)
+            got = pkg.sharding.decode_kv_sharded_fused(ext, d.q, d.k[:, :, lo:hi], d.v[:, :, lo:hi], x2, ll)
+            torch.cuda.synchronize()
+            compare.assert_close_attention(got, attention.sdpa_reference(c.q, c.k, c.v, c.seq_lens))
+        assert x2.check() == 0
         # --- the call number kept on the device: no host state, so the two launches of a step can be captured in
         #     a CUDA graph; eager steps first (both parities), then replays of one captured step on new inputs
         xa = pkg.sharding.KvShardExchange(ext, 2, 32, 128, dev)
