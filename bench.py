@@ -26,7 +26,8 @@ Printed JSON line (rank 0):
                  rank 0's merged output is checked against the CPU oracle BEFORE timing and the process
                  exits non-zero on a mismatch; strong scaling
   c1, c4_rmsnorm, c4_rope, c5
-                 (default workload, N = 1) the other configurations, each with its own roofline
+                 (default workload, N = 1) the other configurations, each with its own roofline; prefill_d64 and
+                 prefill_d128: causal prefill attention (the step before the path) against torch's SDPA
   comparators    torch's SDPA on the same GPU tensors; and, at N = 1, the reference's own CUDA kernels rebuilt
                  for sm_100 (oracle/_ref, when present), timed beside this library's calls
 
@@ -340,6 +341,11 @@ def add_sub_records(line, args, ext, pkg, dev, rank, world):
             line.setdefault("comparators", {})["reference_cuda_sm100"] = time_reference_cuda(ext, pkg, dev)
         except Exception as exc:   # optional evidence, never a reason to lose the bench line
             line.setdefault("comparators", {})["reference_cuda_sm100"] = {"error": str(exc)[:300]}
+        torch.cuda.empty_cache()
+    for hd in (64, 128):
+        pf_args = argparse.Namespace(**vars(args))
+        pf_args.head_dim = hd
+        line[f"prefill_d{hd}"] = brief(bench_prefill(pf_args, ext, pkg, dev, rank, world))
         torch.cuda.empty_cache()
     c5_args = argparse.Namespace(**vars(args))
     c5_args.no_cpu_baseline = True
@@ -841,8 +847,10 @@ def bench_prefill(args, ext, pkg, dev, rank, world):
         "config": {"workload": f"causal GQA prefill B={B} Hq={Hq} Hkv={Hkv} D={D} T={T}", "flops_per_step": flops,
                    "l2": f"{n_rot} rotating q/k/v sets", "max_abs_diff_vs_torch_sdpa_gpu": float((got - ref).abs().max())},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": "measured" if peaks else "fallback", "kernel": "prefill_attention_kernel",
-                     "note": "mma.sync path; its own ceiling is about a quarter of the tcgen05 peak the denominator was measured with"},
+                     "traffic": None, "peak_kind": "measured" if peaks else "fallback",
+                     "kernel": "prefill_tc_kernel (tcgen05 + tensor memory)" if D == 128 else "prefill_attention_kernel (mma.sync)",
+                     "note": None if D == 128 else "mma.sync path; its own ceiling is about a quarter of the tcgen05 peak the "
+                                                   "denominator was measured with"},
         "comparators": {"torch_sdpa_gpu": {"ms_per_step": sd_ms, "TFLOP/s": flops / (sd_ms * 1e-3) / 1e12,
                                            "call": "F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)"}},
         "gpu_launches": steps, "clocks": sampler.summary(),
@@ -884,7 +892,26 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world, workload):
     value = nbytes * world * args.steps / (ms_max * 1e-3) / 1e9
     peak, peak_kind = hbm_peak()
     achieved = nbytes / (ms_total / args.steps * 1e-3) / 1e9
-    return {
+    # What a plain pass over the SAME number of bytes reaches when it is timed the same way (torch's elementwise
+    # kernel over rotating buffers, replayed from a graph): the measured peak is a 2 GB copy, and a launch of a few tens of MB
+    # spends a fifth of its time ramping up and draining whatever it does.
+    comparators = None
+    if world == 1 and not args.no_comparator:
+        half = nbytes // 4   # bf16 elements read (and as many written)
+        src = [torch.empty(half, dtype=torch.bfloat16, device=dev).normal_() for _ in range(n_rot)]
+        dst = [torch.empty_like(src[0]) for _ in range(n_rot)]
+        # (an elementwise kernel: copy_ of same-dtype contiguous tensors becomes a driver memcpy, timed quite differently)
+        cp_step = lambda i: torch.neg(src[i % n_rot], out=dst[i % n_rot])  # noqa: E731
+        cp_run = eager_runner(cp_step) if args.no_graph else graph_runner(cp_step, n_rot, dev)
+        cp_run.prepare(args.steps)
+        cp_run(n_rot)
+        _, cp_total, _ = timed_regions(cp_run, args.steps, 1, dev)
+        cp_gbs = 4 * half / (cp_total / args.steps * 1e-3) / 1e9
+        comparators = {"torch_elementwise_same_bytes": {"ms_per_step": cp_total / args.steps, "GB/s": cp_gbs,
+                                                 "kernel_frac_of_this_copy": achieved / cp_gbs,
+                                                 "call": "torch.neg(src, out=dst), bf16, read + write = the kernel's algorithmic bytes"}}
+        del src, dst
+    line = {
         "metric": "pre-attention HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -897,6 +924,9 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world, workload):
                      "frac_of_8TBs_nominal": achieved / 8000.0},
         "gpu_launches": args.steps, "clocks": sampler.summary(),
     }
+    if comparators is not None:
+        line["comparators"] = comparators
+    return line
 
 
 def bench_end_to_end(args, ext, pkg, dev, rank, world):
@@ -991,7 +1021,54 @@ def bench_end_to_end(args, ext, pkg, dev, rank, world):
         line["cpu_baseline"] = cpu
     if ref_loop is not None:
         line["comparators"] = {"reference_model_loop": ref_loop}
+        try:
+            line["comparators"]["sampling_step"] = time_sampling_step(ext, dev, B, cfg.vocab_size)
+        except Exception as exc:
+            line["comparators"]["sampling_step"] = {"error": str(exc)[:300]}
     return line
+
+
+def time_sampling_step(ext, dev, B, vocab):
+    """The token choice of one decode step over logits [B, vocab]: this library's greedy and nucleus-sampling kernels,
+    and the reference's sampling branch as torch runs it (model.py:367-369 + sample_top_p, model.py:400-423:
+    softmax, full sort, cumsum, mask, renormalise, multinomial, gather), each as eager calls with CUDA events."""
+    logits = torch.randn(B, vocab, device=dev).bfloat16()
+    out = torch.zeros(B, 4, dtype=torch.int64, device=dev)
+    steps = torch.zeros(B, dtype=torch.int64, device=dev)
+    cur = torch.zeros(B, dtype=torch.int64, device=dev)
+    pos = torch.zeros(B, dtype=torch.int32, device=dev)
+    lens = torch.zeros(B, dtype=torch.int32, device=dev)
+
+    def reference_sampling():
+        probs = torch.softmax(logits.float() / 0.6, dim=-1)
+        ps, pi = torch.sort(probs, dim=-1, descending=True)
+        mask = torch.cumsum(ps, dim=-1) - ps > 0.9
+        ps[mask] = 0.0
+        ps.div_(ps.sum(dim=-1, keepdim=True))
+        return torch.gather(pi, -1, torch.multinomial(ps, num_samples=1))
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / n
+
+    def reset_then(fn):
+        def run():
+            steps.zero_()
+            fn()
+        return run
+
+    return {"batch": B, "vocab": vocab, "temperature": 0.6, "top_p": 0.9,
+            "top_p_step_us": timed(reset_then(lambda: ext.top_p_step(logits, out, steps, cur, pos, lens, 0.6, 0.9, 1)), 50),
+            "greedy_step_us": timed(reset_then(lambda: ext.greedy_step(logits, out, steps, cur, pos, lens)), 50),
+            "torch_sample_top_p_us": timed(reference_sampling, 10)}
 
 
 def time_reference_model_loop(pkg, dev, B, P, G, prompts):

@@ -92,6 +92,23 @@ L3CI_API int l3ci_greedy_step(const void* logits, int64_t rows, int64_t vocab, i
                               int64_t* next_input, int32_t* positions, int32_t* seq_lens,
                               l3ci_stream_t stream);
 
+/* Nucleus (top-p) sampling decode step: for every row b of bf16 logits [rows, vocab],
+ *   probs = softmax(logits / temperature); nucleus = the entries whose PRECEDING probability mass, in descending
+ *   order of probability (equal entries in index order), is <= top_p; tok = one draw from the nucleus with
+ *   probabilities renormalised;
+ * then the same bookkeeping as l3ci_greedy_step.  What `sample_top_p` does with a full-vocabulary sort, a
+ * cumulative sum, a multinomial draw and a gather (model.py:367-369, 400-423), as one kernel without a sort.  The
+ * draw of row b at step steps[b] (0 without steps) comes from a Philox4x32-10 stream keyed by `seed`: the same
+ * (seed, row, step) gives the same token, different steps give independent draws, and nothing on the host changes
+ * from step to step (the call can sit in a CUDA graph).  temperature and top_p must be positive (temperature 0 is
+ * the greedy branch of the reference: l3ci_greedy_step).  Optional outputs for inspection: nucleus_count[b]
+ * (entries kept) and nucleus_mass[b] (their probability mass before renormalisation).  Masses are summed in fp32:
+ * an entry whose preceding mass is within ~1e-6 of top_p may fall on either side. */
+L3CI_API int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, int64_t row_stride, float temperature,
+                             float top_p, uint64_t seed, int64_t* out_tokens, int64_t out_stride, int64_t out_cols,
+                             int64_t* steps, int64_t* next_input, int32_t* positions, int32_t* seq_lens,
+                             int32_t* nucleus_count, float* nucleus_mass, l3ci_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Rotary embedding, interleaved-pair (Meta) convention:
  *   (x', y') = (x*c - y*s, x*s + y*c) for (x, y) = in[.., 2i], in[.., 2i+1] and

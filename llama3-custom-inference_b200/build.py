@@ -35,7 +35,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "--expt-relaxed-constexpr",
 ]
-CUDA_SOURCES = ["host_common.cu", "rms_norm.cu", "rope.cu", "flash_decode.cu", "flash_decode_small.cu", "lse_merge.cu", "greedy_step.cu", "prefill_attention.cu", "prefill_attention_tc.cu"]
+CUDA_SOURCES = ["host_common.cu", "rms_norm.cu", "rope.cu", "flash_decode.cu", "flash_decode_small.cu", "lse_merge.cu", "greedy_step.cu", "top_p_step.cu", "prefill_attention.cu", "prefill_attention_tc.cu"]
 
 
 def _nvcc() -> str:

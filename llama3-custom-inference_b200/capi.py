@@ -19,7 +19,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 # Every symbol include/l3ci_b200.h declares.
 EXPORTS = (
     "l3ci_status_string", "l3ci_last_error", "l3ci_version", "l3ci_set_device_wait_limit_ns",
-    "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
+    "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_top_p_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_flash_decode_kernel_choice",
     "l3ci_lse_merge", "l3ci_lse_exchange_bytes", "l3ci_lse_exchange_merge", "l3ci_prefill_attention",
@@ -94,6 +94,8 @@ def load() -> C.CDLL:
     lib.l3ci_prefill_attention.argtypes = [C.POINTER(PrefillArgs)]
     lib.l3ci_greedy_step.restype = C.c_int
     lib.l3ci_greedy_step.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, vp, vp, vp, vp]
+    lib.l3ci_top_p_step.restype = C.c_int
+    lib.l3ci_top_p_step.argtypes = [vp, i64, i64, i64, f32, f32, C.c_uint64, vp, i64, i64, vp, vp, vp, vp, vp, vp, vp]
     lib.l3ci_rot_embed.restype = C.c_int
     lib.l3ci_rot_embed.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp]
     lib.l3ci_rot_embed_kv_cache.restype = C.c_int
@@ -193,6 +195,19 @@ def greedy_step(logits, out_tokens=None, steps=None, next_input=None, positions=
                                        out_tokens.shape[1] if out_tokens is not None and out_tokens.dim() == 2 else 1,
                                        ptr(steps), ptr(next_input), ptr(positions), ptr(seq_lens), _stream(logits)),
                "l3ci_greedy_step")
+
+
+def top_p_step(logits, temperature: float, top_p: float, seed: int, out_tokens=None, steps=None, next_input=None,
+               positions=None, seq_lens=None, nucleus_count=None, nucleus_mass=None):
+    """One nucleus-sampling step over bf16 logits [B, vocab] plus the decode bookkeeping, in place (l3ci_top_p_step)."""
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+    with _on(logits):
+        _check(load().l3ci_top_p_step(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0), temperature,
+                                      top_p, seed, ptr(out_tokens), out_tokens.stride(0) if out_tokens is not None else 0,
+                                      out_tokens.shape[1] if out_tokens is not None and out_tokens.dim() == 2 else 1,
+                                      ptr(steps), ptr(next_input), ptr(positions), ptr(seq_lens), ptr(nucleus_count),
+                                      ptr(nucleus_mass), _stream(logits)), "l3ci_top_p_step")
 
 
 def rot_embed(x, freq):

@@ -105,6 +105,150 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Many rows (a prefill or a token batch): a persistent grid in which every WARP owns a stream of rows.
+//
+// The kernel above spends a CTA per row: 4096 rows of 2048 columns are 4096 CTAs of 128 threads that each load two
+// vectors, meet at two barriers and leave — the launch ramp, the CTA turnover and ~15 instructions per element
+// pair keep it at two thirds of the copy bandwidth.  Here a warp keeps the weight row in registers for its whole
+// life, holds a row as VPL 16-byte vectors per lane, has the NEXT row's loads in flight while it reduces and
+// writes the current one, reduces with shuffles only (no shared memory, no barrier), and does the fp32 arithmetic
+// two lanes at a time (fma.rn.f32x2 / mul.rn.f32x2, exact per component), which halves the arithmetic issue slots.
+// Same values as the kernel above except for the order of the fp32 sum of squares.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// The two bf16 of a packed word widened to an fp32 pair.
+__device__ __forceinline__ unsigned long long bf16x2_to_f32x2(uint32_t w) {
+  return pack_f32x2(bf16lo_to_f32(w), bf16hi_to_f32(w));
+}
+
+constexpr int kRowsBlock = 256;  // 8 warps, each on its own rows
+
+// (Two CTAs per SM, i.e. 128 registers per thread; the widest rows with a residual need more and run one per SM.
+// With eight vectors per lane the weight row is re-read from L1 for every row instead of held in registers.)
+template <int VPL, bool kRes>
+__global__ void __launch_bounds__(kRowsBlock, (VPL >= 8 && kRes) ? 1 : 2)
+rms_norm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                     __nv_bfloat16* __restrict__ out, long long rows, int nvec, long long x_stride, long long out_stride,
+                     float embed_f, float eps, const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ sum_out) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (kRowsBlock / 32);
+  long long row = (long long)blockIdx.x * (kRowsBlock / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  constexpr bool kKeepW = VPL < 8;
+  uint4 wv[kKeepW ? VPL : 1];
+  if constexpr (kKeepW) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int idx = lane + 32 * i;
+      wv[i] = idx < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + idx) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  const long long dense = (long long)nvec * kVecElems;  // row length of res / sum_out
+  uint4 cur[VPL], nxt[VPL], rcur[kRes ? VPL : 1], rnxt[kRes ? VPL : 1];
+  auto fetch = [&](long long r, uint4 (&v)[VPL], uint4 (&rv)[kRes ? VPL : 1]) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int idx = lane + 32 * i;
+      const bool ok = idx < nvec;
+      v[i] = ok ? ld_stream16(x + r * x_stride + (long long)idx * kVecElems) : make_uint4(0, 0, 0, 0);
+      if constexpr (kRes) rv[i] = ok ? ld_stream16(res + r * dense + (long long)idx * kVecElems) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  fetch(row, cur, rcur);
+  while (true) {
+    const long long next = row + warps;
+    const bool more = next < rows;
+    if (more) fetch(next, nxt, rnxt);
+    if constexpr (kRes) {  // s = bf16(x + residual), written out and normalised
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        float a[8], b[8];
+        unpack8(cur[i], a);
+        unpack8(rcur[i], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = __fadd_rn(a[j], b[j]);
+        cur[i] = pack8(a);
+        const int idx = lane + 32 * i;
+        if (idx < nvec) *reinterpret_cast<uint4*>(sum_out + row * dense + (long long)idx * kVecElems) = cur[i];
+      }
+    }
+    unsigned long long acc0 = 0ull, acc1 = 0ull;  // two fp32 pairs of partial sums
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const unsigned long long p0 = bf16x2_to_f32x2(cur[i].x), p1 = bf16x2_to_f32x2(cur[i].y);
+      const unsigned long long p2 = bf16x2_to_f32x2(cur[i].z), p3 = bf16x2_to_f32x2(cur[i].w);
+      acc0 = fma_f32x2(p0, p0, acc0);
+      acc1 = fma_f32x2(p1, p1, acc1);
+      acc0 = fma_f32x2(p2, p2, acc0);
+      acc1 = fma_f32x2(p3, p3, acc1);
+    }
+    float s0, s1, s2, s3;
+    unpack_f32x2(acc0, s0, s1);
+    unpack_f32x2(acc1, s2, s3);
+    const float ss = group_sum<32>((s0 + s1) + (s2 + s3));
+    const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, embed_f), eps));
+    const unsigned long long inv2 = pack_f32x2(inv, inv);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < nvec) {
+        const uint32_t xs[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+        const uint4 wi = kKeepW ? wv[kKeepW ? i : 0] : __ldg(reinterpret_cast<const uint4*>(w) + idx);
+        const uint32_t ws[4] = {wi.x, wi.y, wi.z, wi.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          unpack_f32x2(mul_f32x2(mul_f32x2(bf16x2_to_f32x2(xs[j]), inv2), bf16x2_to_f32x2(ws[j])), lo, hi);
+          o[j] = pack_bf16x2(lo, hi);
+        }
+        st_stream16(out + row * out_stride + (long long)idx * kVecElems, make_uint4(o[0], o[1], o[2], o[3]));
+      }
+    }
+    if (!more) break;
+    row = next;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      cur[i] = nxt[i];
+      if constexpr (kRes) rcur[i] = rnxt[i];
+    }
+  }
+}
+
+template <int VPL>
+int launch_rows(const void* x, const void* w, void* out, long long rows, int nvec, long long xs, long long os, float eps,
+                cudaStream_t stream, const void* res, void* sum_out) {
+  const int sms = sm_count();
+  if (sms <= 0) return fail(L3CI_ERR_CUDA, "rms_norm: no CUDA device");
+  const long long want = (rows + kRowsBlock / 32 - 1) / (kRowsBlock / 32);
+  const long long per_sm = (VPL >= 8 && res) ? 1 : 2;  // CTAs an SM holds (see the launch bounds); all resident for the whole launch
+  const unsigned grid = (unsigned)(want < per_sm * sms ? want : per_sm * sms);
+  const auto xb = static_cast<const __nv_bfloat16*>(x), wb = static_cast<const __nv_bfloat16*>(w), rb = static_cast<const __nv_bfloat16*>(res);
+  const auto ob = static_cast<__nv_bfloat16*>(out), sb = static_cast<__nv_bfloat16*>(sum_out);
+  if (res) rms_norm_rows_kernel<VPL, true><<<grid, kRowsBlock, 0, stream>>>(xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
+  else rms_norm_rows_kernel<VPL, false><<<grid, kRowsBlock, 0, stream>>>(xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
+  L3CI_CHECK_LAUNCH("rms_norm_rows_kernel");
+  return L3CI_OK;
+}
+
 template <int TPR, int VPT>
 int launch(const void* x, const void* w, void* out, long long rows, int nvec, long long xs,
            long long os, float eps, cudaStream_t stream, const void* res, void* sum_out) {
@@ -140,6 +284,15 @@ int rms_norm_dispatch(const void* x, const void* weight, void* out, int64_t rows
       out_row_stride % kVecElems || (res && !aligned16(res)) || (sum_out && !aligned16(sum_out)))
     return fail(L3CI_ERR_ALIGNMENT, "%s: rows must start on 16 bytes", what);
   const int nvec = (int)(embed / kVecElems);
+  // Many rows of up to 2048 columns: a warp per row in a persistent grid (from a few rows per warp of the device on;
+  // below that the rows-in-flight of the one-CTA-per-row kernel win).
+  if (nvec <= 256 && rows >= 16LL * sm_count()) {
+    const int vpl = (nvec + 31) / 32;
+    if (vpl <= 1) return launch_rows<1>(x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    if (vpl <= 2) return launch_rows<2>(x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    if (vpl <= 4) return launch_rows<4>(x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+    return launch_rows<8>(x, weight, out, rows, nvec, x_row_stride, out_row_stride, eps, stream, res, sum_out);
+  }
   // Thread group per row: two vectors per thread where the row allows it (measured on B200 at 2048 columns:
   // 128 threads x 2 vectors beat 32 x 8 by 1 us of 13 at 4096 rows and by 2 us of 8 at 64 rows: the loads of a
   // row are one or two deep instead of eight), up to eight per thread for the longest rows.

@@ -33,10 +33,8 @@ __device__ __forceinline__ void rotate_pair(float x, float y, float c, float s, 
   yo = __fmaf_rn(x, s, __fmul_rn(y, c));
 }
 
-// Rotates the 8 bf16 of `v` with the table entries freq8[0..7] = (c0,s0,c1,s1,c2,s2,c3,s3).
-__device__ __forceinline__ uint4 rotate8(const uint4& v, const float* __restrict__ freq8) {
-  const float4 f0 = __ldg(reinterpret_cast<const float4*>(freq8));
-  const float4 f1 = __ldg(reinterpret_cast<const float4*>(freq8) + 1);
+// Rotates the 8 bf16 of `v` with the table entries (f0, f1) = (c0,s0,c1,s1 | c2,s2,c3,s3).
+__device__ __forceinline__ uint4 rotate8(const uint4& v, const float4& f0, const float4& f1) {
   float a[8], r[8];
   unpack8(v, a);
   rotate_pair(a[0], a[1], f0.x, f0.y, r[0], r[1]);
@@ -45,13 +43,22 @@ __device__ __forceinline__ uint4 rotate8(const uint4& v, const float* __restrict
   rotate_pair(a[6], a[7], f1.z, f1.w, r[6], r[7]);
   return pack8(r);
 }
+__device__ __forceinline__ uint4 rotate8(const uint4& v, const float* __restrict__ freq8) {
+  return rotate8(v, __ldg(reinterpret_cast<const float4*>(freq8)), __ldg(reinterpret_cast<const float4*>(freq8) + 1));
+}
 
 // x [B,S,H,D] strided, out dense.  One CTA per token: (batch, position) is decoded once per CTA and the
-// threads stride over the token's H * D/8 vectors, so no thread does 64-bit index arithmetic.
+// threads stride over the token's H * D/8 vectors, so no thread does 64-bit index arithmetic.  VPH = vectors per
+// head when that is 8 or 16 (head size 64 or 128; 0 = any): the CTA size is a multiple of it, so all vectors of a
+// thread sit at the same place of their heads and share ONE pair of table loads, and head / vector indices are
+// shifts (at 15 instructions per element pair the first version of this kernel was bound by instruction issue,
+// not by memory: two table loads per vector and two integer divisions were most of them).
+template <int VPH>
 __global__ void __launch_bounds__(kTokenBlock)
 rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freq,
-                      __nv_bfloat16* __restrict__ out, int S, int H, int vec_per_head, long long sb, long long ss,
+                      __nv_bfloat16* __restrict__ out, int S, int H, int vec_per_head_rt, long long sb, long long ss,
                       long long sh) {
+  const int vec_per_head = VPH ? VPH : vec_per_head_rt;
   const long long token = blockIdx.x;
   const int s = (int)(token % S);
   const long long b = token / S;
@@ -60,6 +67,12 @@ rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
   const __nv_bfloat16* xin = x + b * sb + s * ss;
   __nv_bfloat16* xout = out + token * (long long)row_vecs * kVecElems;
   const float* f = freq + (long long)s * D;
+  float4 f0 = make_float4(0, 0, 0, 0), f1 = f0;
+  if constexpr (VPH != 0) {
+    const float* fv = f + (threadIdx.x % VPH) * kVecElems;
+    f0 = __ldg(reinterpret_cast<const float4*>(fv));
+    f1 = __ldg(reinterpret_cast<const float4*>(fv) + 1);
+  }
   for (int i0 = threadIdx.x; i0 < row_vecs; i0 += kTokenBlock * kTokenBatch) {
     uint4 v[kTokenBatch];
 #pragma unroll
@@ -73,7 +86,9 @@ rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
 #pragma unroll
     for (int u = 0; u < kTokenBatch; ++u) {
       const int i = i0 + u * kTokenBlock;
-      if (i < row_vecs) st_stream16(xout + i * kVecElems, rotate8(v[u], f + (i % vec_per_head) * kVecElems));
+      if (i >= row_vecs) continue;
+      if constexpr (VPH != 0) st_stream16(xout + i * kVecElems, rotate8(v[u], f0, f1));
+      else st_stream16(xout + i * kVecElems, rotate8(v[u], f + (i % vec_per_head) * kVecElems));
     }
   }
 }
@@ -99,14 +114,16 @@ rot_embed_pair_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
   *reinterpret_cast<uint32_t*>(out + idx * 2) = pack_bf16x2(xo, yo);
 }
 
-// qkv [B,T,(Hq+2Hkv)*D] -> q_out dense [B,T,Hq,D], cache_k/v[b, pos, h, :].  One CTA per token.
+// qkv [B,T,(Hq+2Hkv)*D] -> q_out dense [B,T,Hq,D], cache_k/v[b, pos, h, :].  One CTA per token; VPH as above.
+template <int VPH>
 __global__ void __launch_bounds__(kTokenBlock)
 rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ freq,
                           __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ cache_k,
-                          __nv_bfloat16* __restrict__ cache_v, int T, int Hq, int Hkv, int vec_per_head,
+                          __nv_bfloat16* __restrict__ cache_v, int T, int Hq, int Hkv, int vec_per_head_rt,
                           long long qkv_sb, long long qkv_st, long long cache_sb, long long cache_st,
                           long long start_pos, const int* __restrict__ positions, long long freq_rows,
                           long long cache_len) {
+  const int vec_per_head = VPH ? VPH : vec_per_head_rt;
   const long long token = blockIdx.x;
   const int t = (int)(token % T);
   const long long b = token / T;
@@ -126,6 +143,12 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
   __nv_bfloat16* vo = cache_v + b * cache_sb + pos * cache_st;
   const int q_vecs = Hq * vec_per_head, k_vecs = Hkv * vec_per_head;
   const int row_vecs = q_vecs + 2 * k_vecs;
+  float4 f0 = make_float4(0, 0, 0, 0), f1 = f0;
+  if constexpr (VPH != 0) {
+    const float* fv = f + (threadIdx.x % VPH) * kVecElems;
+    f0 = __ldg(reinterpret_cast<const float4*>(fv));
+    f1 = __ldg(reinterpret_cast<const float4*>(fv) + 1);
+  }
   for (int i0 = threadIdx.x; i0 < row_vecs; i0 += kTokenBlock * kTokenBatch) {
     uint4 v[kTokenBatch];
 #pragma unroll
@@ -137,17 +160,26 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
     for (int u = 0; u < kTokenBatch; ++u) {
       const int i = i0 + u * kTokenBlock;
       if (i >= row_vecs) continue;
-      const int vec = i % vec_per_head;
-      if (i < q_vecs) {
-        st_stream16(qo + i * kVecElems, rotate8(v[u], f + vec * kVecElems));
-      } else if (i < q_vecs + k_vecs) {
+      if (i < q_vecs + k_vecs) {
+        uint4 r;
+        if constexpr (VPH != 0) r = rotate8(v[u], f0, f1);
+        else r = rotate8(v[u], f + (i % vec_per_head) * kVecElems);
+        if (i < q_vecs) st_stream16(qo + i * kVecElems, r);
         // Cache rows are read again by the attention kernel of the same step: plain store.
-        *reinterpret_cast<uint4*>(ko + (i - q_vecs) * kVecElems) = rotate8(v[u], f + vec * kVecElems);
+        else *reinterpret_cast<uint4*>(ko + (i - q_vecs) * kVecElems) = r;
       } else {
         *reinterpret_cast<uint4*>(vo + (i - q_vecs - k_vecs) * kVecElems) = v[u];
       }
     }
   }
+}
+
+// Launch of the instance for this head size (8 or 16 vectors per head: shifts and shared table loads; else generic).
+template <typename... Args>
+void launch_kv_cache(int vec_per_head, unsigned grid, cudaStream_t stream, Args... args) {
+  if (vec_per_head == 8) rot_embed_kv_cache_kernel<8><<<grid, kTokenBlock, 0, stream>>>(args...);
+  else if (vec_per_head == 16) rot_embed_kv_cache_kernel<16><<<grid, kTokenBlock, 0, stream>>>(args...);
+  else rot_embed_kv_cache_kernel<0><<<grid, kTokenBlock, 0, stream>>>(args...);
 }
 
 int grid_for(long long total, unsigned* grid) {
@@ -179,7 +211,10 @@ extern "C" int l3ci_rot_embed(const void* x, const float* freq, void* out, int64
   if (vec8) {
     if (B * S > 0x7fffffffLL || H * (D / kVecElems) > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rot_embed: tensor too large");
     grid = (unsigned)(B * S);
-    rot_embed_vec8_kernel<<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, (int)(D / kVecElems), sb, ss, sh);
+    const int vph = (int)(D / kVecElems);
+    if (vph == 8) rot_embed_vec8_kernel<8><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
+    else if (vph == 16) rot_embed_vec8_kernel<16><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
+    else rot_embed_vec8_kernel<0><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
     L3CI_CHECK_LAUNCH("rot_embed_vec8_kernel");
     return L3CI_OK;
   }
@@ -213,10 +248,11 @@ extern "C" int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void*
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache: rows must start on 16 bytes");
   if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
     return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache: tensor too large");
-  rot_embed_kv_cache_kernel<<<(unsigned)(B * T), kTokenBlock, 0, stream>>>(
+  launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
       static_cast<const __nv_bfloat16*>(qkv), freq, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T,
-      (int)Hq, (int)Hkv, (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, start_pos, nullptr, 0, 0);
+      (int)Hq, (int)Hkv, (int)(D / kVecElems), (long long)qkv_sb, (long long)qkv_st, (long long)cache_sb, (long long)cache_st,
+      (long long)start_pos, (const int*)nullptr, 0LL, 0LL);
   L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
   return L3CI_OK;
 }
@@ -241,10 +277,11 @@ extern "C" int l3ci_rot_embed_kv_cache_at(const void* qkv, const float* freq_tab
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache_at: rows must start on 16 bytes");
   if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
     return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache_at: tensor too large");
-  rot_embed_kv_cache_kernel<<<(unsigned)(B * T), kTokenBlock, 0, stream>>>(
+  launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
       static_cast<const __nv_bfloat16*>(qkv), freq_table, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T, (int)Hq, (int)Hkv,
-      (int)(D / kVecElems), qkv_sb, qkv_st, cache_sb, cache_st, 0, positions, freq_rows, cache_len);
+      (int)(D / kVecElems), (long long)qkv_sb, (long long)qkv_st, (long long)cache_sb, (long long)cache_st, 0LL,
+      (const int*)positions, (long long)freq_rows, (long long)cache_len);
   L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
   return L3CI_OK;
 }

@@ -363,6 +363,35 @@ void greedy_step(Tensor logits, Tensor out_tokens, Tensor steps, Tensor next_inp
                "greedy_step");
 }
 
+// Nucleus sampling step in place (model.py:367-369 + sample_top_p, model.py:400-423, + the bookkeeping of
+// model.py:373-381): one token per row of logits [B, vocab] (bf16) drawn from the top-p nucleus of
+// softmax(logits / temperature); written like greedy_step writes its argmax.
+void top_p_step(Tensor logits, Tensor out_tokens, Tensor steps, Tensor next_input, Tensor positions, Tensor seq_lens,
+                double temperature, double top_p, int64_t seed) {
+  check_bf16_cuda(logits, "logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "logits must be [B, vocab] with a contiguous last axis");
+  TORCH_CHECK(temperature > 0 && top_p > 0, "temperature and top_p must be positive (temperature 0: greedy_step)");
+  const int64_t B = logits.size(0);
+  auto check = [&](const Tensor& t, at::ScalarType ty, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.device() == logits.device() && t.scalar_type() == ty, name, ": wrong device or dtype");
+  };
+  check(out_tokens, at::kLong, "out_tokens");
+  check(steps, at::kLong, "steps");
+  check(next_input, at::kLong, "next_input");
+  check(positions, at::kInt, "positions");
+  check(seq_lens, at::kInt, "seq_lens");
+  TORCH_CHECK(out_tokens.dim() == 2 && out_tokens.size(0) == B && out_tokens.stride(1) == 1, "out_tokens must be [B, G]");
+  TORCH_CHECK(steps.numel() == B && next_input.numel() == B && positions.numel() >= B && seq_lens.numel() >= B &&
+                  steps.is_contiguous() && next_input.is_contiguous() && positions.is_contiguous() && seq_lens.is_contiguous(),
+              "per-sequence state must be contiguous with one entry per row");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  check_status(l3ci_top_p_step(logits.data_ptr(), B, logits.size(1), logits.stride(0), (float)temperature, (float)top_p,
+                               (uint64_t)seed, out_tokens.data_ptr<int64_t>(), out_tokens.stride(0), out_tokens.size(1),
+                               steps.data_ptr<int64_t>(), next_input.data_ptr<int64_t>(), positions.data_ptr<int32_t>(),
+                               seq_lens.data_ptr<int32_t>(), nullptr, nullptr, current_stream()),
+               "top_p_step");
+}
+
 // reference: custom_kernels/custom_kernels.cu:418-442
 Tensor rot_embed(Tensor input, Tensor freq) {
   check_bf16_cuda(input, "input");
@@ -462,6 +491,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul", torch::wrap_pybind_function(silu_mul), "silu_mul", py::arg("gate"), py::arg("up"));
   m.def("greedy_step", torch::wrap_pybind_function(greedy_step), "greedy_step", py::arg("logits"), py::arg("out_tokens"),
         py::arg("steps"), py::arg("next_input"), py::arg("positions"), py::arg("seq_lens"));
+  m.def("top_p_step", torch::wrap_pybind_function(top_p_step), "top_p_step", py::arg("logits"), py::arg("out_tokens"),
+        py::arg("steps"), py::arg("next_input"), py::arg("positions"), py::arg("seq_lens"), py::arg("temperature"),
+        py::arg("top_p"), py::arg("seed"));
   m.def("rot_embed", torch::wrap_pybind_function(rot_embed), "rot_embed", py::arg("input"), py::arg("freq"));
   m.def("rot_embed_kv_cache", torch::wrap_pybind_function(rot_embed_kv_cache), "rot_embed_kv_cache",
         py::arg("qkv"), py::arg("freq"), py::arg("cache_k"), py::arg("cache_v"), py::arg("start_pos"),

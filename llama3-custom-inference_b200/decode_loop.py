@@ -3,9 +3,8 @@
 Host-side mirror of what the reference's model does around its three extension calls — `Block` /
 `CausalSelfAttention` / `MLP` / `LLaMA3.forward` (model.py:92-149, 203-232) and the greedy branch of
 `LLaMA3.generate` (model.py:363-381) — restricted to what the end-to-end benchmark needs: random-init
-weights of the Llama-3.2-1B architecture (or any `DecoderConfig`), a batch of equal-length prompts, greedy
-decoding with `ignore_eos`.  It is a harness, not a model library: no checkpoint loading, no sampling, no
-tokenizer.
+weights of the Llama-3.2-1B architecture (or any `DecoderConfig`), a batch of equal-length prompts, greedy or
+top-p decoding with `ignore_eos`.  It is a harness, not a model library: no checkpoint loading, no tokenizer.
 
 What differs from the reference's loop, all on the caller's side of the kernels:
   * rotary embedding, the K/V cache write and the split of q|k|v are one call (`rot_embed_kv_cache` with
@@ -16,8 +15,8 @@ What differs from the reference's loop, all on the caller's side of the kernels:
     per-step mask construction (model.py:211) and no `all(eos_reached)` host sync (model.py:380).
   * the residual add runs inside the RMSNorm that follows it (`add_rms_norm`), `c_fc2` and `c_fc` are one GEMM
     over the stacked weight, and `silu(gate) * up` is one kernel (`silu_mul`) instead of two elementwise passes.
-GEMMs and the embedding lookup are plain torch ops (cuBLAS); the greedy argmax with its token bookkeeping is one
-kernel (`greedy_step`); prefill attention (torch SDPA in the reference, model.py:114-116) is `prefill_attention`.
+GEMMs and the embedding lookup are plain torch ops (cuBLAS); the token choice (greedy argmax, or nucleus sampling)
+with its token bookkeeping is one kernel (`greedy_step` / `top_p_step`); prefill attention (torch SDPA in the reference, model.py:114-116) is `prefill_attention`.
 """
 from __future__ import annotations
 
@@ -134,29 +133,38 @@ class Llama3Decoder:
 
     # ---- greedy generation --------------------------------------------------------------------------------
     @torch.inference_mode()
-    def generate(self, prompts: torch.Tensor, max_gen_len: int, use_graph: bool = True) -> torch.Tensor:
+    def generate(self, prompts: torch.Tensor, max_gen_len: int, use_graph: bool = True, temperature: float = 0.0,
+                 top_p: float = 0.9, seed: int = 0) -> torch.Tensor:
         """prompts int64 [B, P] (equal lengths, on the device).  Returns the generated tokens int64
-        [B, max_gen_len].  With `use_graph` one decode step is captured in a CUDA graph and replayed."""
+        [B, max_gen_len].  With `use_graph` one decode step is captured in a CUDA graph and replayed.
+        `temperature` 0 is greedy decoding (model.py:370-371); a positive temperature draws every token from the
+        top-p nucleus of softmax(logits / temperature) (model.py:367-369), reproducibly for a given `seed`."""
         B, P = prompts.shape
         assert B <= self.max_batch and P + max_gen_len <= self.max_len
         dev = self.device
         out = torch.empty(B, max_gen_len, dtype=torch.int64, device=dev)
         positions = torch.zeros(B, dtype=torch.int32, device=dev)
         seq_lens = torch.full((B,), P, dtype=torch.int32, device=dev)
-        tok = self.forward(prompts, positions, seq_lens).argmax(dim=-1)                # prefill; model.py:371
-        out[:, 0] = tok
+        steps = torch.zeros(B, dtype=torch.int64, device=dev)  # next free column of `out`, per sequence
+        cur = torch.zeros(B, 1, dtype=torch.int64, device=dev)
+
+        def pick(logits):
+            # token choice, out[b, steps[b]] = token, cur[b] = token, steps / positions / seq_lens += 1: one kernel
+            if temperature > 0:
+                self.ext.top_p_step(logits, out, steps, cur.view(B), positions, seq_lens, temperature, top_p, seed)
+            else:
+                self.ext.greedy_step(logits, out, steps, cur.view(B), positions, seq_lens)  # model.py:370-381
+
+        pick(self.forward(prompts, positions, seq_lens))                                # prefill; model.py:363-371
         # static state of the decode step: everything the step reads or writes lives in these tensors
-        cur = tok.view(B, 1).clone()
         positions.fill_(P)
         seq_lens.fill_(P + 1)
-        steps = torch.ones(B, dtype=torch.int64, device=dev)   # next free column of `out`, per sequence
 
         def step():
             _nvtx_push("forward")
             logits = self.forward(cur, positions, seq_lens)
             _nvtx_pop()
-            # argmax, out[b, steps[b]] = token, cur[b] = token, steps / positions / seq_lens += 1: one kernel
-            self.ext.greedy_step(logits, out, steps, cur.view(B), positions, seq_lens)  # model.py:370-381
+            pick(logits)
 
         n_steps = max_gen_len - 1
         if n_steps <= 0:

@@ -6,6 +6,7 @@ never read the checkout.  What is executed from the reference:
   * model.precompute_freqs_cis / model.apply_scaling (model.py:27-60), imported from the reference's
     model.py with its compiled extension replaced by an empty stub module (model.py:23 imports it at
     module level; neither function touches it);
+  * model.sample_top_p (model.py:400-423) on seeded probability rows under torch.manual_seed;
   * the attention call of model.py:115-116 / benchmark_kernel.py:27-28,
     `sdpa_kernel(SDPBackend.FLASH_ATTENTION)` + `F.scaled_dot_product_attention(q, k, v, enable_gqa=True)`,
     on the bf16 CPU tensors of oracle.inputs (the reference has no other CPU-runnable attention path).
@@ -29,6 +30,10 @@ from oracle import inputs  # noqa: E402
 
 
 # name -> (B, Hq, Hkv, D, T, seed) of oracle.inputs.prefill_case
+# name -> (rows, vocab, scale of the N(0,1) logits, top_p, seed) for the reference's sample_top_p; TOP_P_DRAWS calls each
+TOP_P_CASES = {"flat": (3, 500, 1.0, 0.9, 11), "peaked": (2, 2000, 6.0, 0.9, 12), "half": (4, 300, 2.0, 0.5, 13)}
+TOP_P_DRAWS = 64
+
 PREFILL_CASES = {"d64_r4_t40": (2, 8, 2, 64, 40, 21), "d128_r2_t150": (1, 4, 2, 128, 150, 22)}
 
 
@@ -85,6 +90,13 @@ def main() -> None:
         with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
             out[f"prefill_{name}_bf16"] = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True).contiguous()
         out[f"prefill_{name}_inputs_sha256"] = sha(q) + sha(k) + sha(v)
+    # the reference's nucleus sampler (model.py:400-423) on seeded distributions, under a known RNG state
+    for name, (rows, vocab, scale, p, seed) in TOP_P_CASES.items():
+        g = torch.Generator().manual_seed(seed)
+        probs = torch.softmax(torch.randn(rows, vocab, generator=g) * scale, dim=-1)
+        torch.manual_seed(seed)
+        draws = torch.cat([model.sample_top_p(probs.clone(), p) for _ in range(TOP_P_DRAWS)], dim=1)
+        out[f"top_p_{name}_draws"] = draws.clone()
     out["torch_version"] = str(torch.__version__)
     dst = Path(__file__).with_name("reference_vectors.pt")
     torch.save(out, dst)

@@ -45,3 +45,20 @@ def test_graph_replay_equals_eager_and_tracks_the_cpu_loop(ext, pkg, device):
     assert checked >= B * G // 2
     err = (eager.cache_k[0][:, :P + G - 1].float().cpu() - cpu.cache_k[0][:, :P + G - 1].float()).abs().max().item()
     assert err < 0.1
+
+
+def test_sampled_generation_is_reproducible_and_graph_equals_eager(ext, pkg, device):
+    """temperature > 0: every token is a draw from the top-p nucleus (model.py:367-369); the draws are keyed by (seed,
+    sequence, step), so an eager loop and a replayed graph produce the same tokens, and another seed other ones."""
+    cfg = _small(pkg)
+    weights = pkg.decode_loop.init_weights(cfg, seed=5)
+    B, P, G = 3, 20, 12
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=torch.Generator().manual_seed(1)).to(device)
+    dec = pkg.decode_loop.Llama3Decoder(ext, cfg, device, max_batch=B, max_len=64, weights=weights)
+    a = dec.generate(prompts, G, use_graph=False, temperature=0.8, top_p=0.9, seed=3)
+    b = dec.generate(prompts, G, use_graph=True, temperature=0.8, top_p=0.9, seed=3)
+    c = dec.generate(prompts, G, use_graph=True, temperature=0.8, top_p=0.9, seed=4)
+    g = dec.generate(prompts, G, use_graph=True)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b) and not torch.equal(a, c) and not torch.equal(a, g)
+    assert int(a.min()) >= 0 and int(a.max()) < cfg.vocab_size

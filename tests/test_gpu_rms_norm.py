@@ -27,7 +27,11 @@ def test_config4_token_batch(capi, device):
 
 
 @pytest.mark.parametrize("rows,embed", [(1, 2048), (64, 2048), (7, 8), (5, 64), (3, 256), (33, 1000), (9, 4096),
-                                        (4, 8192), (3, 16384), (2, 5120), (130, 2056), (2, 65536)])
+                                        (4, 8192), (3, 16384), (2, 5120), (130, 2056), (2, 65536),
+                                        # many rows: the warp-per-row persistent kernel, 1, 2, 4 and 8 vectors per lane,
+                                        # full and ragged last vectors, more rows than one pass of the grid
+                                        (3000, 64), (2500, 512), (2400, 1000), (2368, 2048), (20011, 8), (9000, 776),
+                                        (2400, 2056)])
 def test_shapes(capi, device, rows, embed):
     g = torch.Generator().manual_seed(rows * 131 + embed)
     x = (torch.randn(rows, 1, embed, generator=g) * 3).bfloat16().to(device)
@@ -59,6 +63,21 @@ def test_strided_rows_and_untouched_padding(capi, device):
     assert (obuf[:, embed:] == 7.0).all()
 
 
+def test_strided_rows_of_a_token_batch(capi, device):
+    # enough rows for the warp-per-row kernel, rows 640 elements apart, padding must stay untouched
+    rows, embed, pitch = 2500, 512, 640
+    g = torch.Generator().manual_seed(2)
+    xbuf = torch.randn(rows, pitch, generator=g).bfloat16().to(device)
+    w = torch.randn(embed, generator=g).bfloat16().to(device)
+    obuf = torch.full((rows, pitch), 7.0, dtype=torch.bfloat16, device=device)
+    st = capi.load().l3ci_rms_norm(xbuf.data_ptr(), w.data_ptr(), obuf.data_ptr(), rows, embed, pitch, pitch, 1e-5,
+                                   torch.cuda.current_stream().cuda_stream)
+    assert st == capi.OK
+    torch.cuda.synchronize()
+    assert compare.max_bf16_ulp(obuf[:, :embed].contiguous(), rms_norm_reference(xbuf[:, :embed], w, 1e-5)) <= MAX_ULP
+    assert (obuf[:, embed:] == 7.0).all()
+
+
 def test_errors(capi, device):
     lib = capi.load()
     x = torch.zeros(2, 16, dtype=torch.bfloat16, device=device)
@@ -68,7 +87,8 @@ def test_errors(capi, device):
 
 # ---- residual add fused into the norm, and the SwiGLU gate (the elementwise passes either side of the norm) ----
 
-@pytest.mark.parametrize("rows,embed", [(64, 2048), (1, 2048), (7, 8), (33, 1000), (9, 4096), (3, 16384), (130, 2056)])
+@pytest.mark.parametrize("rows,embed", [(64, 2048), (1, 2048), (7, 8), (33, 1000), (9, 4096), (3, 16384), (130, 2056),
+                                        (8192, 2048), (2400, 512), (2500, 1000), (3000, 64)])
 def test_add_rms_norm(capi, device, rows, embed):
     g = torch.Generator().manual_seed(rows * 17 + embed)
     x = (torch.randn(rows, embed, generator=g) * 2).bfloat16().to(device)

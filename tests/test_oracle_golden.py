@@ -111,3 +111,29 @@ def test_bf16_ulp_distance():
     a = torch.tensor([1.0, -1.0, 0.0, 2.0]).bfloat16()
     b = torch.tensor([1.0078125, -1.0, -0.0, 1.9921875]).bfloat16()
     assert compare.bf16_ulp_distance(a, b).tolist() == [1, 0, 0, 1]
+
+
+TOP_P_CASES = {"flat": (3, 500, 1.0, 0.9, 11), "peaked": (2, 2000, 6.0, 0.9, 12), "half": (4, 300, 2.0, 0.5, 13)}
+
+
+@pytest.mark.parametrize("name", sorted(TOP_P_CASES))
+def test_top_p_oracle_matches_the_references_sampler(golden, name):
+    """The golden draws are what the reference's own sample_top_p (model.py:400-423) returned for these seeded
+    distributions under torch.manual_seed(seed): the restatement must return the same tokens, and every one of them
+    must lie in the nucleus the oracle describes."""
+    from oracle import sampling
+
+    rows, vocab, scale, p, seed = TOP_P_CASES[name]
+    g = torch.Generator().manual_seed(seed)
+    probs = torch.softmax(torch.randn(rows, vocab, generator=g) * scale, dim=-1)
+    want = golden[f"top_p_{name}_draws"]
+    torch.manual_seed(seed)
+    got = torch.cat([sampling.sample_top_p_reference(probs.clone(), p) for _ in range(want.shape[1])], dim=1)
+    assert torch.equal(got, want)
+    kept, renorm, before = sampling.nucleus_reference(probs, p)
+    assert bool(torch.gather(kept, 1, want).all())
+    assert torch.allclose(renorm.sum(-1), torch.ones(rows, dtype=torch.float64))
+    # the nucleus is the shortest descending prefix whose mass exceeds p
+    mass = (probs.double() * kept).sum(-1)
+    smallest_kept = torch.where(kept, probs.double(), torch.ones_like(probs.double())).min(-1).values
+    assert bool((mass > p).all()) and bool((mass - smallest_kept <= p + 1e-12).all())
