@@ -335,7 +335,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     constexpr int kOHalf = D / 2;
     const bool any_me = __any_sync(kFullMask, a_me != 0.f), any_ot = __any_sync(kFullMask, a_ot != 0.f);
-    __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh + (long long)t * p.o_st + e * kOHalf;
+    // The merged rows go through shared memory: a thread holds 64 or 32 columns of ONE row, and storing them straight
+    // to global memory makes every store instruction of a warp touch 32 rows (32 sectors for 128 bytes of payload;
+    // that epilogue took 5.9 us of a CTA's life, as long as four tiles of the main loop).  The K and V stages are
+    // free by now: both groups have seen their last product complete before the barrier above.  Rows are 16 bytes
+    // further apart than their length, so that the 16-byte stores of eight neighbouring rows fall into eight
+    // different bank groups.
+    constexpr int kPitch = D * 2 + 16;
+    uint8_t* stage = smem + kTileBytes;
 #pragma unroll
     for (int c = 0; c < kOHalf / 32; ++c) {
       uint32_t y0[32], y1[32];
@@ -343,21 +350,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       if (any_me) tmem_ld32(t_o[e] + lane_addr + e * kOHalf + c * 32, y0);
       if (any_ot) tmem_ld32(t_o[e ^ 1] + lane_addr + e * kOHalf + c * 32, y1);
       tc_wait_ld();
-      if (ok && t < p.T) {
+      uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = 0.f, v1 = 0.f;
-          if (a_me != 0.f) {
-            v0 = __uint_as_float(y0[i]) * a_me;
-            v1 = __uint_as_float(y0[i + 1]) * a_me;
-          }
-          if (a_ot != 0.f) {
-            v0 = fmaf(__uint_as_float(y1[i]), a_ot, v0);
-            v1 = fmaf(__uint_as_float(y1[i + 1]), a_ot, v1);
-          }
-          *reinterpret_cast<uint32_t*>(orow + c * 32 + i) = pack_bf16x2(v0 * inv, v1 * inv);
+      for (int i = 0; i < 32; i += 2) {
+        float v0 = 0.f, v1 = 0.f;
+        if (a_me != 0.f) {
+          v0 = __uint_as_float(y0[i]) * a_me;
+          v1 = __uint_as_float(y0[i + 1]) * a_me;
         }
+        if (a_ot != 0.f) {
+          v0 = fmaf(__uint_as_float(y1[i]), a_ot, v0);
+          v1 = fmaf(__uint_as_float(y1[i + 1]), a_ot, v1);
+        }
+        w[i >> 1] = pack_bf16x2(v0 * inv, v1 * inv);
       }
+      uint4* dst = reinterpret_cast<uint4*>(stage + r * kPitch + (e * kOHalf + c * 32) * 2);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * kTcSoftmaxWarps) : "memory");
+    // coalesced: 16-byte chunks, a row's chunks on neighbouring threads
+    constexpr int kChunks = D * 2 / 16;
+    const int sidx = (int)threadIdx.x - 64;   // 0 .. 255 over the softmax warps
+    __nv_bfloat16* obase = p.out + (long long)b * p.o_sb + (long long)hq * p.o_sh;
+    for (int id = sidx; id < kTcRows * kChunks; id += 32 * kTcSoftmaxWarps) {
+      const int row = id / kChunks, ch = id % kChunks;
+      if (m0 + row < p.T)
+        *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + ch * 8) =
+            *reinterpret_cast<const uint4*>(stage + row * kPitch + ch * 16);
     }
   }
   if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
@@ -375,6 +395,7 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   if (!aligned16(a->q) || a->q_st % 8 || (Hq > 1 && a->q_sh % 8) || (B > 1 && a->q_sb % 8) || a->q_st <= 0 ||
       (Hq > 1 && a->q_sh <= 0) || (B > 1 && a->q_sb <= 0))
     return -1;  // Q cannot be described to the copy engine: the caller falls back to the other kernel
+  if (!aligned16(a->out) || a->o_st % 8 || a->o_sh % 8 || a->o_sb % 8) return -1;  // output rows are written as 16-byte vectors
   CUtensorMap qmap, kmap, vmap;
   if (int st = make_kv_map(&qmap, a->q, D, T, Hq, B, a->q_st, a->q_sh, a->q_sb, kTcRows, 1)) return st;
   if (int st = make_kv_map(&kmap, a->k, D, S, Hkv, B, a->k_st, a->k_sh, a->k_sb, kTcKeys, 1)) return st;
