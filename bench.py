@@ -253,6 +253,13 @@ def run_reference_arm(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
+def launch_kind(args) -> str:
+    """What config.launch says about programmatic dependent launch."""
+    return ("; plain launches (--plain-launch)" if args.plain_launch else
+            "; kernels launched with programmatic stream serialization (each waits with griddepcontrol.wait for "
+            "the previous step's kernel before its first global access)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -272,6 +279,8 @@ def main():
                     "instead of replaying a captured launch")
     ap.add_argument("--seq-len", type=int, default=131072, help="c3: cached tokens (a shard of C3 on one GPU: 131072 / N)")
     ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--plain-launch", action="store_true", help="launch kernels without programmatic dependent launch "
+                    "(l3ci_set_programmatic_launch(0)); for A/B runs")
     ap.add_argument("--nccl-merge", action="store_true", help="c3 on >1 GPU: all_gather + merge kernel instead of the fused exchange")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -298,6 +307,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     pkg = load_package()
+    if args.plain_launch:
+        pkg.capi.load().l3ci_set_programmatic_launch(0)
     ext = pkg.extension()  # no fallback: raises if the CUDA extension is not built
 
     if args.workload == "c5":
@@ -576,8 +587,8 @@ def bench_decode(args, ext, pkg, dev, rank, world, workload, lean=False):
         "scaling": "strong" if workload == "c3" else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "global_batch": B * (1 if sharded_seq else world), "kv_bytes_per_step": int(total_bytes),
                    "l2": f"{n_rot} rotating KV caches per GPU, {rot_bytes / 1e6:.0f} MB > 126 MB L2: each step reads a cold cache",
-                   "launch": f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
-                             else "each step is an eager extension call",
+                   "launch": (f"steps are replayed from a CUDA graph of {n_graph} steps back to back" if use_graph
+                              else "each step is an eager extension call") + launch_kind(args),
                    "parallelism": ("kv-sequence sharded x%d + %s" % (world, "NCCL all_gather + lse merge" if xchg is None else
                                                                   ("exchange over NVLink (peer stores, no collective) and merge in the decode "
                                                                    "kernel's tail: one launch per rank and step" if one_launch else
@@ -916,8 +927,8 @@ def bench_pre_attention(args, ext, pkg, dev, rank, world, workload):
         "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": desc, "l2": f"{n_rot} rotating inputs and outputs > 126 MB L2", "bytes_per_step": nbytes,
-                   "launch": "each step is an eager extension call (with its output allocation)" if args.no_graph else
-                             f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back"},
+                   "launch": ("each step is an eager extension call (with its output allocation)" if args.no_graph else
+                              f"steps are replayed from a CUDA graph of {n_rot} extension calls back to back") + launch_kind(args)},
         "regions": regions,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "kernel": kernel, "algorithmic_bytes_per_launch": nbytes,

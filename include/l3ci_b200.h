@@ -55,6 +55,16 @@ L3CI_API const char* l3ci_version(void);
  * tests use it to let a wait run out in milliseconds.  No counterpart in the reference (one GPU, no waits). */
 L3CI_API uint64_t l3ci_set_device_wait_limit_ns(uint64_t ns);
 
+/* Programmatic dependent launch, on (1, the default) or off (0), for the launches made after this call; returns the
+ * previous setting.  When on, the streaming kernels of this library (decode attention's static-deal kernel, RMSNorm,
+ * SiLU*mul, the rotary kernels, the token-choice steps) are launched so that their grid may be set up on the SMs
+ * while the previous kernel of the stream is still draining; each of them waits (griddepcontrol.wait) for that
+ * kernel's completion and the visibility of its writes before its first global access, so results and stream order
+ * are what they are without it: what overlaps is the launch itself and the start of the CTAs (about a microsecond
+ * per launch between kernels of this library, e.g. RoPE + cache write -> attention in a decode step, also inside a
+ * captured CUDA graph).  No counterpart in the reference (legacy-stream <<<>>> launches). */
+L3CI_API int l3ci_set_programmatic_launch(int on);
+
 /* ------------------------------------------------------------------------------------------
  * RMSNorm.   out[r, :] = bf16( (float(x[r, :]) * rsqrt(mean(x[r, :]^2) + eps)) * float(w) )
  * fp32 arithmetic, one rounding.  Replaces `rms_norm(input, weight, eps)` and

@@ -18,7 +18,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_CUDA, ERR_DEVI
 
 # Every symbol include/l3ci_b200.h declares.
 EXPORTS = (
-    "l3ci_status_string", "l3ci_last_error", "l3ci_version", "l3ci_set_device_wait_limit_ns",
+    "l3ci_status_string", "l3ci_last_error", "l3ci_version", "l3ci_set_device_wait_limit_ns", "l3ci_set_programmatic_launch",
     "l3ci_rms_norm", "l3ci_add_rms_norm", "l3ci_silu_mul", "l3ci_greedy_step", "l3ci_top_p_step", "l3ci_rot_embed", "l3ci_rot_embed_kv_cache", "l3ci_rot_embed_kv_cache_at",
     "l3ci_flash_decode_scratch_bytes", "l3ci_flash_decode", "l3ci_flash_decode_static", "l3ci_flash_decode_poll",
     "l3ci_flash_decode_kernel_choice",
@@ -82,6 +82,8 @@ def load() -> C.CDLL:
     lib.l3ci_last_error.argtypes = []
     lib.l3ci_version.restype = C.c_char_p
     lib.l3ci_version.argtypes = []
+    lib.l3ci_set_programmatic_launch.restype = C.c_int
+    lib.l3ci_set_programmatic_launch.argtypes = [C.c_int]
     lib.l3ci_set_device_wait_limit_ns.restype = C.c_uint64
     lib.l3ci_set_device_wait_limit_ns.argtypes = [C.c_uint64]
     lib.l3ci_rms_norm.restype = C.c_int
@@ -394,6 +396,23 @@ class device_wait_limit:
 
     def __exit__(self, *exc):
         load().l3ci_set_device_wait_limit_ns(self.prev)
+        return False
+
+
+class programmatic_launch:
+    """Context manager: launches made inside use (True) or do not use (False) programmatic dependent launch
+    (l3ci_set_programmatic_launch); the previous setting comes back on exit.  A CUDA graph keeps the kind of launch
+    it was captured with."""
+
+    def __init__(self, on: bool):
+        self.on = bool(on)
+
+    def __enter__(self):
+        self.prev = load().l3ci_set_programmatic_launch(int(self.on))
+        return self
+
+    def __exit__(self, *exc):
+        load().l3ci_set_programmatic_launch(self.prev)
         return False
 
 

@@ -198,7 +198,7 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t cta) {
 }
 
 // kCluster: launched as clusters of CTAs per unit (the instances without hold no cluster instruction and are
-// launched the plain way, which starts sooner).  kWholeCta: all eight warps on one unit, known at compile time
+// launched without the cluster attribute, which starts sooner).  kWholeCta: all eight warps on one unit, known at compile time
 // (the merge loops then unroll without predicates: 0.5 us on a call of a few microseconds).
 // kWide: 12 warps x 2 tiles in flight instead of 8 x 3 (cluster instances on long runs of tiles).
 // kExchange: the results of this launch are one GPU's shard of a sequence-sharded cache; the exchange with the
@@ -228,6 +228,8 @@ flash_decode_small_kernel(const SmallParams p) {
   uint32_t cta_rank = 0;
   if constexpr (kCluster) cta_rank = cluster_cta_rank();
   const int n_units = p.B * p.Hkv;
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const int unit0 = (int)(blockIdx.x >> lgC) * U;   // first unit of this CTA (of this cluster)
   const int unit = unit0 + (kWholeCta ? 0 : warp >> lgW);
   const bool has_unit = unit < n_units;
@@ -614,11 +616,10 @@ int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq) {
 
 template <int D, bool kExchange>
 int launch_instance(const SmallParams& p, const UnitSplit& s, bool wide, size_t smem, cudaStream_t stream) {
-  if (s.C == 1) {  // (the instances without cluster instructions, launched the plain way)
-    const unsigned grid = (unsigned)s.ctas, block = 32 * kSmWarps;
-    if (s.W == kSmWarps) flash_decode_small_kernel<D, false, true, false, kExchange><<<grid, block, smem, stream>>>(p);
-    else flash_decode_small_kernel<D, false, false, false, kExchange><<<grid, block, smem, stream>>>(p);
-    L3CI_CHECK_LAUNCH("flash_decode_small_kernel");
+  if (s.C == 1) {  // (the instances without cluster instructions)
+    const dim3 grid((unsigned)s.ctas), block(32 * kSmWarps);
+    if (s.W == kSmWarps) L3CI_LAUNCH("flash_decode_small_kernel", flash_decode_small_kernel<D, false, true, false, kExchange>, grid, block, smem, stream, p);
+    else L3CI_LAUNCH("flash_decode_small_kernel", flash_decode_small_kernel<D, false, false, false, kExchange>, grid, block, smem, stream, p);
     return L3CI_OK;
   }
   cudaLaunchConfig_t cfg = {};
@@ -626,13 +627,15 @@ int launch_instance(const SmallParams& p, const UnitSplit& s, bool wide, size_t 
   cfg.blockDim = dim3(32 * (wide ? kClWarps : kSmWarps));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)s.C;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = programmatic_launch_enabled() ? 2 : 1;
   const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, true, kExchange>, p)
                              : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, false, kExchange>, p);
   if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));

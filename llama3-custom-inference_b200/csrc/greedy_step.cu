@@ -14,6 +14,7 @@
 
 #include "bf16x8.cuh"
 #include "host_common.h"
+#include "ptx_sm100.cuh"
 #include "warp_reduce.cuh"
 
 namespace l3ci {
@@ -48,6 +49,8 @@ greedy_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lo
                    int* __restrict__ seq_lens) {
   __shared__ float s_val[kGreedyBlock / kWarp];
   __shared__ long long s_idx[kGreedyBlock / kWarp];
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const long long b = blockIdx.x;
   const __nv_bfloat16* row = logits + b * row_stride;
   float best = -INFINITY;
@@ -133,9 +136,8 @@ extern "C" int l3ci_greedy_step(const void* logits, int64_t rows, int64_t vocab,
   if (!logits || (!out_tokens && !next_input)) return fail(L3CI_ERR_INVALID, "greedy_step: null logits or no output");
   if (rows > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "greedy_step: too many rows");
   if (steps && (!out_tokens || out_cols <= 0)) return fail(L3CI_ERR_INVALID, "greedy_step: steps needs out_tokens and its width");
-  greedy_step_kernel<<<(unsigned)rows, kGreedyBlock, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const __nv_bfloat16*>(logits), vocab, row_stride, reinterpret_cast<long long*>(out_tokens), out_stride,
-      out_cols, reinterpret_cast<long long*>(steps), reinterpret_cast<long long*>(next_input), positions, seq_lens);
-  L3CI_CHECK_LAUNCH("greedy_step_kernel");
+  L3CI_LAUNCH("greedy_step_kernel", greedy_step_kernel, dim3((unsigned)rows), dim3(kGreedyBlock), 0, reinterpret_cast<cudaStream_t>(stream_),
+              static_cast<const __nv_bfloat16*>(logits), vocab, row_stride, reinterpret_cast<long long*>(out_tokens), out_stride,
+              out_cols, reinterpret_cast<long long*>(steps), reinterpret_cast<long long*>(next_input), positions, seq_lens);
   return L3CI_OK;
 }

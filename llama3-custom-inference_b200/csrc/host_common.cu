@@ -13,7 +13,10 @@ constexpr int kMaxDev = 64;
 int g_sms[kMaxDev] = {0};
 int g_smem[kMaxDev] = {0};
 std::atomic<unsigned long long> g_wait_limit_ns{0};  // 0: every kernel's own default
+std::atomic<int> g_programmatic_launch{1};
 }  // namespace
+
+bool programmatic_launch_enabled() { return g_programmatic_launch.load(std::memory_order_relaxed) != 0; }
 
 unsigned long long device_wait_limit_ns(unsigned long long default_ns) {
   const unsigned long long v = g_wait_limit_ns.load(std::memory_order_relaxed);
@@ -76,6 +79,8 @@ const char* l3ci_status_string(int status) {
 const char* l3ci_last_error(void) { return l3ci::g_err; }
 
 const char* l3ci_version(void) { return "0.2.0"; }
+
+int l3ci_set_programmatic_launch(int on) { return l3ci::g_programmatic_launch.exchange(on ? 1 : 0, std::memory_order_relaxed); }
 
 uint64_t l3ci_set_device_wait_limit_ns(uint64_t ns) {
   return l3ci::g_wait_limit_ns.exchange(ns, std::memory_order_relaxed);

@@ -39,6 +39,10 @@ int flash_decode_small_split_code(int B, int Hkv, int D, int n_seq);
 // l3ci_set_device_wait_limit_ns, else `default_ns`.
 unsigned long long device_wait_limit_ns(unsigned long long default_ns);
 
+// Programmatic dependent launch (l3ci_set_programmatic_launch): whether kernels are launched so that their grid may
+// be set up while the previous kernel of the stream is still draining.
+bool programmatic_launch_enabled();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 #define L3CI_CUDA_TRY(expr)                                                              \
@@ -56,5 +60,33 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
       return ::l3ci::fail(L3CI_ERR_CUDA, "launch of %s failed: %s", name,                  \
                           cudaGetErrorString(e_));                                         \
   } while (0)
+
+#if defined(__CUDACC__)
+// Launch of `kernel`, as <<<grid, block, smem, stream>>> would do it, or, when programmatic dependent launch is on,
+// with the attribute that lets the grid be scheduled before the previous kernel of the stream has finished.  Kernels
+// launched this way call pdl_wait() (ptx_sm100.cuh) before they touch global memory: it returns once the previous
+// kernel has completed and its writes are visible, so the overlap is the launch itself, the CTAs' start and whatever
+// a kernel does before its first global access; a kernel launched the plain way passes through it at once.
+template <typename... Params, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+#define L3CI_LAUNCH(name, ...)                                                                     \
+  do {                                                                                             \
+    cudaError_t e_ = ::l3ci::launch_kernel(__VA_ARGS__);                                           \
+    if (e_ != cudaSuccess)                                                                         \
+      return ::l3ci::fail(L3CI_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+#endif
 
 }  // namespace l3ci

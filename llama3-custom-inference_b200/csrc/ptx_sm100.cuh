@@ -59,6 +59,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   }
   return true;
 }
+// Programmatic dependent launch.  pdl_wait: blocks until the kernel this one was launched behind has completed and
+// its memory operations are visible (at once when the kernel was launched the plain way); everything before it may
+// run while that kernel is still draining.  pdl_launch_dependents: lets the NEXT kernel of the stream be set up on the
+// SMs as they come free (it stops at its own pdl_wait until this grid has completed).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));

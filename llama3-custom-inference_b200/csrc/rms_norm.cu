@@ -14,6 +14,7 @@
 
 #include "bf16x8.cuh"
 #include "host_common.h"
+#include "ptx_sm100.cuh"
 #include "warp_reduce.cuh"
 
 namespace l3ci {
@@ -36,6 +37,8 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 __nv_bfloat16* __restrict__ sum_out) {
   constexpr int kRows = RmsCfg<TPR>::kRowsPerCta;
   __shared__ float red[32];
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const int t = threadIdx.x % TPR;
   const long long row = (long long)blockIdx.x * kRows + threadIdx.x / TPR;
   const bool row_ok = row < rows;
@@ -148,6 +151,8 @@ __global__ void __launch_bounds__(kRowsBlock, (VPL >= 8 && kRes) ? 1 : 2)
 rms_norm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                      __nv_bfloat16* __restrict__ out, long long rows, int nvec, long long x_stride, long long out_stride,
                      float embed_f, float eps, const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ sum_out) {
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const int lane = threadIdx.x & 31;
   const long long warps = (long long)gridDim.x * (kRowsBlock / 32);
   long long row = (long long)blockIdx.x * (kRowsBlock / 32) + (threadIdx.x >> 5);
@@ -243,9 +248,8 @@ int launch_rows(const void* x, const void* w, void* out, long long rows, int nve
   const unsigned grid = (unsigned)(want < per_sm * sms ? want : per_sm * sms);
   const auto xb = static_cast<const __nv_bfloat16*>(x), wb = static_cast<const __nv_bfloat16*>(w), rb = static_cast<const __nv_bfloat16*>(res);
   const auto ob = static_cast<__nv_bfloat16*>(out), sb = static_cast<__nv_bfloat16*>(sum_out);
-  if (res) rms_norm_rows_kernel<VPL, true><<<grid, kRowsBlock, 0, stream>>>(xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
-  else rms_norm_rows_kernel<VPL, false><<<grid, kRowsBlock, 0, stream>>>(xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
-  L3CI_CHECK_LAUNCH("rms_norm_rows_kernel");
+  if (res) L3CI_LAUNCH("rms_norm_rows_kernel", rms_norm_rows_kernel<VPL, true>, dim3(grid), dim3(kRowsBlock), 0, stream, xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
+  else L3CI_LAUNCH("rms_norm_rows_kernel", rms_norm_rows_kernel<VPL, false>, dim3(grid), dim3(kRowsBlock), 0, stream, xb, wb, ob, rows, nvec, xs, os, (float)(nvec * kVecElems), eps, rb, sb);
   return L3CI_OK;
 }
 
@@ -255,11 +259,10 @@ int launch(const void* x, const void* w, void* out, long long rows, int nvec, lo
   constexpr int kRows = RmsCfg<TPR>::kRowsPerCta;
   const long long ctas = (rows + kRows - 1) / kRows;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rms_norm: too many rows (%lld)", rows);
-  rms_norm_kernel<TPR, VPT><<<(unsigned)ctas, RmsCfg<TPR>::kBlock, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      static_cast<__nv_bfloat16*>(out), rows, nvec, xs, os, (float)(nvec * kVecElems), eps,
-      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(sum_out));
-  L3CI_CHECK_LAUNCH("rms_norm_kernel");
+  L3CI_LAUNCH("rms_norm_kernel", rms_norm_kernel<TPR, VPT>, dim3((unsigned)ctas), dim3(RmsCfg<TPR>::kBlock), 0, stream,
+              static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+              static_cast<__nv_bfloat16*>(out), rows, nvec, xs, os, (float)(nvec * kVecElems), eps,
+              static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(sum_out));
   return L3CI_OK;
 }
 
@@ -314,6 +317,8 @@ __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                 __nv_bfloat16* __restrict__ out, long long nvec, int row_vecs, long long gate_stride,
                 long long up_stride) {
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= nvec) return;
   const long long r = i / row_vecs, c = (i % row_vecs) * kVecElems;
@@ -362,9 +367,8 @@ extern "C" int l3ci_silu_mul(const void* gate, const void* up, void* out, int64_
   const long long nvec = rows * (cols / kVecElems);
   const long long ctas = (nvec + 255) / 256;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "silu_mul: tensor too large");
-  silu_mul_kernel<<<(unsigned)ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), nvec,
-      (int)(cols / kVecElems), gate_row_stride, up_row_stride);
-  L3CI_CHECK_LAUNCH("silu_mul_kernel");
+  L3CI_LAUNCH("silu_mul_kernel", silu_mul_kernel, dim3((unsigned)ctas), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream_),
+              static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), nvec,
+              (int)(cols / kVecElems), gate_row_stride, up_row_stride);
   return L3CI_OK;
 }

@@ -16,6 +16,7 @@
 
 #include "bf16x8.cuh"
 #include "host_common.h"
+#include "ptx_sm100.cuh"
 
 namespace l3ci {
 namespace {
@@ -58,6 +59,8 @@ __global__ void __launch_bounds__(kTokenBlock)
 rot_embed_vec8_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ freq,
                       __nv_bfloat16* __restrict__ out, int S, int H, int vec_per_head_rt, long long sb, long long ss,
                       long long sh) {
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const int vec_per_head = VPH ? VPH : vec_per_head_rt;
   const long long token = blockIdx.x;
   const int s = (int)(token % S);
@@ -123,6 +126,8 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
                           long long qkv_sb, long long qkv_st, long long cache_sb, long long cache_st,
                           long long start_pos, const int* __restrict__ positions, long long freq_rows,
                           long long cache_len) {
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const int vec_per_head = VPH ? VPH : vec_per_head_rt;
   const long long token = blockIdx.x;
   const int t = (int)(token % T);
@@ -176,10 +181,10 @@ rot_embed_kv_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __
 
 // Launch of the instance for this head size (8 or 16 vectors per head: shifts and shared table loads; else generic).
 template <typename... Args>
-void launch_kv_cache(int vec_per_head, unsigned grid, cudaStream_t stream, Args... args) {
-  if (vec_per_head == 8) rot_embed_kv_cache_kernel<8><<<grid, kTokenBlock, 0, stream>>>(args...);
-  else if (vec_per_head == 16) rot_embed_kv_cache_kernel<16><<<grid, kTokenBlock, 0, stream>>>(args...);
-  else rot_embed_kv_cache_kernel<0><<<grid, kTokenBlock, 0, stream>>>(args...);
+cudaError_t launch_kv_cache(int vec_per_head, unsigned grid, cudaStream_t stream, Args... args) {
+  if (vec_per_head == 8) return launch_kernel(rot_embed_kv_cache_kernel<8>, dim3(grid), dim3(kTokenBlock), 0, stream, args...);
+  if (vec_per_head == 16) return launch_kernel(rot_embed_kv_cache_kernel<16>, dim3(grid), dim3(kTokenBlock), 0, stream, args...);
+  return launch_kernel(rot_embed_kv_cache_kernel<0>, dim3(grid), dim3(kTokenBlock), 0, stream, args...);
 }
 
 int grid_for(long long total, unsigned* grid) {
@@ -212,10 +217,9 @@ extern "C" int l3ci_rot_embed(const void* x, const float* freq, void* out, int64
     if (B * S > 0x7fffffffLL || H * (D / kVecElems) > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "rot_embed: tensor too large");
     grid = (unsigned)(B * S);
     const int vph = (int)(D / kVecElems);
-    if (vph == 8) rot_embed_vec8_kernel<8><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
-    else if (vph == 16) rot_embed_vec8_kernel<16><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
-    else rot_embed_vec8_kernel<0><<<grid, kTokenBlock, 0, stream>>>(xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
-    L3CI_CHECK_LAUNCH("rot_embed_vec8_kernel");
+    if (vph == 8) L3CI_LAUNCH("rot_embed_vec8_kernel", rot_embed_vec8_kernel<8>, dim3(grid), dim3(kTokenBlock), 0, stream, xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
+    else if (vph == 16) L3CI_LAUNCH("rot_embed_vec8_kernel", rot_embed_vec8_kernel<16>, dim3(grid), dim3(kTokenBlock), 0, stream, xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
+    else L3CI_LAUNCH("rot_embed_vec8_kernel", rot_embed_vec8_kernel<0>, dim3(grid), dim3(kTokenBlock), 0, stream, xp, freq, op, (int)S, (int)H, vph, sb, ss, sh);
     return L3CI_OK;
   }
   if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(out) & 3) ||
@@ -248,12 +252,12 @@ extern "C" int l3ci_rot_embed_kv_cache(const void* qkv, const float* freq, void*
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache: rows must start on 16 bytes");
   if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
     return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache: tensor too large");
-  launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
+  const cudaError_t le = launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
       static_cast<const __nv_bfloat16*>(qkv), freq, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T,
       (int)Hq, (int)Hkv, (int)(D / kVecElems), (long long)qkv_sb, (long long)qkv_st, (long long)cache_sb, (long long)cache_st,
       (long long)start_pos, (const int*)nullptr, 0LL, 0LL);
-  L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
+  if (le != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of rot_embed_kv_cache_kernel failed: %s", cudaGetErrorString(le));
   return L3CI_OK;
 }
 
@@ -277,11 +281,11 @@ extern "C" int l3ci_rot_embed_kv_cache_at(const void* qkv, const float* freq_tab
     return fail(L3CI_ERR_ALIGNMENT, "rot_embed_kv_cache_at: rows must start on 16 bytes");
   if (B * T > 0x7fffffffLL || (Hq + 2 * Hkv) * (D / kVecElems) > 0x7fffffffLL)
     return fail(L3CI_ERR_INVALID, "rot_embed_kv_cache_at: tensor too large");
-  launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
+  const cudaError_t le = launch_kv_cache((int)(D / kVecElems), (unsigned)(B * T), stream,
       static_cast<const __nv_bfloat16*>(qkv), freq_table, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(cache_k), static_cast<__nv_bfloat16*>(cache_v), (int)T, (int)Hq, (int)Hkv,
       (int)(D / kVecElems), (long long)qkv_sb, (long long)qkv_st, (long long)cache_sb, (long long)cache_st, 0LL,
       (const int*)positions, (long long)freq_rows, (long long)cache_len);
-  L3CI_CHECK_LAUNCH("rot_embed_kv_cache_kernel");
+  if (le != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of rot_embed_kv_cache_kernel failed: %s", cudaGetErrorString(le));
   return L3CI_OK;
 }

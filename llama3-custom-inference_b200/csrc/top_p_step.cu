@@ -177,6 +177,8 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   __shared__ u64 s_above;
   __shared__ int s_owner;
   __shared__ long long s_token;
+  pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
+  pdl_launch_dependents();  // the next one may be set up while this one runs
   const long long b = blockIdx.x;
   RowView rv;
   rv.row = logits + b * row_stride;
@@ -324,10 +326,9 @@ extern "C" int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, 
   if (!logits || (!out_tokens && !next_input)) return fail(L3CI_ERR_INVALID, "top_p_step: null logits or no output");
   if (rows > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "top_p_step: too many rows");
   if (steps && (!out_tokens || out_cols <= 0)) return fail(L3CI_ERR_INVALID, "top_p_step: steps needs out_tokens and its width");
-  top_p_step_kernel<<<(unsigned)rows, kTopPBlock, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
-      static_cast<const __nv_bfloat16*>(logits), vocab, row_stride, 1.0f / temperature, top_p, seed,
-      reinterpret_cast<long long*>(out_tokens), out_stride, out_cols, reinterpret_cast<long long*>(steps),
-      reinterpret_cast<long long*>(next_input), positions, seq_lens, nucleus_count, nucleus_mass);
-  L3CI_CHECK_LAUNCH("top_p_step_kernel");
+  L3CI_LAUNCH("top_p_step_kernel", top_p_step_kernel, dim3((unsigned)rows), dim3(kTopPBlock), 0, reinterpret_cast<cudaStream_t>(stream_),
+              static_cast<const __nv_bfloat16*>(logits), vocab, row_stride, 1.0f / temperature, top_p, (unsigned long long)seed,
+              reinterpret_cast<long long*>(out_tokens), out_stride, out_cols, reinterpret_cast<long long*>(steps),
+              reinterpret_cast<long long*>(next_input), positions, seq_lens, nucleus_count, nucleus_mass);
   return L3CI_OK;
 }
