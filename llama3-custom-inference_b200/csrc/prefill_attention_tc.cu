@@ -61,22 +61,25 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void tc_commit(uint32_t bar, uint32_t elected) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(bar), "r"(elected) : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                       uint32_t elected) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(elected) : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                       uint32_t elected) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(elected) : "memory");
 }
 // 32 consecutive 32-bit columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -101,6 +104,37 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+// fp32 arithmetic two lanes at a time and a three-input maximum: the softmax warps' own instructions, not the
+// special-function unit, were what a score tile cost, so every instruction saved per element counts.
+__device__ __forceinline__ unsigned long long f2_pack(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f2_packf(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, rows (or 8-row groups) 1024 bytes apart: address and byte
@@ -196,19 +230,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     // ---- MMA issue (lane 0), the whole warp takes the waits ----
     constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
     constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
-    auto issue_s = [&](int j) {  // S_j = Q K_j^T; its accumulator held P_{j-2}, read by an MMA issued before this one
+    const uint32_t elected = lane == 0 ? 1u : 0u;
+    const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
+    const uint64_t k_desc = smem_desc(k_smem, 16, 1024);
+    const uint64_t v_desc = smem_desc(v_smem, kBoxBytes, 1024);
+    auto issue_s = [&](int j) {
       const int s = j % kTcStages;
-      if (lane == 0) {
+      const uint64_t kd = k_desc + (uint64_t)((s * kTileBytes) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t a = smem_desc(q_smem + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc(k_smem + s * kTileBytes + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
-          mma_ss(t_s[j & 1], a, bd, idesc_qk, ks > 0);
-        }
-        tc_commit(bar(S_FULL + (j & 1)));
-        tc_commit(bar(K_EMPTY + s));
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint64_t step = (uint64_t)(((ks >> 2) * kBoxBytes + (ks & 3) * 32) / 16);
+        mma_ss(t_s[j & 1], q_desc + step, kd + step, idesc_qk, ks > 0, elected);
       }
-      __syncwarp();
+      tc_commit(bar(S_FULL + (j & 1)), elected);
+      tc_commit(bar(K_EMPTY + s), elected);
     };
     if (!mbar_wait_bounded(bar(Q_FULL), 0)) ok = false;
     if (ok && !mbar_wait_bounded(bar(K_FULL), 0)) ok = false;
@@ -228,17 +263,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       if (!mbar_wait_bounded(bar(P_FULL + (j & 1)), (j >> 1) & 1)) { ok = false; break; }
       if (!mbar_wait_bounded(bar(V_FULL + s), (j / kTcStages) & 1)) { ok = false; break; }
       tc_fence_after();
-      if (lane == 0) {
+      {
+        const uint64_t vd = v_desc + (uint64_t)((s * kTileBytes) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kTcKeys / 16; ++kk) {
-          // V tile: [keys][64 columns] boxes; 16 keys = 2048 bytes further; second 64-column half one box further
-          const uint64_t bd = smem_desc(v_smem + s * kTileBytes + kk * 2048, kBoxBytes, 1024);
-          mma_ts(t_o[j & 1], t_s[j & 1] + kk * 8, bd, idesc_pv, (j > 1 || kk > 0) ? 1u : 0u);
-        }
-        tc_commit(bar(O_FULL + (j & 1)));
-        tc_commit(bar(V_EMPTY + s));
+        for (int kk = 0; kk < kTcKeys / 16; ++kk)
+          mma_ts(t_o[j & 1], t_s[j & 1] + kk * 8, vd + (uint64_t)(kk * 128), idesc_pv, (j > 1 || kk > 0) ? 1u : 0u, elected);
+        tc_commit(bar(O_FULL + (j & 1)), elected);
+        tc_commit(bar(V_EMPTY + s), elected);
       }
-      __syncwarp();
     }
   } else {
     // ---- softmax and output: group e = tiles j % 2 == e; thread owns query row r of its group's tiles ----
@@ -262,16 +294,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
       for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, x[c]);
       tc_wait_ld();
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (edge) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (edge) {
+          for (int i = 0; i < 32; ++i) {
             const int key = j0 + c * 32 + i;
             if (key > limit || key >= p.n_keys) x[c][i] = 0xff800000u;  // -inf
           }
-          mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(x[c][i]));
-        }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(x[c][i]), __uint_as_float(x[c][i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
       // Move the reference maximum (and rescale this warp's rows of O_e) only when some row needs it.
       if (__any_sync(kFullMask, mx > m_ref + kLazy)) {
@@ -300,20 +336,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         m_ref = m_new;
       }
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      const unsigned long long scale2 = f2_packf(p.scale_log2e, p.scale_log2e), nmu2 = f2_packf(-mu, -mu);
+      unsigned long long ps2[4] = {0ull, 0ull, 0ull, 0ull};   // four fp32 pairs of partial row sums
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(x[c][2 * i]), p.scale_log2e, -mu));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(x[c][2 * i + 1]), p.scale_log2e, -mu));
-          ps4[i & 3] += p0 + p1;
+          float t0, t1;
+          f2_unpack(f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2), t0, t1);
+          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(p0, p1));
           pk[i] = pack_bf16x2(p0, p1);
         }
         tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
       }
-      l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(f2_add(ps2[0], ps2[1]), a0, a1);
+        f2_unpack(f2_add(ps2[2], ps2[3]), b0, b1);
+        l_run += (a0 + a1) + (b0 + b1);
+      }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
