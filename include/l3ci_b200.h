@@ -274,8 +274,8 @@ typedef struct l3ci_prefill_args {
   int32_t T, n_keys, start_pos;
   int64_t q_sb, q_sh, q_st, k_sb, k_sh, k_st, v_sb, v_sh, v_st, o_sb, o_sh, o_st;
   float scale;            /* <= 0: 1/sqrt(D)                                                           */
-  int32_t variant;        /* 0: choose (tcgen05 kernel at D = 128 from 128 query rows on); 1: the tcgen05 /
-                             tensor-memory kernel; 2: the mma.sync kernel                              */
+  int32_t variant;        /* 0: choose (tcgen05 kernel from 128 query rows on, where q and out rows are 16-byte
+                             aligned); 1: the tcgen05 / tensor-memory kernel; 2: the mma.sync kernel   */
   l3ci_stream_t stream;
 } l3ci_prefill_args;
 

@@ -430,6 +430,275 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+// The same, with TWO query heads of one KV head per CTA (Hq / Hkv even): softmax group e owns head hq0 + e with all
+// its key tiles -- its own Q tile, score accumulator S_e, output accumulator O_e -- and the K and V tiles are loaded once
+// for both, which halves the traffic from L2 into shared memory (1.2 GB a launch at B=4, T=2048 with one head per
+// CTA: 5.7 TB/s, enough to make the MMA warp wait for K), halves the number of CTAs and with it the share of their
+// start and end in the launch, and needs no merge of two partial results at the end.
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap, const TcParams p) {
+  constexpr int kHalves = D / 64;
+  constexpr int kBoxBytes = 128 * 128;             // 128 rows of 128 bytes
+  constexpr int kTileBytes = kHalves * kBoxBytes;  // a Q, K or V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_smem = smem_u32(smem);
+  const uint32_t k_smem = q_smem + 2 * kTileBytes;             // [kTcStages], behind the two Q tiles
+  const uint32_t v_smem = k_smem + kTcStages * kTileBytes;     // [kTcStages]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * kTcStages) * kTileBytes);
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, N_BARS = 15 };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps / 2 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&vmap)) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s[2] = {tmem, tmem + 128u};
+  const uint32_t t_o[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
+
+  const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
+  const int pairs = p.Hq >> 1;
+  const int hq0 = 2 * (int)((blockIdx.x / p.m_blocks) % pairs);   // the CTA's query heads: hq0, hq0 + 1 (R is even)
+  const int b = (int)(blockIdx.x / ((long long)p.m_blocks * pairs));
+  const int hkv = hq0 / p.R;
+  const int m0 = mb * kTcRows;
+  const int last_row = min(m0 + kTcRows, p.T) - 1;
+  const int keys = min(p.n_keys, p.start_pos + last_row + 1);
+  const int n_tiles = (keys + kTcKeys - 1) / kTcKeys;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ---- producer ----
+    const uint64_t policy = l2_evict_first_policy();
+    if (lane == 0) {
+      mbar_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_4d(q_smem + e * kTileBytes + h * kBoxBytes, &qmap, bar(Q_FULL), h * 64, m0, hq0 + e, b, policy);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kTcStages;
+      const uint32_t par = ((j / kTcStages) - 1) & 1;
+      if (j >= kTcStages && !mbar_wait_bounded(bar(K_EMPTY + s), par)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(bar(K_FULL + s), kTileBytes);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_4d(k_smem + s * kTileBytes + h * kBoxBytes, &kmap, bar(K_FULL + s), h * 64, j * kTcKeys, hkv, b, policy);
+      }
+      if (j >= kTcStages && !mbar_wait_bounded(bar(V_EMPTY + s), par)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(bar(V_FULL + s), kTileBytes);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          tma_load_4d(v_smem + s * kTileBytes + h * kBoxBytes, &vmap, bar(V_FULL + s), h * 64, j * kTcKeys, hkv, b, policy);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (lane 0), the whole warp takes the waits ----
+    constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
+    constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
+    const uint32_t elected = lane == 0 ? 1u : 0u;
+    const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
+    const uint64_t k_desc = smem_desc(k_smem, 16, 1024);
+    const uint64_t v_desc = smem_desc(v_smem, kBoxBytes, 1024);
+    // S_{e,j} = Q_e K_j^T into group e's score accumulator, which held P_{e,j-1}, read by an MMA issued before this one
+    auto issue_s = [&](int e, int j) {
+      const int s = j % kTcStages;
+      const uint64_t qd = q_desc + (uint64_t)((e * kTileBytes) >> 4);
+      const uint64_t kd = k_desc + (uint64_t)((s * kTileBytes) >> 4);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint64_t step = (uint64_t)(((ks >> 2) * kBoxBytes + (ks & 3) * 32) / 16);
+        mma_ss(t_s[e], qd + step, kd + step, idesc_qk, ks > 0, elected);
+      }
+      tc_commit(bar(S_FULL + e), elected);
+      if (e == 1) tc_commit(bar(K_EMPTY + s), elected);   // both heads have read the K stage
+    };
+    if (!mbar_wait_bounded(bar(Q_FULL), 0)) ok = false;
+    if (ok && !mbar_wait_bounded(bar(K_FULL), 0)) ok = false;
+    if (ok) {
+      tc_fence_after();
+      issue_s(0, 0);
+      issue_s(1, 0);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % kTcStages;
+      if (!mbar_wait_bounded(bar(V_FULL + s), (j / kTcStages) & 1)) { ok = false; break; }
+      for (int e = 0; e < 2; ++e) {
+        // O_e += P_{e,j} V_j once P_{e,j} is in TMEM (any rescaling of O_e happened before that), then at once the
+        // head's next scores, which go where P_{e,j} lay
+        if (!mbar_wait_bounded(bar(P_FULL + e), j & 1)) { ok = false; break; }
+        tc_fence_after();
+        {
+          const uint64_t vd = v_desc + (uint64_t)((s * kTileBytes) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < kTcKeys / 16; ++kk)
+            mma_ts(t_o[e], t_s[e] + kk * 8, vd + (uint64_t)(kk * 128), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u, elected);
+          tc_commit(bar(O_FULL + e), elected);
+          if (e == 1) tc_commit(bar(V_EMPTY + s), elected);
+        }
+        if (j + 1 < n_tiles) {
+          if (e == 0) {
+            if (!mbar_wait_bounded(bar(K_FULL + (j + 1) % kTcStages), ((j + 1) / kTcStages) & 1)) { ok = false; break; }
+            tc_fence_after();
+          }
+          issue_s(e, j + 1);
+        }
+      }
+    }
+  } else {
+    // ---- softmax and output: group e = query head hq0 + e, all key tiles; thread owns query row r ----
+    const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int e = (warp - 2) >> 2;                 // warps 2-5: head hq0, warps 6-9: head hq0 + 1
+    const int r = q4 * 32 + lane;
+    const int t = m0 + r;                          // query index
+    const int limit = p.start_pos + t;             // last key this row may see
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    const uint32_t ts = t_s[e] + lane_addr, to = t_o[e] + lane_addr;
+    constexpr float kLazy = 8.f;                   // log2 of how far the running maximum may outgrow m_ref
+    float m_ref = -INFINITY, l_run = 0.f;
+    int done = 0;                                  // tiles of this group so far
+    for (int j = 0; j < n_tiles && ok; ++j, ++done) {
+      if (!mbar_wait_bounded(bar(S_FULL + e), done & 1)) { ok = false; break; }
+      tc_fence_after();
+      const int j0 = j * kTcKeys;
+      const bool edge = j0 + kTcKeys - 1 > p.start_pos + m0 || j0 + kTcKeys > p.n_keys;  // some row of the block is cut
+      uint32_t x[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, x[c]);
+      tc_wait_ld();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = j0 + c * 32 + i;
+            if (key > limit || key >= p.n_keys) x[c][i] = 0xff800000u;  // -inf
+          }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(x[c][i]), __uint_as_float(x[c][i + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+      // Move the reference maximum (and rescale this warp's rows of O_e) only when some row needs it.
+      if (__any_sync(kFullMask, mx > m_ref + kLazy)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        if (done > 0) {
+          // O_e holds the products of this group's earlier tiles once their MMA has completed
+          if (!mbar_wait_bounded(bar(O_FULL + e), (done - 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t y[32];
+            tmem_ld32(to + c * 32, y);
+            tc_wait_ld();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(y[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(y[16 + i]) * alpha);
+            }
+            tmem_st16(to + c * 32, lo);
+            tmem_st16(to + c * 32 + 16, hi);
+          }
+          l_run *= alpha;
+        }
+        m_ref = m_new;
+      }
+      const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+      const unsigned long long scale2 = f2_packf(p.scale_log2e, p.scale_log2e), nmu2 = f2_packf(-mu, -mu);
+      unsigned long long ps2[4] = {0ull, 0ull, 0ull, 0ull};   // four fp32 pairs of partial row sums
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float t0, t1;
+          f2_unpack(f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2), t0, t1);
+          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(p0, p1));
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
+      }
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(f2_add(ps2[0], ps2[1]), a0, a1);
+        f2_unpack(f2_add(ps2[2], ps2[3]), b0, b1);
+        l_run += (a0 + a1) + (b0 + b1);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + e));
+    }
+    // this head's last product
+    if (ok && done > 0 && !mbar_wait_bounded(bar(O_FULL + e), (done - 1) & 1)) ok = false;
+    tc_fence_after();
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    // Both heads' MMAs have completed once both groups are here: the K and V stages are free and take the output
+    // rows, which leave as 16-byte vectors (a thread holds one row; stored straight to global memory every store
+    // instruction of a warp would touch 32 rows).  Rows are 16 bytes further apart than their length, so that the
+    // 16-byte stores of eight neighbouring rows fall into eight different bank groups.
+    asm volatile("bar.sync 1, %0;" ::"r"(32 * kTcSoftmaxWarps) : "memory");
+    constexpr int kPitch = D * 2 + 16;
+    uint8_t* stage = smem + 2 * kTileBytes + e * (kTcRows * kPitch);
+    static_assert(2 * kTcRows * kPitch <= 2 * kTcStages * kTileBytes, "output staging fits the K and V stages");
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t y[32];
+      tmem_ld32(to + c * 32, y);
+      tc_wait_ld();
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) w[i >> 1] = pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
+      uint4* dst = reinterpret_cast<uint4*>(stage + r * kPitch + c * 64);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(2 + e), "r"(32 * kTcSoftmaxWarps / 2) : "memory");   // this group's 128 threads
+    // coalesced: 16-byte chunks, a row's chunks on neighbouring threads
+    constexpr int kChunks = D * 2 / 16;
+    __nv_bfloat16* obase = p.out + (long long)b * p.o_sb + (long long)(hq0 + e) * p.o_sh;
+    for (int id = r; id < kTcRows * kChunks; id += 32 * kTcSoftmaxWarps / 2) {
+      const int row = id / kChunks, ch = id % kChunks;
+      if (m0 + row < p.T)
+        *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + ch * 8) =
+            *reinterpret_cast<const uint4*>(stage + row * kPitch + ch * 16);
+    }
+  }
+  if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+  // Every thread comes here (all waits are bounded); then nothing of this CTA uses TMEM any more.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
 }  // namespace
 
 // Launch for prompts of at least one full block; called by l3ci_prefill_attention.
@@ -451,20 +720,26 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf((float)D);
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = a->status;
-  const long long ctas = (long long)B * Hq * p.m_blocks;
+  const bool pair = (Hq / Hkv) % 2 == 0;   // two query heads of a KV head per CTA
+  const long long ctas = (long long)B * (pair ? Hq / 2 : Hq) * p.m_blocks;
   if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", ctas);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
-  const size_t smem = 1024 + (size_t)(1 + 2 * kTcStages) * (D / 64) * 128 * 128 + 15 * 8 + 4 * kTcRows * 4 + 16;
-  static bool configured[2][64] = {{false}};
+  const size_t tile = (size_t)(D / 64) * 128 * 128;
+  const size_t smem = 1024 + ((pair ? 2 : 1) + 2 * kTcStages) * tile + 15 * 8 + 4 * kTcRows * 4 + 16;
+  static bool configured[2][2][64] = {{{false}}};
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
   const int di = D == 64 ? 0 : 1;
-  if (dev < 0 || dev >= 64 || !configured[di][dev]) {
-    if (D == 64) L3CI_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    else L3CI_CUDA_TRY(cudaFuncSetAttribute(prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev >= 0 && dev < 64) configured[di][dev] = true;
+  if (dev < 0 || dev >= 64 || !configured[pair][di][dev]) {
+    const void* fn = pair ? (D == 64 ? (const void*)prefill_tc_pair_kernel<64> : (const void*)prefill_tc_pair_kernel<128>)
+                          : (D == 64 ? (const void*)prefill_tc_kernel<64> : (const void*)prefill_tc_kernel<128>);
+    L3CI_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 64) configured[pair][di][dev] = true;
   }
-  if (D == 64) prefill_tc_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+  if (pair) {
+    if (D == 64) prefill_tc_pair_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    else prefill_tc_pair_kernel<128><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+  } else if (D == 64) prefill_tc_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
   else prefill_tc_kernel<128><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
   L3CI_CHECK_LAUNCH("prefill_tc_kernel");
   return L3CI_OK;

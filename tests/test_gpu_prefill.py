@@ -41,6 +41,15 @@ def test_head_ratios(capi, device, Hq, Hkv):
     _check(capi, device, 1, Hq, Hkv, 64, 150, seed=Hq)
 
 
+# The tcgen05 kernel comes in two forms: two query heads of a KV head per CTA when the head ratio is even, one head
+# per CTA otherwise (ratios 1 and 3 here).
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 8), (6, 2), (8, 4), (16, 2), (2, 1)])
+@pytest.mark.parametrize("T", [128, 300, 640])
+def test_head_ratios_on_the_tensor_memory_kernel(capi, device, Hq, Hkv, D, T):
+    _check(capi, device, 2, Hq, Hkv, D, T, seed=Hq * 7 + T + D, variant=1)
+
+
 def test_model_prefill_shape(capi, device):
     # benchmark_model.py's first scenario at a smaller batch: 128-token prompts of the 1B shape
     _check(capi, device, 4, 32, 8, 64, 128, seed=5)
