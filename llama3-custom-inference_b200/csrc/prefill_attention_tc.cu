@@ -2,21 +2,25 @@
 // memory (filled by bulk tensor copies) or tensor memory, accumulators in tensor memory (TMEM).
 //
 // Same computation as prefill_attention.cu (the reference's model.py:114-116 SDPA call), for prompts long enough
-// that the arithmetic, not the launch, is what costs.  One CTA = 128 query rows of one query head:
+// that the arithmetic, not the launch, is what costs.  Two kernels, 128 query rows per head and CTA, 10 warps:
 //   warp 0        producer: Q once, then K and V tiles of 128 keys through 2-stage rings of bulk tensor copies
-//   warp 1        allocates TMEM and issues the MMAs (one thread): S_j = Q K_j^T into one of two 128-column
-//                 accumulators, O += P_j V_j into a third; tcgen05.commit signals the mbarriers
-//   warps 2-9     softmax, two groups of four warps: group e takes the tiles j with j % 2 == e, with its own
-//                 score accumulator S_e, its own output accumulator O_e and its own running (m_ref, l) per row, so
-//                 the two groups never wait for each other and one group's TMEM reads run under the other's
-//                 exponentials.  Thread r of a group owns query row r (tcgen05.ld 32x32b gives a thread its row):
-//                 the row of S_j goes to registers, p = 2^(s * scale - m_ref) is packed to bf16 and stored over
-//                 S_j as the A operand of the second MMA.  O_e stays in TMEM and the MMA accumulates into it; the
-//                 reference maximum m_ref of a row only moves when the running maximum has outgrown it by more
-//                 than 2^8 (p stays below 2^8, harmless in fp32 / bf16), and only then is the row of O_e rescaled
-//                 in TMEM.  At the end the two groups' (m_ref, l, O) of a row are merged like two split-KV partials
-// S_{j+1} is computed while the softmax of S_j runs.  K is the B operand as it lies in the cache ([keys][D],
-// K-major); V is used MN-major, again as it lies.  Every wait is bounded; TMEM is freed on every path.
+//   warp 1        allocates TMEM and issues the MMAs: S = Q K_j^T into a 128-column score accumulator,
+//                 O += P_j V_j into an output accumulator; tcgen05.commit signals the mbarriers.  All lanes run the
+//                 issue code and one elected lane predicates the instructions (see tc_commit below).
+//   warps 2-9     softmax, two groups of four warps.  Thread r of a group owns query row r (tcgen05.ld 32x32b gives
+//                 a thread its row): the row of S_j goes to registers, p = 2^(s * scale - m_ref) is packed to bf16
+//                 and stored over S_j as the A operand of the second MMA.  O stays in TMEM and the MMA accumulates
+//                 into it; the reference maximum m_ref of a row only moves when the running maximum has outgrown it
+//                 by more than 2^8 (p stays below 2^8, harmless in fp32 / bf16), and only then is the row of O
+//                 rescaled in TMEM.  The arithmetic runs two lanes at a time (fma / add .f32x2, three-input max):
+//                 the groups' own instructions, not the special-function unit, were what a tile cost.
+// prefill_tc_pair_kernel (head ratio Hq / Hkv even): a CTA takes TWO query heads of one KV head; group e owns head
+//                 hq0 + e with all its key tiles (its own Q tile, S_e, O_e), K and V tiles are loaded once for both.
+// prefill_tc_kernel (any head ratio): one head per CTA; group e takes the key tiles j with j % 2 == e with its own
+//                 S_e, O_e and running (m_ref, l), and the two partial results of a row are merged at the end like
+//                 two split-KV partials.
+// K is the B operand as it lies in the cache ([keys][D], K-major); V is used MN-major, again as it lies.  Every
+// wait is bounded; TMEM is freed on every path.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -341,13 +345,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
+        // in stages over the whole chunk, so that the 32 exponentials are issued back to back
+        unsigned long long t2[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t2[i] = f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2);
+        float pe[32];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float t0, t1;
-          f2_unpack(f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2), t0, t1);
-          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(p0, p1));
-          pk[i] = pack_bf16x2(p0, p1);
+          f2_unpack(t2[i], t0, t1);
+          pe[2 * i] = fast_exp2(t0);
+          pe[2 * i + 1] = fast_exp2(t1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(pe[2 * i], pe[2 * i + 1]));
+          pk[i] = pack_bf16x2(pe[2 * i], pe[2 * i + 1]);
         }
         tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
       }
@@ -636,13 +649,22 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
+        // in stages over the whole chunk, so that the 32 exponentials are issued back to back
+        unsigned long long t2[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t2[i] = f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2);
+        float pe[32];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float t0, t1;
-          f2_unpack(f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2), t0, t1);
-          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(p0, p1));
-          pk[i] = pack_bf16x2(p0, p1);
+          f2_unpack(t2[i], t0, t1);
+          pe[2 * i] = fast_exp2(t0);
+          pe[2 * i + 1] = fast_exp2(t1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(pe[2 * i], pe[2 * i + 1]));
+          pk[i] = pack_bf16x2(pe[2 * i], pe[2 * i + 1]);
         }
         tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
       }
