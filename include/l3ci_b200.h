@@ -56,7 +56,8 @@ L3CI_API const char* l3ci_version(void);
 L3CI_API uint64_t l3ci_set_device_wait_limit_ns(uint64_t ns);
 
 /* Programmatic dependent launch, on (1, the default) or off (0), for the launches made after this call; returns the
- * previous setting.  When on, the streaming kernels of this library (decode attention's static-deal kernel, RMSNorm,
+ * previous setting.  When on, the streaming kernels of this library (decode attention's static-deal kernel where it
+ * runs without clusters, RMSNorm,
  * SiLU*mul, the rotary kernels, the token-choice steps) are launched so that their grid may be set up on the SMs
  * while the previous kernel of the stream is still draining; each of them waits (griddepcontrol.wait) for that
  * kernel's completion and the visibility of its writes before its first global access, so results and stream order

@@ -627,15 +627,15 @@ int launch_instance(const SmallParams& p, const UnitSplit& s, bool wide, size_t 
   cfg.blockDim = dim3(32 * (wide ? kClWarps : kSmWarps));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  // (Cluster launches stay plain: with programmatic stream serialization on top of the cluster attribute the
+  // 131 072-token call measured 84.7 us against 83.7, a 16 384-token shard 15.41 against 15.29.)
+  cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)s.C;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = programmatic_launch_enabled() ? 2 : 1;
+  cfg.numAttrs = 1;
   const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, true, kExchange>, p)
                              : cudaLaunchKernelEx(&cfg, flash_decode_small_kernel<D, true, true, false, kExchange>, p);
   if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of flash_decode_small_kernel failed: %s", cudaGetErrorString(e));

@@ -1,6 +1,6 @@
 """Compiles the reference's own CUDA extension, unmodified, for sm_100.  TEST INFRASTRUCTURE.
 
-    python oracle/build_ref.py [<reference checkout>]        (default: /root/reference)
+    python oracle/build_ref.py [<reference checkout>]        (default: $L3CI_REFERENCE_CHECKOUT, else DEFAULT_CHECKOUT below)
 
 Sources are compiled where they lie in the checkout (custom_kernels/custom_kernels.cu and
 custom_kernels/main.cpp with their two headers); nothing is copied.  The only output is
@@ -34,7 +34,7 @@ HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
 MODULE = "reference_kernels_sm100"
 OUT = OUT_DIR / (MODULE + ".so")
-DEFAULT_CHECKOUT = Path("/root/reference")
+DEFAULT_CHECKOUT = Path(os.environ.get("L3CI_REFERENCE_CHECKOUT", "/root/reference"))
 
 
 def _run(cmd):
