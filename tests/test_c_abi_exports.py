@@ -94,3 +94,15 @@ def test_device_wait_limit_setter_round_trips(capi):
     prev = lib.l3ci_set_device_wait_limit_ns(123)
     assert lib.l3ci_set_device_wait_limit_ns(prev) == 123
     assert lib.l3ci_set_device_wait_limit_ns(prev) == prev
+
+
+def test_programmatic_launch_switch_round_trips(capi):
+    lib = capi.load()
+    prev = lib.l3ci_set_programmatic_launch(0)
+    assert prev in (0, 1)
+    assert lib.l3ci_set_programmatic_launch(1) == 0
+    assert lib.l3ci_set_programmatic_launch(7) == 1       # any non-zero value means on
+    assert lib.l3ci_set_programmatic_launch(prev) == 1
+    with capi.programmatic_launch(False):
+        assert lib.l3ci_set_programmatic_launch(0) == 0
+    assert lib.l3ci_set_programmatic_launch(prev) == prev
