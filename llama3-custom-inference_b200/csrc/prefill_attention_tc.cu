@@ -193,9 +193,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
   const uint32_t t_s[2] = {tmem, tmem + 128u};
   const uint32_t t_o[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
 
-  const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
-  const int hq = (int)((blockIdx.x / p.m_blocks) % p.Hq);
-  const int b = (int)(blockIdx.x / ((long long)p.m_blocks * p.Hq));
+  // Longest query blocks first over the WHOLE launch (all heads' last block, then all heads' last but one, ...): the
+  // CTAs are handed out in this order as SMs come free, which is longest-processing-time-first scheduling.  (With
+  // the blocks of one head in a row, the last heads' long blocks started late: 16 % of the SM time stood idle.)
+  const int heads_all = p.Hq * p.B;
+  const int mb = p.m_blocks - 1 - (int)(blockIdx.x / heads_all);
+  const int hq = (int)(blockIdx.x % heads_all) % p.Hq;
+  const int b = (int)(blockIdx.x % heads_all) / p.Hq;
   const int hkv = hq / p.R;
   const int m0 = mb * kTcRows;
   const int last_row = min(m0 + kTcRows, p.T) - 1;
@@ -486,10 +490,12 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
   const uint32_t t_s[2] = {tmem, tmem + 128u};
   const uint32_t t_o[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
 
-  const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
+  // longest query blocks first over the whole launch (see prefill_tc_kernel)
   const int pairs = p.Hq >> 1;
-  const int hq0 = 2 * (int)((blockIdx.x / p.m_blocks) % pairs);   // the CTA's query heads: hq0, hq0 + 1 (R is even)
-  const int b = (int)(blockIdx.x / ((long long)p.m_blocks * pairs));
+  const int pairs_all = pairs * p.B;
+  const int mb = p.m_blocks - 1 - (int)(blockIdx.x / pairs_all);
+  const int hq0 = 2 * ((int)(blockIdx.x % pairs_all) % pairs);   // the CTA's query heads: hq0, hq0 + 1 (R is even)
+  const int b = (int)(blockIdx.x % pairs_all) / pairs;
   const int hkv = hq0 / p.R;
   const int m0 = mb * kTcRows;
   const int last_row = min(m0 + kTcRows, p.T) - 1;
