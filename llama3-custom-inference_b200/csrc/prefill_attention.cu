@@ -73,9 +73,11 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_
   __syncthreads();
 
   // work item: query block (last first), then query head, then sequence
-  const int mb = p.m_blocks - 1 - (int)(blockIdx.x % p.m_blocks);
-  const int hq = (int)((blockIdx.x / p.m_blocks) % p.Hq);
-  const int b = (int)(blockIdx.x / ((long long)p.m_blocks * p.Hq));
+  // longest query blocks first over the whole launch: CTAs are handed out in this order as SMs come free
+  const int heads_all = p.Hq * p.B;
+  const int mb = p.m_blocks - 1 - (int)(blockIdx.x / heads_all);
+  const int hq = (int)(blockIdx.x % heads_all) % p.Hq;
+  const int b = (int)(blockIdx.x % heads_all) / p.Hq;
   const int hkv = hq / p.R;
   const int m0 = mb * kPfRows;
   // keys this block can see: j <= start_pos + (last row of the block), j < n_keys
@@ -283,8 +285,8 @@ extern "C" int l3ci_prefill_attention(const l3ci_prefill_args* a) {
       (B > 1 && (a->k_sb <= 0 || a->v_sb <= 0)))
     return fail(L3CI_ERR_INVALID, "prefill_attention: k/v strides must be positive");
   if (a->variant < 0 || a->variant > 2) return fail(L3CI_ERR_INVALID, "prefill_attention: variant %d", a->variant);
-  // By measurement (B=4, Hq=32, T=2048): the tcgen05 kernel wins at both head sizes (654 vs 321 TFLOP/s at 128,
-  // 371 vs 278 at 64); prompts shorter than its block of 128 query rows, and q or out layouts the copy engine or
+  // By measurement (B=4, Hq=32, T=2048): the tcgen05 kernel wins at both head sizes (797 vs 321 TFLOP/s at 128,
+  // 470 vs 278 at 64); prompts shorter than its block of 128 query rows, and q or out layouts the copy engine or
   // 16-byte stores cannot take, go to the mma.sync kernel.
   if (a->variant == 1 || (a->variant == 0 && T >= 128)) {
     const int st = launch_prefill_tc(a);
