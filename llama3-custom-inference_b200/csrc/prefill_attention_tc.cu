@@ -40,6 +40,11 @@ constexpr int kTcKeys = 128;   // keys per tile (N of S, K of P V)
 constexpr int kTcStages = 2;
 constexpr int kTcSoftmaxWarps = 8;                       // two groups of four: even tiles, odd tiles
 constexpr int kTcThreads = 32 * (2 + kTcSoftmaxWarps);   // + producer warp + MMA warp
+// The head-pair kernel keeps its roles in whole warpgroups (setmaxnreg acts on four warps at a time): warps 0-3 are
+// producer, MMA warp and two idle warps, warps 4-11 the softmax groups.  384 threads start with 168 registers each.
+constexpr int kTcPairThreads = 32 * (4 + kTcSoftmaxWarps);
+constexpr int kTcPairRegsLow = 56, kTcPairRegsHigh = 224;
+static_assert(4 * kTcPairRegsLow + kTcSoftmaxWarps * kTcPairRegsHigh <= 12 * 168, "the re-deal stays within the CTA's registers");
 constexpr uint32_t kTmemCols = 512;                      // S_0, S_1 (128 columns each), O_0, O_1 (D columns each)
 
 struct TcParams {
@@ -453,7 +458,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 // CTA: 5.7 TB/s, enough to make the MMA warp wait for K), halves the number of CTAs and with it the share of their
 // start and end in the launch, and needs no merge of two partial results at the end.
 template <int D>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcPairThreads, 1)
 prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, const TcParams p) {
   constexpr int kHalves = D / 64;
@@ -503,7 +508,11 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
   const int n_tiles = (keys + kTcKeys - 1) / kTcKeys;
   bool ok = true;
 
+  // Registers follow the roles: the first warpgroup (producer, MMA warp, two idle warps) hands most of its share to
+  // the two softmax warpgroups, whose threads carry a row of 128 scores each.
+  // (each role's branch opens with its own setmaxnreg, so that the compiler sees which budget holds where)
   if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
     // ---- producer ----
     const uint64_t policy = l2_evict_first_policy();
     if (lane == 0) {
@@ -534,6 +543,7 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
       __syncwarp();
     }
   } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
     // ---- MMA issue (lane 0), the whole warp takes the waits ----
     constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
     constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
@@ -586,10 +596,11 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         }
       }
     }
-  } else {
+  } else if (warp >= 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcPairRegsHigh));
     // ---- softmax and output: group e = query head hq0 + e, all key tiles; thread owns query row r ----
     const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
-    const int e = (warp - 2) >> 2;                 // warps 2-5: head hq0, warps 6-9: head hq0 + 1
+    const int e = (warp - 4) >> 2;                 // warps 4-7: head hq0, warps 8-11: head hq0 + 1
     const int r = q4 * 32 + lane;
     const int t = m0 + r;                          // query index
     const int limit = p.start_pos + t;             // last key this row may see
@@ -719,6 +730,8 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
         *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + ch * 8) =
             *reinterpret_cast<const uint4*>(stage + row * kPitch + ch * 16);
     }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));   // the two idle warps of the first warpgroup
   }
   if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
   // Every thread comes here (all waits are bounded); then nothing of this CTA uses TMEM any more.
@@ -765,8 +778,8 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
     if (dev >= 0 && dev < 64) configured[pair][di][dev] = true;
   }
   if (pair) {
-    if (D == 64) prefill_tc_pair_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
-    else prefill_tc_pair_kernel<128><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    if (D == 64) prefill_tc_pair_kernel<64><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    else prefill_tc_pair_kernel<128><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
   } else if (D == 64) prefill_tc_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
   else prefill_tc_kernel<128><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);
   L3CI_CHECK_LAUNCH("prefill_tc_kernel");
