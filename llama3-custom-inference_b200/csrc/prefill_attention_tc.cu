@@ -16,6 +16,8 @@
 //                 the groups' own instructions, not the special-function unit, were what a tile cost.
 // prefill_tc_pair_kernel (head ratio Hq / Hkv even): a CTA takes TWO query heads of one KV head; group e owns head
 //                 hq0 + e with all its key tiles (its own Q tile, S_e, O_e), K and V tiles are loaded once for both.
+//                 12 warps: the roles sit in whole warpgroups (warps 0-3: producer, MMA warp, two idle warps; warps
+//                 4-11: the softmax groups) so that setmaxnreg can move registers from the first to the other two.
 // prefill_tc_kernel (any head ratio): one head per CTA; group e takes the key tiles j with j % 2 == e with its own
 //                 S_e, O_e and running (m_ref, l), and the two partial results of a row are merged at the end like
 //                 two split-KV partials.
