@@ -61,6 +61,12 @@ def test_long_prompt(capi, device, variant):
     _check(capi, device, 2, 32, 8, 64, 1000, seed=7, variant=variant)
 
 
+def test_very_long_prompt_on_the_default_kernel(capi, device):
+    # 32 query blocks per head: every CTA of the head-pair kernel walks up to 32 key tiles
+    _check(capi, device, 1, 8, 2, 128, 4096, seed=8)
+    _check(capi, device, 1, 4, 4, 64, 4000, seed=9)      # head ratio 1: one head per CTA, ragged last block
+
+
 @pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("start_pos,T,S", [(100, 60, 160), (64, 64, 200), (1, 1, 2), (300, 5, 305), (7, 130, 137),
                                            (200, 300, 640), (128, 128, 256)])
