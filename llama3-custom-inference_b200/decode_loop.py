@@ -4,7 +4,9 @@ Host-side mirror of what the reference's model does around its three extension c
 `CausalSelfAttention` / `MLP` / `LLaMA3.forward` (model.py:92-149, 203-232) and the greedy branch of
 `LLaMA3.generate` (model.py:363-381) — restricted to what the end-to-end benchmark needs: random-init
 weights of the Llama-3.2-1B architecture (or any `DecoderConfig`), a batch of equal-length prompts, greedy or
-top-p decoding with `ignore_eos`.  It is a harness, not a model library: no checkpoint loading, no tokenizer.
+top-p decoding with `ignore_eos`.  It is a harness, not a model library: no tokenizer; weights come from
+`init_weights` (random) or from a Hugging Face Llama state dict through `weights_from_hf` / `config_from_hf`, which
+restate the reference's key mapping and its un-permutation of the q and k projections (model.py:235-280).
 
 What differs from the reference's loop, all on the caller's side of the kernels:
   * rotary embedding, the K/V cache write and the split of q|k|v are one call (`rot_embed_kv_cache` with
@@ -45,7 +47,11 @@ class DecoderConfig:
     hidden_dim: int = 8192
     norm_eps: float = 1e-5
     rope_theta: float = 500000.0
-    rope_scale_factor: float = 32.0
+    rope_scale_factor: float = 32.0      # (the reference's apply_scaling hard-codes 8, model.py:29; Llama-3.2 uses 32)
+    rope_low_freq_factor: float = 1.0    # model.py:30-32
+    rope_high_freq_factor: float = 4.0
+    rope_old_context_len: int = 8192
+    rope_scaled: bool = True
 
     @property
     def head_dim(self) -> int:
@@ -69,8 +75,11 @@ class Llama3Decoder:
         bf16 = dict(dtype=torch.bfloat16, device=self.device)
         self.cache_k = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
         self.cache_v = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, **bf16) for _ in range(cfg.n_layer)]
-        self.freqs = rope_table.precompute_freqs_cis(D, max_len, cfg.rope_theta, True,
-                                                     scale_factor=cfg.rope_scale_factor).to(self.device)
+        self.freqs = rope_table.precompute_freqs_cis(D, max_len, cfg.rope_theta, cfg.rope_scaled,
+                                                     scale_factor=cfg.rope_scale_factor,
+                                                     low_freq_factor=cfg.rope_low_freq_factor,
+                                                     high_freq_factor=cfg.rope_high_freq_factor,
+                                                     old_context_len=cfg.rope_old_context_len).to(self.device)
         assert self.w["h0.attn"].shape == (qkv_rows, E) and self.w["h0.gate_up"].shape == (2 * F_, E)
         self._graph = None
         self._kernel_for_batch = {}
@@ -129,7 +138,8 @@ class Llama3Decoder:
             _nvtx_pop()
         # the reference widens the logits to fp32 first (model.py:226); the widening is monotonic, so the argmax
         # of the bf16 values is the same index
-        return F.linear(h[:, -1, :], w["wte"])                                         # model.py:225 (tied head)
+        # model.py:225; the head is tied to the embedding (model.py:189) unless the checkpoint brought its own
+        return F.linear(h[:, -1, :], w.get("lm_head", w["wte"]))
 
     # ---- greedy generation --------------------------------------------------------------------------------
     @torch.inference_mode()
@@ -190,6 +200,55 @@ class Llama3Decoder:
         torch.cuda.current_stream(dev).wait_stream(side)
         self._graph = graph
         return out
+
+
+def config_from_hf(hf_config) -> DecoderConfig:
+    """The architecture numbers `from_pretrained_llama3_hf` takes from a Hugging Face Llama config (model.py:290-296),
+    plus the rotary parameters, which the reference hard-codes (model.py:29-32, 163) and the config carries."""
+    rope = getattr(hf_config, "rope_parameters", None) or getattr(hf_config, "rope_scaling", None) or {}
+    theta = rope.get("rope_theta", None) or getattr(hf_config, "rope_theta", None) or 500000.0
+    scaled = rope.get("rope_type", rope.get("type", "default")) == "llama3"
+    return DecoderConfig(vocab_size=hf_config.vocab_size, n_layer=hf_config.num_hidden_layers,
+                         n_head=hf_config.num_attention_heads, n_kv_head=hf_config.num_key_value_heads,
+                         n_embd=hf_config.hidden_size, hidden_dim=hf_config.intermediate_size,
+                         norm_eps=hf_config.rms_norm_eps, rope_theta=float(theta), rope_scaled=scaled,
+                         rope_scale_factor=float(rope.get("factor", 8.0)),
+                         rope_low_freq_factor=float(rope.get("low_freq_factor", 1.0)),
+                         rope_high_freq_factor=float(rope.get("high_freq_factor", 4.0)),
+                         rope_old_context_len=int(rope.get("original_max_position_embeddings", 8192)))
+
+
+def weights_from_hf(state_dict: dict, cfg: DecoderConfig) -> dict:
+    """This loop's weights from a Hugging Face Llama state dict: the key mapping of `adapt_llama_state_dict_keys_hf`
+    (model.py:235-280).  The q and k projections are un-permuted (model.py:244-245, 258-264): the Hugging Face
+    conversion reorders each head's rows from the interleaved (even, odd) pair layout of the original weights to
+    "first half, second half", and the rotary kernel here, like the reference's, rotates adjacent pairs."""
+    D = cfg.head_dim
+
+    def unpermute(w, n_heads):
+        rows, cols = w.shape
+        return w.view(n_heads, 2, rows // n_heads // 2, cols).transpose(1, 2).reshape(rows, cols)
+
+    def get(name):
+        return state_dict[name].detach().to(torch.bfloat16)
+
+    w = {"wte": get("model.embed_tokens.weight"), "ln_f": get("model.norm.weight")}
+    head = state_dict.get("lm_head.weight")
+    if head is not None and head.data_ptr() != state_dict["model.embed_tokens.weight"].data_ptr():
+        w["lm_head"] = head.detach().to(torch.bfloat16)   # an untied output projection (the 8B and 70B checkpoints)
+    for l in range(cfg.n_layer):
+        src, p = f"model.layers.{l}.", f"h{l}."
+        q = unpermute(get(src + "self_attn.q_proj.weight"), cfg.n_head)
+        k = unpermute(get(src + "self_attn.k_proj.weight"), cfg.n_kv_head)
+        assert q.shape[0] == cfg.n_head * D and k.shape[0] == cfg.n_kv_head * D
+        w[p + "attn"] = torch.cat([q, k, get(src + "self_attn.v_proj.weight")], dim=0)          # c_attn, model.py:255-266
+        w[p + "proj"] = get(src + "self_attn.o_proj.weight")
+        w[p + "ln_1"] = get(src + "input_layernorm.weight")
+        w[p + "ln_2"] = get(src + "post_attention_layernorm.weight")
+        w[p + "fc2"] = get(src + "mlp.gate_proj.weight")                                        # model.py:271
+        w[p + "fc"] = get(src + "mlp.up_proj.weight")
+        w[p + "mlp_proj"] = get(src + "mlp.down_proj.weight")
+    return w
 
 
 def init_weights(cfg: DecoderConfig, seed: int = 42) -> dict:

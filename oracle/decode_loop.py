@@ -19,7 +19,11 @@ class CpuDecoder:
         D = cfg.n_embd // cfg.n_head
         self.cache_k = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, dtype=torch.bfloat16) for _ in range(cfg.n_layer)]
         self.cache_v = [torch.zeros(max_batch, max_len, cfg.n_kv_head, D, dtype=torch.bfloat16) for _ in range(cfg.n_layer)]
-        self.freqs = freqs_cis_reference(D, max_len, cfg.rope_theta, True, scale_factor=cfg.rope_scale_factor)
+        self.freqs = freqs_cis_reference(D, max_len, cfg.rope_theta, getattr(cfg, "rope_scaled", True),
+                                         scale_factor=cfg.rope_scale_factor,
+                                         low_freq_factor=getattr(cfg, "rope_low_freq_factor", 1.0),
+                                         high_freq_factor=getattr(cfg, "rope_high_freq_factor", 4.0),
+                                         old_context_len=getattr(cfg, "rope_old_context_len", 8192))
 
     def forward(self, tokens: torch.Tensor, start_pos: int, return_logits: bool = False):
         cfg, w = self.cfg, self.w
@@ -49,5 +53,5 @@ class CpuDecoder:
             h = rms_norm_reference(x, w[p + "ln_2"], cfg.norm_eps)
             x = x + F.linear(F.silu(F.linear(h, w[p + "fc2"])) * F.linear(h, w[p + "fc"]), w[p + "mlp_proj"])
         x = rms_norm_reference(x[:, -1:, :], w["ln_f"], cfg.norm_eps)
-        logits = F.linear(x, w["wte"]).float()[:, -1]
+        logits = F.linear(x, w.get("lm_head", w["wte"])).float()[:, -1]
         return logits if return_logits else logits.argmax(dim=-1)
