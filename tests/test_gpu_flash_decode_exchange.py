@@ -63,6 +63,36 @@ def test_two_ranks_with_the_peer_played_by_the_host(capi, device, shape, max_cta
         assert torch.allclose(got0[:, D], lse0.view(rows), atol=1e-3, rtol=1e-4)
 
 
+@pytest.mark.parametrize("ranks,me", [(8, 5), (4, 3), (3, 0)])
+def test_many_ranks_with_the_peers_played_by_the_host(capi, device, ranks, me):
+    # the widest exchange (8 ranks) and a rank that is not the first: every peer's words are in this rank's buffer
+    # before it starts, and its own words must arrive in every peer's buffer
+    B, Hq, Hkv, D, S = 1, 32, 8, 128, 16384
+    case = inputs.decode_case(B, Hq, Hkv, D, S, seed=111)
+    dc = case.to(device)
+    step = (S // ranks // 64) * 64
+    bounds = [(r * step, S if r == ranks - 1 else (r + 1) * step) for r in range(ranks)]
+    bufs, ptrs = _buffers(capi, ranks, B, Hq, D, device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    want = attention.sdpa_reference(case.q, case.k, case.v)
+    rows = B * Hq
+    for epoch in (1, 2):
+        for r, (lo, hi) in enumerate(bounds):
+            if r != me:
+                o, lse = capi.flash_attention_decode_partial(dc.q, dc.k[:, :, lo:hi], dc.v[:, :, lo:hi])
+                _post(bufs[me], ranks, r, epoch, o, lse)
+        torch.cuda.synchronize()
+        lo, hi = bounds[me]
+        out = capi.flash_decode_exchange(dc.q, dc.k[:, :, lo:hi], dc.v[:, :, lo:hi], ptrs, me, ranks, epoch, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == capi.OK
+        compare.assert_close_attention(out, want)
+        base = ((epoch & 1) * ranks + me) * rows * (D + 1)
+        for r in range(ranks):
+            if r != me:
+                assert bool(((bufs[r][base: base + rows * (D + 1)] >> 32) == epoch).all()), r
+
+
 def test_one_rank_and_the_call_number_kept_in_the_buffer(capi, device):
     # a "world" of one GPU: nothing to wait for; with epoch 0 the kernel numbers its calls itself
     case = inputs.decode_case(2, 32, 8, 128, 5000, seed=102)
