@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "bf16x8.cuh"
 #include "host_common.h"
@@ -742,6 +743,328 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+// The head-pair kernel as a PERSISTENT grid: one CTA per SM walks a list of (head pair, query block) items.  A CTA's
+// start (tensor-memory allocation, and above all the 2.3-3.6 us until Q and the first K tile have landed) and its end
+// (output pass) were 5 us of the 22 an item takes on average; here the producer asks for the next item's Q tiles as
+// soon as the last scores of this one have been computed, the K / V rings and all barrier phases run on across
+// items, and the next item's first scores are computed while the softmax groups still write this one's output.
+// Items are dealt statically, longest first, in snake order over the CTAs (round r: item r * G + c for CTA c, then
+// r * G + G - 1 - c, ...), which balances like a greedy longest-first deal.  The output leaves through a small
+// staging buffer of its own, 32 columns at a time (the K and V stages belong to the next item by then).
+template <int D>
+__global__ void __launch_bounds__(kTcPairThreads, 1)
+prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                  const __grid_constant__ CUtensorMap vmap, const TcParams p) {
+  constexpr int kHalves = D / 64;
+  constexpr int kBoxBytes = 128 * 128;             // 128 rows of 128 bytes
+  constexpr int kTileBytes = kHalves * kBoxBytes;  // a Q, K or V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t q_smem = smem_u32(smem);
+  const uint32_t k_smem = q_smem + 2 * kTileBytes;             // [kTcStages], behind the two Q tiles
+  const uint32_t v_smem = k_smem + kTcStages * kTileBytes;     // [kTcStages]
+  constexpr int kSPitch = 64 + 16;                                 // staging row: 32 output columns + padding
+  uint8_t* stage_all = smem + (2 + 2 * kTcStages) * kTileBytes;    // [2 heads][128 rows][kSPitch]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage_all + 2 * kTcRows * kSPitch);
+  // Q_EMPTY: the item's last scores have been computed, the Q tiles may take the next item's
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, Q_EMPTY = 15, N_BARS = 16 };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps / 2 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&vmap)) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s[2] = {tmem, tmem + 128u};
+  const uint32_t t_o[2] = {tmem + 256u, tmem + 256u + (uint32_t)D};
+
+  // Items in launch order: longest query blocks first over all head pairs (see prefill_tc_kernel); this CTA's
+  // item of round r is r * G + c (r even) or r * G + G - 1 - c (r odd), c = blockIdx.x, G = gridDim.x.
+  const int pairs = p.Hq >> 1;
+  const int pairs_all = pairs * p.B;
+  const long long n_items = (long long)pairs_all * p.m_blocks;
+  struct Item { int hq0, b, hkv, m0, n_tiles; bool valid; };
+  auto item_of = [&](int round) {
+    Item it;
+    const long long idx = (long long)round * gridDim.x + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+    it.valid = idx < n_items;
+    const int mb = p.m_blocks - 1 - (int)(idx / pairs_all);
+    it.hq0 = 2 * ((int)(idx % pairs_all) % pairs);
+    it.b = (int)(idx % pairs_all) / pairs;
+    it.hkv = it.hq0 / p.R;
+    it.m0 = mb * kTcRows;
+    const int last_row = min(it.m0 + kTcRows, p.T) - 1;
+    const int keys = min(p.n_keys, p.start_pos + last_row + 1);
+    it.n_tiles = (keys + kTcKeys - 1) / kTcKeys;
+    return it;
+  };
+  bool ok = true;
+
+  // Registers follow the roles: the first warpgroup (producer, MMA warp, two idle warps) hands most of its share to
+  // the two softmax warpgroups, whose threads carry a row of 128 scores each.
+  // (each role's branch opens with its own setmaxnreg, so that the compiler sees which budget holds where)
+  if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
+    // ---- producer ----
+    const uint64_t policy = l2_evict_first_policy();
+    int fill = 0;   // K (and V) tiles asked for so far, over all items: stage and phase follow from it
+    for (int round = 0; ok; ++round) {
+      const Item it = item_of(round);
+      if (!it.valid) break;
+      if (round > 0 && !mbar_wait_bounded(bar(Q_EMPTY), (round - 1) & 1)) { ok = false; break; }
+      if (lane == 0) {
+        mbar_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+            tma_load_4d(q_smem + e * kTileBytes + h * kBoxBytes, &qmap, bar(Q_FULL), h * 64, it.m0, it.hq0 + e, it.b, policy);
+      }
+      for (int j = 0; j < it.n_tiles && ok; ++j, ++fill) {
+        const int s = fill % kTcStages;
+        const uint32_t par = ((fill / kTcStages) - 1) & 1;
+        if (fill >= kTcStages && !mbar_wait_bounded(bar(K_EMPTY + s), par)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(bar(K_FULL + s), kTileBytes);
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+            tma_load_4d(k_smem + s * kTileBytes + h * kBoxBytes, &kmap, bar(K_FULL + s), h * 64, j * kTcKeys, it.hkv, it.b, policy);
+        }
+        if (fill >= kTcStages && !mbar_wait_bounded(bar(V_EMPTY + s), par)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(bar(V_FULL + s), kTileBytes);
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+            tma_load_4d(v_smem + s * kTileBytes + h * kBoxBytes, &vmap, bar(V_FULL + s), h * 64, j * kTcKeys, it.hkv, it.b, policy);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
+    // ---- MMA issue (lane 0), the whole warp takes the waits ----
+    constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
+    constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
+    const uint32_t elected = lane == 0 ? 1u : 0u;
+    const uint64_t q_desc = smem_desc(q_smem, 16, 1024);
+    const uint64_t k_desc = smem_desc(k_smem, 16, 1024);
+    const uint64_t v_desc = smem_desc(v_smem, kBoxBytes, 1024);
+    // S_{e,g} = Q_e K^T (g: tile number over all items) into head e's score accumulator, which held P_{e,g-1}, read by
+    // an MMA issued before this one; `last`: the item's last tile, after which the Q tiles are free
+    auto issue_s = [&](int e, int g, bool last) {
+      const int s = g % kTcStages;
+      const uint64_t qd = q_desc + (uint64_t)((e * kTileBytes) >> 4);
+      const uint64_t kd = k_desc + (uint64_t)((s * kTileBytes) >> 4);
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint64_t step = (uint64_t)(((ks >> 2) * kBoxBytes + (ks & 3) * 32) / 16);
+        mma_ss(t_s[e], qd + step, kd + step, idesc_qk, ks > 0, elected);
+      }
+      tc_commit(bar(S_FULL + e), elected);
+      if (e == 1) {
+        tc_commit(bar(K_EMPTY + s), elected);   // both heads have read the K stage
+        if (last) tc_commit(bar(Q_EMPTY), elected);
+      }
+    };
+    int g0 = 0;   // tiles of the items before this one
+    for (int round = 0; ok; ++round) {
+      const Item it = item_of(round);
+      if (!it.valid) break;
+      const int n_tiles = it.n_tiles;
+      if (!mbar_wait_bounded(bar(Q_FULL), round & 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(bar(K_FULL + g0 % kTcStages), (g0 / kTcStages) & 1)) { ok = false; break; }
+      tc_fence_after();
+      issue_s(0, g0, n_tiles == 1);
+      issue_s(1, g0, n_tiles == 1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int g = g0 + j, s = g % kTcStages;
+        if (!mbar_wait_bounded(bar(V_FULL + s), (g / kTcStages) & 1)) { ok = false; break; }
+        for (int e = 0; e < 2; ++e) {
+          // O_e += P_{e,g} V once P_{e,g} is in TMEM (any rescaling of O_e happened before that; on an item's first
+          // tile the head's softmax group has also finished reading the previous item's O_e, which it does before
+          // it turns to these scores), then at once the head's next scores, which go where P_{e,g} lay
+          if (!mbar_wait_bounded(bar(P_FULL + e), g & 1)) { ok = false; break; }
+          tc_fence_after();
+          {
+            const uint64_t vd = v_desc + (uint64_t)((s * kTileBytes) >> 4);
+#pragma unroll
+            for (int kk = 0; kk < kTcKeys / 16; ++kk)
+              mma_ts(t_o[e], t_s[e] + kk * 8, vd + (uint64_t)(kk * 128), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u, elected);
+            tc_commit(bar(O_FULL + e), elected);
+            if (e == 1) tc_commit(bar(V_EMPTY + s), elected);
+          }
+          if (j + 1 < n_tiles) {
+            if (e == 0) {
+              if (!mbar_wait_bounded(bar(K_FULL + (g + 1) % kTcStages), ((g + 1) / kTcStages) & 1)) { ok = false; break; }
+              tc_fence_after();
+            }
+            issue_s(e, g + 1, j + 2 == n_tiles);
+          }
+        }
+      }
+      g0 += n_tiles;
+    }
+  } else if (warp >= 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcPairRegsHigh));
+    // ---- softmax and output: group e = query head hq0 + e, all key tiles; thread owns query row r ----
+    const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int e = (warp - 4) >> 2;                 // warps 4-7: head hq0, warps 8-11: head hq0 + 1
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    const uint32_t ts = t_s[e] + lane_addr, to = t_o[e] + lane_addr;
+    constexpr float kLazy = 8.f;                   // log2 of how far the running maximum may outgrow m_ref
+    uint8_t* stage = stage_all + e * (kTcRows * kSPitch);
+    int g0 = 0;                                    // tiles of the items before this one
+    for (int round = 0; ok; ++round) {
+    const Item it = item_of(round);
+    if (!it.valid) break;
+    const int m0 = it.m0, n_tiles = it.n_tiles, hq0 = it.hq0, b = it.b;
+    const int limit = p.start_pos + m0 + r;        // last key this row may see
+    float m_ref = -INFINITY, l_run = 0.f;
+    int done = 0;                                  // tiles of this item so far
+    for (int j = 0; j < n_tiles && ok; ++j, ++done) {
+      if (!mbar_wait_bounded(bar(S_FULL + e), (g0 + j) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const int j0 = j * kTcKeys;
+      const bool edge = j0 + kTcKeys - 1 > p.start_pos + m0 || j0 + kTcKeys > p.n_keys;  // some row of the block is cut
+      uint32_t x[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(ts + c * 32, x[c]);
+      tc_wait_ld();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (edge) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = j0 + c * 32 + i;
+            if (key > limit || key >= p.n_keys) x[c][i] = 0xff800000u;  // -inf
+          }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(x[c][i]), __uint_as_float(x[c][i + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+      // Move the reference maximum (and rescale this warp's rows of O_e) only when some row needs it.
+      if (__any_sync(kFullMask, mx > m_ref + kLazy)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+        if (done > 0) {
+          // O_e holds the products of this group's earlier tiles once their MMA has completed
+          if (!mbar_wait_bounded(bar(O_FULL + e), (g0 + done - 1) & 1)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t y[32];
+            tmem_ld32(to + c * 32, y);
+            tc_wait_ld();
+            uint32_t lo[16], hi[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              lo[i] = __float_as_uint(__uint_as_float(y[i]) * alpha);
+              hi[i] = __float_as_uint(__uint_as_float(y[16 + i]) * alpha);
+            }
+            tmem_st16(to + c * 32, lo);
+            tmem_st16(to + c * 32 + 16, hi);
+          }
+          l_run *= alpha;
+        }
+        m_ref = m_new;
+      }
+      const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+      const unsigned long long scale2 = f2_packf(p.scale_log2e, p.scale_log2e), nmu2 = f2_packf(-mu, -mu);
+      unsigned long long ps2[4] = {0ull, 0ull, 0ull, 0ull};   // four fp32 pairs of partial row sums
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+        // in stages over the whole chunk, so that the 32 exponentials are issued back to back
+        unsigned long long t2[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t2[i] = f2_fma(f2_pack(x[c][2 * i], x[c][2 * i + 1]), scale2, nmu2);
+        float pe[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float t0, t1;
+          f2_unpack(t2[i], t0, t1);
+          pe[2 * i] = fast_exp2(t0);
+          pe[2 * i + 1] = fast_exp2(t1);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          ps2[i & 3] = f2_add(ps2[i & 3], f2_packf(pe[2 * i], pe[2 * i + 1]));
+          pk[i] = pack_bf16x2(pe[2 * i], pe[2 * i + 1]);
+        }
+        tmem_st16(ts + c * 16, pk);                // P_j: 64 packed columns over the first 64 of S_j
+      }
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(f2_add(ps2[0], ps2[1]), a0, a1);
+        f2_unpack(f2_add(ps2[2], ps2[3]), b0, b1);
+        l_run += (a0 + a1) + (b0 + b1);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + e));
+    }
+    // this head's last product of the item
+    if (ok && !mbar_wait_bounded(bar(O_FULL + e), (g0 + n_tiles - 1) & 1)) ok = false;
+    if (!ok) break;
+    tc_fence_after();
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    // The output rows of this head, 32 columns at a time through the group's own staging rows (a thread holds one
+    // row; stored straight to global memory every store instruction of a warp would touch 32 rows): out of tensor
+    // memory, scaled, packed, into shared memory; then 16-byte chunks, a row's four chunks on neighbouring threads.
+    __nv_bfloat16* obase = p.out + (long long)b * p.o_sb + (long long)(hq0 + e) * p.o_sh;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t y[32];
+      tmem_ld32(to + c * 32, y);
+      tc_wait_ld();
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) w[i >> 1] = pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
+      uint4* dst = reinterpret_cast<uint4*>(stage + r * kSPitch);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + e), "r"(32 * kTcSoftmaxWarps / 2) : "memory");   // this group's 128 threads
+#pragma unroll
+      for (int id = r; id < kTcRows * 4; id += 32 * kTcSoftmaxWarps / 2) {
+        const int row = id >> 2, ch = id & 3;
+        if (m0 + row < p.T)
+          *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + c * 32 + ch * 8) =
+              *reinterpret_cast<const uint4*>(stage + row * kSPitch + ch * 16);
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + e), "r"(32 * kTcSoftmaxWarps / 2) : "memory");   // the rows may be written again
+    }
+    g0 += n_tiles;
+    }   // items
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));   // the two idle warps of the first warpgroup
+  }
+  if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
+  // Every thread comes here (all waits are bounded); then nothing of this CTA uses TMEM any more.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
 }  // namespace
 
 // Launch for prompts of at least one full block; called by l3ci_prefill_attention.
@@ -764,22 +1087,32 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = a->status;
   const bool pair = (Hq / Hkv) % 2 == 0;   // two query heads of a KV head per CTA
-  const long long ctas = (long long)B * (pair ? Hq / 2 : Hq) * p.m_blocks;
-  if (ctas > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", ctas);
+  const long long items = (long long)B * (pair ? Hq / 2 : Hq) * p.m_blocks;
+  if (items > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "prefill_attention: too many query blocks (%lld)", items);
+  const int sms = sm_count();
+  // More items than SMs: the persistent form (one CTA per SM walks its items); otherwise a CTA per item.
+  static const bool no_persist = getenv("L3CI_PF_NO_PERSIST") != nullptr;
+  const bool persist = pair && sms > 0 && items > sms && !no_persist;
+  const long long ctas = persist ? sms : items;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   const size_t tile = (size_t)(D / 64) * 128 * 128;
-  const size_t smem = 1024 + ((pair ? 2 : 1) + 2 * kTcStages) * tile + 15 * 8 + 4 * kTcRows * 4 + 16;
-  static bool configured[2][2][64] = {{{false}}};
+  const size_t smem = persist ? 1024 + 6 * tile + 2 * kTcRows * 80 + 16 * 8 + 16
+                              : 1024 + ((pair ? 2 : 1) + 2 * kTcStages) * tile + 15 * 8 + 4 * kTcRows * 4 + 16;
+  static bool configured[3][2][64] = {{{false}}};
   int dev = 0;
   L3CI_CUDA_TRY(cudaGetDevice(&dev));
-  const int di = D == 64 ? 0 : 1;
-  if (dev < 0 || dev >= 64 || !configured[pair][di][dev]) {
-    const void* fn = pair ? (D == 64 ? (const void*)prefill_tc_pair_kernel<64> : (const void*)prefill_tc_pair_kernel<128>)
-                          : (D == 64 ? (const void*)prefill_tc_kernel<64> : (const void*)prefill_tc_kernel<128>);
+  const int di = D == 64 ? 0 : 1, ki = persist ? 2 : pair ? 1 : 0;
+  if (dev < 0 || dev >= 64 || !configured[ki][di][dev]) {
+    const void* fn = persist ? (D == 64 ? (const void*)prefill_tc_persist_kernel<64> : (const void*)prefill_tc_persist_kernel<128>)
+                     : pair  ? (D == 64 ? (const void*)prefill_tc_pair_kernel<64> : (const void*)prefill_tc_pair_kernel<128>)
+                             : (D == 64 ? (const void*)prefill_tc_kernel<64> : (const void*)prefill_tc_kernel<128>);
     L3CI_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev >= 0 && dev < 64) configured[pair][di][dev] = true;
+    if (dev >= 0 && dev < 64) configured[ki][di][dev] = true;
   }
-  if (pair) {
+  if (persist) {
+    if (D == 64) prefill_tc_persist_kernel<64><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    else prefill_tc_persist_kernel<128><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
+  } else if (pair) {
     if (D == 64) prefill_tc_pair_kernel<64><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
     else prefill_tc_pair_kernel<128><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
   } else if (D == 64) prefill_tc_kernel<64><<<(unsigned)ctas, kTcThreads, smem, stream>>>(qmap, kmap, vmap, p);

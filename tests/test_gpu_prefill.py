@@ -61,6 +61,15 @@ def test_long_prompt(capi, device, variant):
     _check(capi, device, 2, 32, 8, 64, 1000, seed=7, variant=variant)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_more_query_blocks_than_sms(capi, device, D):
+    # the persistent form of the head-pair kernel: a CTA per SM walks several (head pair, query block) items, with a
+    # ragged last block, and as a later chunk of a longer cache
+    _check(capi, device, 3, 32, 8, D, 1111, seed=21 + D)
+    _check(capi, device, 2, 32, 8, D, 700, S=1500, start_pos=800, seed=22 + D)
+    _check(capi, device, 5, 16, 8, D, 640, seed=23 + D, scale=0.11)
+
+
 def test_very_long_prompt_on_the_default_kernel(capi, device):
     # 32 query blocks per head: every CTA of the head-pair kernel walks up to 32 key tiles
     _check(capi, device, 1, 8, 2, 128, 4096, seed=8)
