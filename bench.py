@@ -859,7 +859,7 @@ def bench_prefill(args, ext, pkg, dev, rank, world):
                    "l2": f"{n_rot} rotating q/k/v sets", "max_abs_diff_vs_torch_sdpa_gpu": float((got - ref).abs().max())},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": "measured" if peaks else "fallback",
-                     "kernel": "prefill_tc_pair_kernel (tcgen05 + tensor memory, two query heads of a KV head per CTA)"},
+                     "kernel": "prefill_tc_persist_kernel (tcgen05 + tensor memory, two query heads of a KV head per item, persistent grid)"},
         "comparators": {"torch_sdpa_gpu": {"ms_per_step": sd_ms, "TFLOP/s": flops / (sd_ms * 1e-3) / 1e12,
                                            "call": "F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)"}},
         "gpu_launches": steps, "clocks": sampler.summary(),

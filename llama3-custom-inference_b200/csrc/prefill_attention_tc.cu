@@ -18,6 +18,8 @@
 //                 hq0 + e with all its key tiles (its own Q tile, S_e, O_e), K and V tiles are loaded once for both.
 //                 12 warps: the roles sit in whole warpgroups (warps 0-3: producer, MMA warp, two idle warps; warps
 //                 4-11: the softmax groups) so that setmaxnreg can move registers from the first to the other two.
+// prefill_tc_persist_kernel: the same as a persistent grid (one CTA per SM walks its items), when there are more
+//                 (head pair, query block) items than SMs.
 // prefill_tc_kernel (any head ratio): one head per CTA; group e takes the key tiles j with j % 2 == e with its own
 //                 S_e, O_e and running (m_ref, l), and the two partial results of a row are merged at the end like
 //                 two split-KV partials.
