@@ -285,8 +285,8 @@ extern "C" int l3ci_prefill_attention(const l3ci_prefill_args* a) {
       (B > 1 && (a->k_sb <= 0 || a->v_sb <= 0)))
     return fail(L3CI_ERR_INVALID, "prefill_attention: k/v strides must be positive");
   if (a->variant < 0 || a->variant > 2) return fail(L3CI_ERR_INVALID, "prefill_attention: variant %d", a->variant);
-  // By measurement (B=4, Hq=32, T=2048): the tcgen05 kernel wins at both head sizes (914 vs 321 TFLOP/s at 128,
-  // 543 vs 278 at 64); prompts shorter than its block of 128 query rows, and q or out layouts the copy engine or
+  // By measurement (B=4, Hq=32, T=2048): the tcgen05 kernel wins at both head sizes (948 vs 321 TFLOP/s at 128,
+  // 540 vs 278 at 64); prompts shorter than its block of 128 query rows, and q or out layouts the copy engine or
   // 16-byte stores cannot take, go to the mma.sync kernel.
   if (a->variant == 1 || (a->variant == 0 && T >= 128)) {
     const int st = launch_prefill_tc(a);

@@ -50,6 +50,10 @@ constexpr int kTcThreads = 32 * (2 + kTcSoftmaxWarps);   // + producer warp + MM
 constexpr int kTcPairThreads = 32 * (4 + kTcSoftmaxWarps);
 constexpr int kTcPairRegsLow = 56, kTcPairRegsHigh = 224;
 static_assert(4 * kTcPairRegsLow + kTcSoftmaxWarps * kTcPairRegsHigh <= 12 * 168, "the re-deal stays within the CTA's registers");
+// The persistent kernel adds an output warpgroup (warps 12-15): 512 threads start with 128 registers each.
+constexpr int kTcPersistThreads = kTcPairThreads + 128;
+constexpr int kTcPersistRegsLow = 56, kTcPersistRegsHigh = 192, kTcPersistRegsOut = 72;
+static_assert(4 * kTcPersistRegsLow + kTcSoftmaxWarps * kTcPersistRegsHigh + 4 * kTcPersistRegsOut <= 16 * 128, "register re-deal");
 constexpr uint32_t kTmemCols = 512;                      // S_0, S_1 (128 columns each), O_0, O_1 (D columns each)
 
 struct TcParams {
@@ -752,9 +756,11 @@ prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_co
 // items, and the next item's first scores are computed while the softmax groups still write this one's output.
 // Items are dealt statically, longest first, in snake order over the CTAs (round r: item r * G + c for CTA c, then
 // r * G + G - 1 - c, ...), which balances like a greedy longest-first deal.  The output leaves through a small
-// staging buffer of its own, 32 columns at a time (the K and V stages belong to the next item by then).
+// staging buffer of its own, 32 columns at a time (the K and V stages belong to the next item by then), and it is
+// written by a warpgroup of its own (warps 12-15): a softmax group hands over the row sums after its last tile and
+// turns to the next item at once instead of waiting for the last product and writing 32 KB itself.
 template <int D>
-__global__ void __launch_bounds__(kTcPairThreads, 1)
+__global__ void __launch_bounds__(kTcPersistThreads, 1)
 prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, const TcParams p) {
   constexpr int kHalves = D / 64;
@@ -769,14 +775,18 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
   uint8_t* stage_all = smem + (2 + 2 * kTcStages) * kTileBytes;    // [2 heads][128 rows][kSPitch]
   uint64_t* bars = reinterpret_cast<uint64_t*>(stage_all + 2 * kTcRows * kSPitch);
   // Q_EMPTY: the item's last scores have been computed, the Q tiles may take the next item's
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, Q_EMPTY = 15, N_BARS = 16 };
+  // L_FULL: a head's row sums of the item are in shared memory (its softmax group is done with the item);
+  // O_READ: the output warpgroup has the head's O in registers (the accumulator may take the next item's products)
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, O_FULL = 13, Q_EMPTY = 15,
+         L_FULL = 16, O_READ = 18, N_BARS = 20 };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + N_BARS);
+  float* lrow = reinterpret_cast<float*>(bars + N_BARS + 2);       // [2 heads][128 rows]
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1) ? kTcSoftmaxWarps / 2 : 1);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), (i == P_FULL || i == P_FULL + 1 || i >= L_FULL) ? kTcSoftmaxWarps / 2 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&qmap)) : "memory");
@@ -820,7 +830,7 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
   // the two softmax warpgroups, whose threads carry a row of 128 scores each.
   // (each role's branch opens with its own setmaxnreg, so that the compiler sees which budget holds where)
   if (warp == 0) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPersistRegsLow));
     // ---- producer ----
     const uint64_t policy = l2_evict_first_policy();
     int fill = 0;   // K (and V) tiles asked for so far, over all items: stage and phase follow from it
@@ -857,7 +867,7 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
       }
     }
   } else if (warp == 1) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPersistRegsLow));
     // ---- MMA issue (lane 0), the whole warp takes the waits ----
     constexpr uint32_t idesc_qk = instr_desc(kTcRows, kTcKeys, false);
     constexpr uint32_t idesc_pv = instr_desc(kTcRows, D, true);
@@ -897,9 +907,10 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
         if (!mbar_wait_bounded(bar(V_FULL + s), (g / kTcStages) & 1)) { ok = false; break; }
         for (int e = 0; e < 2; ++e) {
           // O_e += P_{e,g} V once P_{e,g} is in TMEM (any rescaling of O_e happened before that; on an item's first
-          // tile the head's softmax group has also finished reading the previous item's O_e, which it does before
-          // it turns to these scores), then at once the head's next scores, which go where P_{e,g} lay
+          // tile the output warpgroup must have read the previous item's O_e), then at once the head's next scores,
+          // which go where P_{e,g} lay
           if (!mbar_wait_bounded(bar(P_FULL + e), g & 1)) { ok = false; break; }
+          if (j == 0 && round > 0 && !mbar_wait_bounded(bar(O_READ + e), (round - 1) & 1)) { ok = false; break; }
           tc_fence_after();
           {
             const uint64_t vd = v_desc + (uint64_t)((s * kTileBytes) >> 4);
@@ -920,8 +931,8 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
       }
       g0 += n_tiles;
     }
-  } else if (warp >= 4) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcPairRegsHigh));
+  } else if (warp >= 4 && warp < 4 + kTcSoftmaxWarps) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcPersistRegsHigh));
     // ---- softmax and output: group e = query head hq0 + e, all key tiles; thread owns query row r ----
     const int q4 = warp & 3;                       // TMEM lane quarter this warp may touch
     const int e = (warp - 4) >> 2;                 // warps 4-7: head hq0, warps 8-11: head hq0 + 1
@@ -929,12 +940,11 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     const uint32_t ts = t_s[e] + lane_addr, to = t_o[e] + lane_addr;
     constexpr float kLazy = 8.f;                   // log2 of how far the running maximum may outgrow m_ref
-    uint8_t* stage = stage_all + e * (kTcRows * kSPitch);
     int g0 = 0;                                    // tiles of the items before this one
     for (int round = 0; ok; ++round) {
     const Item it = item_of(round);
     if (!it.valid) break;
-    const int m0 = it.m0, n_tiles = it.n_tiles, hq0 = it.hq0, b = it.b;
+    const int m0 = it.m0, n_tiles = it.n_tiles;
     const int limit = p.start_pos + m0 + r;        // last key this row may see
     float m_ref = -INFINITY, l_run = 0.f;
     int done = 0;                                  // tiles of this item so far
@@ -1025,40 +1035,69 @@ prefill_tc_persist_kernel(const __grid_constant__ CUtensorMap qmap, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_FULL + e));
     }
-    // this head's last product of the item
-    if (ok && !mbar_wait_bounded(bar(O_FULL + e), (g0 + n_tiles - 1) & 1)) ok = false;
     if (!ok) break;
-    tc_fence_after();
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    // The output rows of this head, 32 columns at a time through the group's own staging rows (a thread holds one
-    // row; stored straight to global memory every store instruction of a warp would touch 32 rows): out of tensor
-    // memory, scaled, packed, into shared memory; then 16-byte chunks, a row's four chunks on neighbouring threads.
-    __nv_bfloat16* obase = p.out + (long long)b * p.o_sb + (long long)(hq0 + e) * p.o_sh;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t y[32];
-      tmem_ld32(to + c * 32, y);
-      tc_wait_ld();
-      uint32_t w[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) w[i >> 1] = pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
-      uint4* dst = reinterpret_cast<uint4*>(stage + r * kSPitch);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-      asm volatile("bar.sync %0, %1;" ::"r"(2 + e), "r"(32 * kTcSoftmaxWarps / 2) : "memory");   // this group's 128 threads
-#pragma unroll
-      for (int id = r; id < kTcRows * 4; id += 32 * kTcSoftmaxWarps / 2) {
-        const int row = id >> 2, ch = id & 3;
-        if (m0 + row < p.T)
-          *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + c * 32 + ch * 8) =
-              *reinterpret_cast<const uint4*>(stage + row * kSPitch + ch * 16);
-      }
-      asm volatile("bar.sync %0, %1;" ::"r"(2 + e), "r"(32 * kTcSoftmaxWarps / 2) : "memory");   // the rows may be written again
-    }
+    // The row sums go to the output warpgroup (which has read the previous item's before it arrived on O_READ), and
+    // this group turns to the next item: the last product and the output pass are no longer its business.
+    if (round > 0 && !mbar_wait_bounded(bar(O_READ + e), (round - 1) & 1)) { ok = false; break; }
+    lrow[e * kTcRows + r] = l_run;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(L_FULL + e));
     g0 += n_tiles;
     }   // items
+  } else if (warp >= 4 + kTcSoftmaxWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPersistRegsOut));
+    // ---- output: thread owns row r of both heads' O, one head after the other ----
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+    int g0 = 0;
+    for (int round = 0; ok; ++round) {
+      const Item it = item_of(round);
+      if (!it.valid) break;
+      const int m0 = it.m0;
+      for (int e = 0; e < 2 && ok; ++e) {
+        if (!mbar_wait_bounded(bar(L_FULL + e), round & 1)) { ok = false; break; }
+        const float l_all = lrow[e * kTcRows + r];
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        if (!mbar_wait_bounded(bar(O_FULL + e), (g0 + it.n_tiles - 1) & 1)) { ok = false; break; }   // the head's last product
+        tc_fence_after();
+        // 32 columns at a time through the staging rows (a thread holds one row; stored straight to global memory
+        // every store instruction of a warp would touch 32 rows): out of tensor memory, scaled, packed, into shared
+        // memory; then 16-byte chunks, a row's four chunks on neighbouring threads.
+        uint8_t* stage = stage_all + e * (kTcRows * kSPitch);
+        __nv_bfloat16* obase = p.out + (long long)it.b * p.o_sb + (long long)(it.hq0 + e) * p.o_sh;
+        const uint32_t to = t_o[e] + lane_addr;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t y[32];
+          tmem_ld32(to + c * 32, y);
+          tc_wait_ld();
+          if (c == D / 32 - 1) {   // O_e is in registers: the accumulator may take the next item's first product
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_READ + e));
+          }
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) w[i >> 1] = pack_bf16x2(__uint_as_float(y[i]) * inv, __uint_as_float(y[i + 1]) * inv);
+          uint4* dst = reinterpret_cast<uint4*>(stage + r * kSPitch);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          asm volatile("bar.sync 2, 128;" ::: "memory");   // the output warpgroup
+#pragma unroll
+          for (int id = r; id < kTcRows * 4; id += 128) {
+            const int row = id >> 2, ch = id & 3;
+            if (m0 + row < p.T)
+              *reinterpret_cast<uint4*>(obase + (long long)(m0 + row) * p.o_st + c * 32 + ch * 8) =
+                  *reinterpret_cast<const uint4*>(stage + row * kSPitch + ch * 16);
+          }
+          asm volatile("bar.sync 2, 128;" ::: "memory");   // the rows may be written again
+        }
+      }
+      g0 += it.n_tiles;
+    }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPairRegsLow));   // the two idle warps of the first warpgroup
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcPersistRegsLow));   // the two idle warps of the first warpgroup
   }
   if (!ok && lane == 0 && p.status) atomicExch(p.status, (int)L3CI_ERR_DEVICE_WAIT);
   // Every thread comes here (all waits are bounded); then nothing of this CTA uses TMEM any more.
@@ -1098,7 +1137,7 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
   const long long ctas = persist ? sms : items;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
   const size_t tile = (size_t)(D / 64) * 128 * 128;
-  const size_t smem = persist ? 1024 + 6 * tile + 2 * kTcRows * 80 + 16 * 8 + 16
+  const size_t smem = persist ? 1024 + 6 * tile + 2 * kTcRows * 80 + 20 * 8 + 16 + 2 * kTcRows * 4
                               : 1024 + ((pair ? 2 : 1) + 2 * kTcStages) * tile + 15 * 8 + 4 * kTcRows * 4 + 16;
   static bool configured[3][2][64] = {{{false}}};
   int dev = 0;
@@ -1112,8 +1151,8 @@ int launch_prefill_tc(const l3ci_prefill_args* a) {
     if (dev >= 0 && dev < 64) configured[ki][di][dev] = true;
   }
   if (persist) {
-    if (D == 64) prefill_tc_persist_kernel<64><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
-    else prefill_tc_persist_kernel<128><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    if (D == 64) prefill_tc_persist_kernel<64><<<(unsigned)ctas, kTcPersistThreads, smem, stream>>>(qmap, kmap, vmap, p);
+    else prefill_tc_persist_kernel<128><<<(unsigned)ctas, kTcPersistThreads, smem, stream>>>(qmap, kmap, vmap, p);
   } else if (pair) {
     if (D == 64) prefill_tc_pair_kernel<64><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
     else prefill_tc_pair_kernel<128><<<(unsigned)ctas, kTcPairThreads, smem, stream>>>(qmap, kmap, vmap, p);
