@@ -17,7 +17,8 @@
 //      (a block-wide scan of per-thread nucleus mass, then the owning thread walks its 128 entries) to the entry
 //      where the running mass passes u * nucleus mass.  Any fixed order gives the multinomial distribution; index
 //      order needs no permutation.
-// then writes the token exactly as l3ci_greedy_step does.  Weights are recomputed from the logits in every pass
+// Batches of up to half the SMs run as a cluster of two CTAs per row (see peer_value below).
+// It then writes the token exactly as l3ci_greedy_step does.  Weights are recomputed from the logits in every pass
 // (same expression, same bits; the row is 256 KB and stays in L2), nothing is sorted and nothing leaves the SM.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -74,9 +75,46 @@ __device__ __forceinline__ T block_exclusive_scan(T v, T* red, T& total) {
 
 typedef unsigned long long u64;
 
+// Two CTAs per row (a cluster of two, batches of up to half the SMs): each walks half of the row in every pass, and
+// the few numbers a pass yields (maximum, histogram, totals of the scans) are read from the peer's shared memory.
+// Both CTAs then hold the same values and take the same decisions; sums are integers, so the split changes no bit.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename T>
+__device__ __forceinline__ T ld_peer(const T* mine, uint32_t peer) {
+  static_assert(sizeof(T) == 4 || sizeof(T) == 8, "32- or 64-bit values");
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(mine)), "r"(peer));
+  if constexpr (sizeof(T) == 4) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return *reinterpret_cast<T*>(&v);
+  } else {
+    u64 v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+    return *reinterpret_cast<T*>(&v);
+  }
+}
+// This CTA's value and the peer's (kCtas == 2): written to a slot of its own (no slot is used twice in a launch,
+// so one cluster barrier per exchange is enough), read from the peer's after the barrier.
+template <int kCtas, typename T>
+__device__ __forceinline__ T peer_value(T mine, T* slot, uint32_t rank) {
+  if constexpr (kCtas == 1) return T(0);
+  if (threadIdx.x == 0) *slot = mine;
+  cluster_barrier();
+  return ld_peer(slot, rank ^ 1u);
+}
+
 struct RowView {
   const __nv_bfloat16* row;
   long long vocab, nvec;   // nvec 16-byte vectors, then vocab - 8 * nvec scalars
+  long long v_begin, v_end, s_begin;   // this CTA's vectors and where its scalars start (vocab: none)
   float scale, shift;      // weight of logit x: exp2(x * scale - shift), at most 1
   // The weight as a 2^-40 fixed-point integer.  (The hardware exponential, one instruction: a row is walked four
   // times and an SM has to evaluate 128 256 weights per pass; the same instruction on the same input gives the same
@@ -105,8 +143,9 @@ constexpr int kCopies = 8;   // histogram copies (warp w adds to copy w % 8): sp
 // 256 values finds the crossing.  Returns the byte (0xffffffff: the candidates all fit the budget) and subtracts the
 // mass above it from `budget`.  On level 0 the budget is not known yet: the pass yields the sum of all weights
 // (`total_out`) and the budget becomes top_p times it.  All threads take part and get the same answer.
+template <int kCtas>
 __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, uint32_t prefix, float top_p, u64& total_out,
-                                                 u64& budget, uint32_t* limbs, u64* red, int* s_pick, u64* s_above) {
+                                                 u64& budget, uint32_t* limbs, u64* red, int* s_pick, u64* s_above, uint32_t rank) {
   for (int i = threadIdx.x; i < kCopies * 3 * 256; i += kTopPBlock) limbs[i] = 0u;
   __syncthreads();
   uint32_t* mine = limbs + ((threadIdx.x >> 5) % kCopies) * 3 * 256;
@@ -128,15 +167,16 @@ __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, u
     if (bin == run_bin) run_q += q;
     else { flush(); run_bin = bin; run_q = q; }
   };
-  for (long long v = threadIdx.x; v < rv.nvec; v += kTopPBlock) {
+  for (long long v = rv.v_begin + threadIdx.x; v < rv.v_end; v += kTopPBlock) {
     float f[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(rv.row) + v), f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) visit(f[j]);
   }
-  for (long long i = rv.nvec * kVecElems + threadIdx.x; i < rv.vocab; i += kTopPBlock) visit(__bfloat162float(rv.row[i]));
+  for (long long i = rv.s_begin + threadIdx.x; i < rv.vocab; i += kTopPBlock) visit(__bfloat162float(rv.row[i]));
   flush();
   __syncthreads();
+  if constexpr (kCtas == 2) cluster_barrier();   // the peer's histogram is complete too
   // thread t < 256 owns byte value d = 255 - t (a prefix scan over threads is then a suffix scan over byte values):
   // the wanted value is the largest d whose inclusive suffix sum exceeds the budget, i.e. the mass strictly above it
   // is still within the budget and the mass down to it is not
@@ -147,8 +187,11 @@ __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, u
     for (int c = 0; c < kCopies; ++c) {
       const uint32_t* l = limbs + c * 3 * 256;
       h += (u64)l[d] + ((u64)l[256 + d] << 16) + ((u64)l[512 + d] << 32);
+      if constexpr (kCtas == 2)
+        h += (u64)ld_peer(l + d, rank ^ 1u) + ((u64)ld_peer(l + 256 + d, rank ^ 1u) << 16) + ((u64)ld_peer(l + 512 + d, rank ^ 1u) << 32);
     }
   }
+  if constexpr (kCtas == 2) cluster_barrier();   // both have read: the histograms may be cleared for the next level
   u64 total;
   const u64 before = block_exclusive_scan<u64>(h, red, total);   // mass of the byte values above d
   total_out = total;
@@ -163,6 +206,7 @@ __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, u
   return (uint32_t)pick;
 }
 
+template <int kCtas>
 __global__ void __launch_bounds__(kTopPBlock)
 top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, long long row_stride, float inv_temperature,
                   float top_p, unsigned long long seed, long long* __restrict__ out_tokens, long long out_stride,
@@ -177,28 +221,36 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   __shared__ u64 s_above;
   __shared__ int s_owner;
   __shared__ long long s_token;
+  __shared__ u64 s_slots[8];     // values for the peer CTA, one slot per exchange
   pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
   pdl_launch_dependents();  // the next one may be set up while this one runs
-  const long long b = blockIdx.x;
+  const long long b = blockIdx.x / kCtas;
+  const uint32_t rank = kCtas == 2 ? cluster_rank() : 0u;
   RowView rv;
   rv.row = logits + b * row_stride;
   rv.vocab = vocab;
   rv.nvec = (reinterpret_cast<uintptr_t>(rv.row) & 15u) == 0 ? vocab / kVecElems : 0;
   rv.scale = inv_temperature * 1.4426950408889634f;
+  // this CTA's share of the row in the passes that take it in any order: half of the vectors each, the scalars
+  // behind them with the last CTA
+  rv.v_begin = rv.nvec * rank / kCtas;
+  rv.v_end = rv.nvec * (rank + 1) / kCtas;
+  rv.s_begin = rank == kCtas - 1 ? rv.nvec * kVecElems : vocab;
 
   // ---- 1. maximum of the row (the sum of the weights falls out of the first histogram) ----
   float m = -INFINITY;
-  for (long long v = threadIdx.x; v < rv.nvec; v += kTopPBlock) {
+  for (long long v = rv.v_begin + threadIdx.x; v < rv.v_end; v += kTopPBlock) {
     float f[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(rv.row) + v), f);
     m = fmaxf(m, fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7]))));
   }
-  for (long long i = rv.nvec * kVecElems + threadIdx.x; i < vocab; i += kTopPBlock) m = fmaxf(m, __bfloat162float(rv.row[i]));
+  for (long long i = rv.s_begin + threadIdx.x; i < vocab; i += kTopPBlock) m = fmaxf(m, __bfloat162float(rv.row[i]));
   m = group_max<kWarp>(m);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = m;
   __syncthreads();
-  const float row_max = group_max<kWarp>(redf[threadIdx.x & 31]);
+  float row_max = group_max<kWarp>(redf[threadIdx.x & 31]);
+  if constexpr (kCtas == 2) row_max = fmaxf(row_max, peer_value<kCtas>(row_max, reinterpret_cast<float*>(&s_slots[0]), rank));
   rv.shift = row_max * rv.scale;
 
   // ---- 2. boundary of the nucleus: the largest logit pattern k* whose strictly-larger mass is still <= p * Z ----
@@ -206,13 +258,13 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   bool all_kept = false;
   u64 Z = 0, budget = 0, bud = 0;
   {
-    const uint32_t hi = search_level(rv, 0, 0u, top_p, Z, bud, limbs, red, &s_pick, &s_above);
+    const uint32_t hi = search_level<kCtas>(rv, 0, 0u, top_p, Z, bud, limbs, red, &s_pick, &s_above, rank);
     budget = (u64)((double)top_p * (double)Z);
     if (hi == 0xffffffffu) {
       all_kept = true;   // top_p >= 1
     } else {
       u64 unused;
-      const uint32_t lo = search_level(rv, 1, hi, 0.f, unused, bud, limbs, red, &s_pick, &s_above);
+      const uint32_t lo = search_level<kCtas>(rv, 1, hi, 0.f, unused, bud, limbs, red, &s_pick, &s_above, rank);
       key_star = (hi << 8) | (lo == 0xffffffffu ? 0u : lo);   // (the sums are exact, so the second level finds its byte)
     }
   }
@@ -223,8 +275,10 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
 
   // ---- 3. nucleus mass per thread over a CONTIGUOUS run of the row (index order), ties at the boundary counted ----
   // runs of a multiple of 8 entries, so that an aligned row is walked with 16-byte loads
-  const long long per = ((vocab + kTopPBlock - 1) / kTopPBlock + kVecElems - 1) / kVecElems * kVecElems;
-  const long long i_begin = threadIdx.x * per < vocab ? threadIdx.x * per : vocab;
+  constexpr long long kRowThreads = (long long)kTopPBlock * kCtas;   // the first CTA takes the front of the row
+  const long long per = ((vocab + kRowThreads - 1) / kRowThreads + kVecElems - 1) / kVecElems * kVecElems;
+  const long long row_thread = (long long)rank * kTopPBlock + threadIdx.x;
+  const long long i_begin = row_thread * per < vocab ? row_thread * per : vocab;
   const long long i_end = i_begin + per < vocab ? i_begin + per : vocab;
   // calls fn(index, logit) for the entries of this thread's run in increasing order until fn returns true
   auto walk = [&](auto&& fn) {
@@ -250,7 +304,12 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
     return false;
   });
   long long eq_total;
-  const long long eq_before = block_exclusive_scan<long long>(n_eq, redl, eq_total);
+  long long eq_before = block_exclusive_scan<long long>(n_eq, redl, eq_total);
+  if constexpr (kCtas == 2) {   // index order over both CTAs: the second one's entries come after all of the first's
+    const long long peer = peer_value<kCtas>(eq_total, reinterpret_cast<long long*>(&s_slots[1]), rank);
+    if (rank == 1) eq_before += peer;
+    eq_total += peer;
+  }
   // entries equal to the boundary pattern, in index order: the j-th is kept while above + j * w* <= budget
   long long eq_kept = 0;
   if (!all_kept && eq_total > 0) {
@@ -261,7 +320,13 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   eq_mine = eq_mine < 0 ? 0 : (eq_mine > n_eq ? n_eq : eq_mine);
   const u64 mass_mine = w_mine + (u64)eq_mine * w_star;
   u64 mass_total;
-  const u64 mass_before = block_exclusive_scan<u64>(mass_mine, red, mass_total);
+  u64 mass_before = block_exclusive_scan<u64>(mass_mine, red, mass_total);
+  const u64 mass_here = mass_total;   // this CTA's part of the nucleus
+  if constexpr (kCtas == 2) {
+    const u64 peer = peer_value<kCtas>(mass_total, &s_slots[2], rank);
+    if (rank == 1) mass_before += peer;
+    mass_total += peer;
+  }
 
   // ---- 4. the draw: u in [0, 1) with 32 bits, target = floor(u * nucleus mass) < nucleus mass ----
   const long long step = steps ? steps[b] : 0;
@@ -272,8 +337,12 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   __syncthreads();
   if (mass_mine > 0 && mass_before <= target && target < mass_before + mass_mine) s_owner = (int)threadIdx.x;   // exactly one thread
   __syncthreads();
-  const int owner = s_owner < kTopPBlock ? s_owner : 0;   // (an empty nucleus: a row of NaNs)
-  if ((int)threadIdx.x == owner) {
+  // The thread whose run holds the target sits in one of the CTAs; that CTA writes the token.  An empty nucleus (a
+  // row of NaNs) has no such thread: the first CTA's first thread stands in.
+  const bool mine = s_owner < kTopPBlock || (mass_total == 0 && rank == 0);
+  const int owner = s_owner < kTopPBlock ? s_owner : 0;
+  (void)mass_here;
+  if (mine && (int)threadIdx.x == owner) {
     u64 run = mass_before;
     long long eq_seen = eq_before, tok = -1, last = -1;
     walk([&](long long i, float x) {
@@ -290,7 +359,7 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
     s_token = tok;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (mine && threadIdx.x == 0) {
     const long long tok = s_token;
     if (out_tokens && steps) {
       if (step >= 0 && step < out_cols) out_tokens[b * out_stride + step] = tok;
@@ -306,8 +375,10 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   if (nucleus_count) {
     long long total;
     block_exclusive_scan<long long>(n_above + eq_mine, redl, total);
-    if (threadIdx.x == 0) nucleus_count[b] = (int)total;
+    if constexpr (kCtas == 2) total += peer_value<kCtas>(total, reinterpret_cast<long long*>(&s_slots[3]), rank);
+    if (threadIdx.x == 0 && rank == 0) nucleus_count[b] = (int)total;
   }
+  if constexpr (kCtas == 2) cluster_barrier();   // no CTA leaves while its peer may still read its shared memory
 }
 
 }  // namespace
@@ -326,9 +397,33 @@ extern "C" int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, 
   if (!logits || (!out_tokens && !next_input)) return fail(L3CI_ERR_INVALID, "top_p_step: null logits or no output");
   if (rows > 0x7fffffffLL) return fail(L3CI_ERR_INVALID, "top_p_step: too many rows");
   if (steps && (!out_tokens || out_cols <= 0)) return fail(L3CI_ERR_INVALID, "top_p_step: steps needs out_tokens and its width");
-  L3CI_LAUNCH("top_p_step_kernel", top_p_step_kernel, dim3((unsigned)rows), dim3(kTopPBlock), 0, reinterpret_cast<cudaStream_t>(stream_),
-              static_cast<const __nv_bfloat16*>(logits), vocab, row_stride, 1.0f / temperature, top_p, (unsigned long long)seed,
-              reinterpret_cast<long long*>(out_tokens), out_stride, out_cols, reinterpret_cast<long long*>(steps),
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const auto lp = static_cast<const __nv_bfloat16*>(logits);
+  const float inv_t = 1.0f / temperature;
+  const int sms = sm_count();
+  if (sms > 0 && 2 * rows <= sms) {
+    // small batches: a cluster of two CTAs per row, so that the batch still covers the device (64 rows: 128 SMs)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * rows));
+    cfg.blockDim = dim3(kTopPBlock);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, top_p_step_kernel<2>, lp, (long long)vocab, (long long)row_stride, inv_t, top_p,
+                                             (unsigned long long)seed, reinterpret_cast<long long*>(out_tokens), (long long)out_stride,
+                                             (long long)out_cols, reinterpret_cast<long long*>(steps),
+                                             reinterpret_cast<long long*>(next_input), positions, seq_lens, nucleus_count, nucleus_mass);
+    if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of top_p_step_kernel failed: %s", cudaGetErrorString(e));
+    return L3CI_OK;
+  }
+  L3CI_LAUNCH("top_p_step_kernel", top_p_step_kernel<1>, dim3((unsigned)rows), dim3(kTopPBlock), 0, stream,
+              lp, (long long)vocab, (long long)row_stride, inv_t, top_p, (unsigned long long)seed,
+              reinterpret_cast<long long*>(out_tokens), (long long)out_stride, (long long)out_cols, reinterpret_cast<long long*>(steps),
               reinterpret_cast<long long*>(next_input), positions, seq_lens, nucleus_count, nucleus_mass);
   return L3CI_OK;
 }
