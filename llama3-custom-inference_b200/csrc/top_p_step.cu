@@ -75,9 +75,10 @@ __device__ __forceinline__ T block_exclusive_scan(T v, T* red, T& total) {
 
 typedef unsigned long long u64;
 
-// Two CTAs per row (a cluster of two, batches of up to half the SMs): each walks half of the row in every pass, and
-// the few numbers a pass yields (maximum, histogram, totals of the scans) are read from the peer's shared memory.
-// Both CTAs then hold the same values and take the same decisions; sums are integers, so the split changes no bit.
+// Several CTAs per row (a cluster of 2, 4 or 8 while rows x CTAs fit the device): each walks its share of the row in
+// every pass, and the few numbers a pass yields (maximum, histogram, totals of the scans) are read from the peers'
+// shared memory.  All CTAs then hold the same values and take the same decisions; sums are integers, so the split
+// changes no bit.
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -101,14 +102,34 @@ __device__ __forceinline__ T ld_peer(const T* mine, uint32_t peer) {
     return *reinterpret_cast<T*>(&v);
   }
 }
-// This CTA's value and the peer's (kCtas == 2): written to a slot of its own (no slot is used twice in a launch,
-// so one cluster barrier per exchange is enough), read from the peer's after the barrier.
+// The CTAs' values of one quantity: each writes its own to a slot (no slot is used twice in a launch, so one cluster
+// barrier per exchange is enough) and reads the others' after the barrier.  `before`: the sum over the CTAs in front
+// of this one (the first CTA takes the front of the row); returns the sum over all.
 template <int kCtas, typename T>
-__device__ __forceinline__ T peer_value(T mine, T* slot, uint32_t rank) {
-  if constexpr (kCtas == 1) return T(0);
+__device__ __forceinline__ T peer_sum(T mine, T* slot, uint32_t rank, T& before) {
+  before = T(0);
+  if constexpr (kCtas == 1) return mine;
   if (threadIdx.x == 0) *slot = mine;
   cluster_barrier();
-  return ld_peer(slot, rank ^ 1u);
+  T all = T(0);
+#pragma unroll
+  for (uint32_t c = 0; c < (uint32_t)kCtas; ++c) {
+    const T v = c == rank ? mine : ld_peer(slot, c);
+    if (c < rank) before += v;
+    all += v;
+  }
+  return all;
+}
+template <int kCtas>
+__device__ __forceinline__ float peer_max(float mine, float* slot, uint32_t rank) {
+  if constexpr (kCtas == 1) return mine;
+  if (threadIdx.x == 0) *slot = mine;
+  cluster_barrier();
+  float m = mine;
+#pragma unroll
+  for (uint32_t c = 0; c < (uint32_t)kCtas; ++c)
+    if (c != rank) m = fmaxf(m, ld_peer(slot, c));
+  return m;
 }
 
 struct RowView {
@@ -176,7 +197,7 @@ __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, u
   for (long long i = rv.s_begin + threadIdx.x; i < rv.vocab; i += kTopPBlock) visit(__bfloat162float(rv.row[i]));
   flush();
   __syncthreads();
-  if constexpr (kCtas == 2) cluster_barrier();   // the peer's histogram is complete too
+  if constexpr (kCtas > 1) cluster_barrier();   // the peers' histograms are complete too
   // thread t < 256 owns byte value d = 255 - t (a prefix scan over threads is then a suffix scan over byte values):
   // the wanted value is the largest d whose inclusive suffix sum exceeds the budget, i.e. the mass strictly above it
   // is still within the budget and the mass down to it is not
@@ -187,11 +208,14 @@ __device__ __forceinline__ uint32_t search_level(const RowView& rv, int level, u
     for (int c = 0; c < kCopies; ++c) {
       const uint32_t* l = limbs + c * 3 * 256;
       h += (u64)l[d] + ((u64)l[256 + d] << 16) + ((u64)l[512 + d] << 32);
-      if constexpr (kCtas == 2)
-        h += (u64)ld_peer(l + d, rank ^ 1u) + ((u64)ld_peer(l + 256 + d, rank ^ 1u) << 16) + ((u64)ld_peer(l + 512 + d, rank ^ 1u) << 32);
+      if constexpr (kCtas > 1) {
+#pragma unroll
+        for (uint32_t pc = 0; pc < (uint32_t)kCtas; ++pc)
+          if (pc != rank) h += (u64)ld_peer(l + d, pc) + ((u64)ld_peer(l + 256 + d, pc) << 16) + ((u64)ld_peer(l + 512 + d, pc) << 32);
+      }
     }
   }
-  if constexpr (kCtas == 2) cluster_barrier();   // both have read: the histograms may be cleared for the next level
+  if constexpr (kCtas > 1) cluster_barrier();   // all have read: the histograms may be cleared for the next level
   u64 total;
   const u64 before = block_exclusive_scan<u64>(h, red, total);   // mass of the byte values above d
   total_out = total;
@@ -225,7 +249,7 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   pdl_wait();               // the previous kernel of the stream has completed; its writes are visible
   pdl_launch_dependents();  // the next one may be set up while this one runs
   const long long b = blockIdx.x / kCtas;
-  const uint32_t rank = kCtas == 2 ? cluster_rank() : 0u;
+  const uint32_t rank = kCtas > 1 ? cluster_rank() : 0u;
   RowView rv;
   rv.row = logits + b * row_stride;
   rv.vocab = vocab;
@@ -250,7 +274,7 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = m;
   __syncthreads();
   float row_max = group_max<kWarp>(redf[threadIdx.x & 31]);
-  if constexpr (kCtas == 2) row_max = fmaxf(row_max, peer_value<kCtas>(row_max, reinterpret_cast<float*>(&s_slots[0]), rank));
+  row_max = peer_max<kCtas>(row_max, reinterpret_cast<float*>(&s_slots[0]), rank);
   rv.shift = row_max * rv.scale;
 
   // ---- 2. boundary of the nucleus: the largest logit pattern k* whose strictly-larger mass is still <= p * Z ----
@@ -305,10 +329,10 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   });
   long long eq_total;
   long long eq_before = block_exclusive_scan<long long>(n_eq, redl, eq_total);
-  if constexpr (kCtas == 2) {   // index order over both CTAs: the second one's entries come after all of the first's
-    const long long peer = peer_value<kCtas>(eq_total, reinterpret_cast<long long*>(&s_slots[1]), rank);
-    if (rank == 1) eq_before += peer;
-    eq_total += peer;
+  {   // index order over the CTAs: a CTA's entries come after all of those in front of it
+    long long front;
+    eq_total = peer_sum<kCtas>(eq_total, reinterpret_cast<long long*>(&s_slots[1]), rank, front);
+    eq_before += front;
   }
   // entries equal to the boundary pattern, in index order: the j-th is kept while above + j * w* <= budget
   long long eq_kept = 0;
@@ -321,11 +345,10 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   const u64 mass_mine = w_mine + (u64)eq_mine * w_star;
   u64 mass_total;
   u64 mass_before = block_exclusive_scan<u64>(mass_mine, red, mass_total);
-  const u64 mass_here = mass_total;   // this CTA's part of the nucleus
-  if constexpr (kCtas == 2) {
-    const u64 peer = peer_value<kCtas>(mass_total, &s_slots[2], rank);
-    if (rank == 1) mass_before += peer;
-    mass_total += peer;
+  {
+    u64 front;
+    mass_total = peer_sum<kCtas>(mass_total, &s_slots[2], rank, front);
+    mass_before += front;
   }
 
   // ---- 4. the draw: u in [0, 1) with 32 bits, target = floor(u * nucleus mass) < nucleus mass ----
@@ -341,7 +364,6 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   // row of NaNs) has no such thread: the first CTA's first thread stands in.
   const bool mine = s_owner < kTopPBlock || (mass_total == 0 && rank == 0);
   const int owner = s_owner < kTopPBlock ? s_owner : 0;
-  (void)mass_here;
   if (mine && (int)threadIdx.x == owner) {
     u64 run = mass_before;
     long long eq_seen = eq_before, tok = -1, last = -1;
@@ -375,10 +397,11 @@ top_p_step_kernel(const __nv_bfloat16* __restrict__ logits, long long vocab, lon
   if (nucleus_count) {
     long long total;
     block_exclusive_scan<long long>(n_above + eq_mine, redl, total);
-    if constexpr (kCtas == 2) total += peer_value<kCtas>(total, reinterpret_cast<long long*>(&s_slots[3]), rank);
+    long long front;
+    total = peer_sum<kCtas>(total, reinterpret_cast<long long*>(&s_slots[3]), rank, front);
     if (threadIdx.x == 0 && rank == 0) nucleus_count[b] = (int)total;
   }
-  if constexpr (kCtas == 2) cluster_barrier();   // no CTA leaves while its peer may still read its shared memory
+  if constexpr (kCtas > 1) cluster_barrier();   // no CTA leaves while a peer may still read its shared memory
 }
 
 }  // namespace
@@ -401,23 +424,30 @@ extern "C" int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, 
   const auto lp = static_cast<const __nv_bfloat16*>(logits);
   const float inv_t = 1.0f / temperature;
   const int sms = sm_count();
-  if (sms > 0 && 2 * rows <= sms) {
-    // small batches: a cluster of two CTAs per row, so that the batch still covers the device (64 rows: 128 SMs)
+  // Small batches: a cluster of CTAs per row, as many (8, 4, 2) as still run all at once, so that the batch covers
+  // the device (64 rows: 128 SMs; one row: 8).  A 148-SM part holds 15 clusters of 8, 33 of 4 or 74 of 2 of these
+  // CTAs at a time (cudaOccupancyMaxActiveClusters); the bounds scale with the SM count.
+  const int ctas_per_row = sms <= 0 ? 1 : rows * 148 <= 15LL * sms ? 8 : rows * 148 <= 33LL * sms ? 4 : 2 * rows <= sms ? 2 : 1;
+  if (ctas_per_row > 1) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * rows));
+    cfg.gridDim = dim3((unsigned)(ctas_per_row * rows));
     cfg.blockDim = dim3(kTopPBlock);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.x = (unsigned)ctas_per_row;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, top_p_step_kernel<2>, lp, (long long)vocab, (long long)row_stride, inv_t, top_p,
-                                             (unsigned long long)seed, reinterpret_cast<long long*>(out_tokens), (long long)out_stride,
-                                             (long long)out_cols, reinterpret_cast<long long*>(steps),
-                                             reinterpret_cast<long long*>(next_input), positions, seq_lens, nucleus_count, nucleus_mass);
+    auto launch = [&](auto kernel) {
+      return cudaLaunchKernelEx(&cfg, kernel, lp, (long long)vocab, (long long)row_stride, inv_t, top_p, (unsigned long long)seed,
+                                reinterpret_cast<long long*>(out_tokens), (long long)out_stride, (long long)out_cols,
+                                reinterpret_cast<long long*>(steps), reinterpret_cast<long long*>(next_input), positions, seq_lens,
+                                nucleus_count, nucleus_mass);
+    };
+    const cudaError_t e = ctas_per_row == 8 ? launch(top_p_step_kernel<8>) : ctas_per_row == 4 ? launch(top_p_step_kernel<4>)
+                                                                                              : launch(top_p_step_kernel<2>);
     if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of top_p_step_kernel failed: %s", cudaGetErrorString(e));
     return L3CI_OK;
   }

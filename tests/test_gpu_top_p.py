@@ -122,21 +122,26 @@ def test_limits_greedy_and_whole_vocabulary(capi, device):
 
 @pytest.mark.parametrize("kind,vocab", [("normal", 128256), ("flat", 32003), ("two_levels", 128256), ("peaked", 1001),
                                         ("one_hot", 4096)])
-def test_two_ctas_per_row_change_no_bit(capi, device, kind, vocab):
-    """Batches of up to half the SMs run as a cluster of two CTAs per row, larger ones with one CTA per row.  The draw
-    is keyed by (seed, row, step) and all sums are integers, so the same rows give the same tokens, nucleus sizes
-    and masses either way: 40 rows (two CTAs each) against the same 40 rows at the front of a batch of 80."""
-    small, large = 40, 80
+def test_several_ctas_per_row_change_no_bit(capi, device, kind, vocab):
+    """Small batches run as a cluster of 8, 4 or 2 CTAs per row (up to 15, 33, 74 rows), larger ones with one CTA per
+    row.  The draw is keyed by (seed, row, step) and all sums are integers, so the same rows give the same tokens,
+    nucleus sizes and masses either way: the first rows of a batch of 80 (one CTA each) against batches of 10, 30 and
+    40 of them."""
+    large = 80
     logits = _logits(kind, large, vocab, seed=17 + vocab)
-    res = []
-    for rows in (small, large):
+
+    def run(rows):
         out, steps, cur, pos, lens = _state(rows, 3, device)
         count = torch.zeros(rows, dtype=torch.int32, device=device)
         mass = torch.zeros(rows, dtype=torch.float32, device=device)
         for _ in range(3):
             capi.top_p_step(logits[:rows].to(device), 0.7, 0.9, 4242, out, steps, cur, pos, lens, count, mass)
         torch.cuda.synchronize()
-        res.append((out.cpu()[:small], count.cpu()[:small], mass.cpu()[:small], pos.cpu()[:small]))
-    for a, b in zip(*res):
-        assert torch.equal(a, b)
-    assert bool((res[0][3] == 3).all())
+        return out.cpu(), count.cpu(), mass.cpu(), pos.cpu()
+
+    ref = run(large)
+    for small in (10, 30, 40):
+        got = run(small)
+        for a, b in zip(got, ref):
+            assert torch.equal(a, b[:small]), small
+        assert bool((got[3] == 3).all())
