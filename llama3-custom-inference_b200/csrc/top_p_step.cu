@@ -428,14 +428,15 @@ extern "C" int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, 
   // the device (64 rows: 128 SMs; one row: 8).  A 148-SM part holds 15 clusters of 8, 33 of 4 or 74 of 2 of these
   // CTAs at a time (cudaOccupancyMaxActiveClusters); the bounds scale with the SM count.
   const int ctas_per_row = sms <= 0 ? 1 : rows * 148 <= 15LL * sms ? 8 : rows * 148 <= 33LL * sms ? 4 : 2 * rows <= sms ? 2 : 1;
-  if (ctas_per_row > 1) {
+  // (a cluster size the device or its partition cannot place falls back to the next smaller one)
+  for (int c = ctas_per_row; c > 1; c /= 2) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(ctas_per_row * rows));
+    cfg.gridDim = dim3((unsigned)(c * rows));
     cfg.blockDim = dim3(kTopPBlock);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)ctas_per_row;
+    attr[0].val.clusterDim.x = (unsigned)c;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
@@ -446,10 +447,9 @@ extern "C" int l3ci_top_p_step(const void* logits, int64_t rows, int64_t vocab, 
                                 reinterpret_cast<long long*>(steps), reinterpret_cast<long long*>(next_input), positions, seq_lens,
                                 nucleus_count, nucleus_mass);
     };
-    const cudaError_t e = ctas_per_row == 8 ? launch(top_p_step_kernel<8>) : ctas_per_row == 4 ? launch(top_p_step_kernel<4>)
-                                                                                              : launch(top_p_step_kernel<2>);
-    if (e != cudaSuccess) return fail(L3CI_ERR_CUDA, "launch of top_p_step_kernel failed: %s", cudaGetErrorString(e));
-    return L3CI_OK;
+    const cudaError_t e = c == 8 ? launch(top_p_step_kernel<8>) : c == 4 ? launch(top_p_step_kernel<4>) : launch(top_p_step_kernel<2>);
+    if (e == cudaSuccess) return L3CI_OK;
+    (void)cudaGetLastError();   // not placed: nothing ran
   }
   L3CI_LAUNCH("top_p_step_kernel", top_p_step_kernel<1>, dim3((unsigned)rows), dim3(kTopPBlock), 0, stream,
               lp, (long long)vocab, (long long)row_stride, inv_t, top_p, (unsigned long long)seed,
