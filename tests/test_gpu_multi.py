@@ -107,10 +107,11 @@ def _rank_main(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_gpu_sequence_sharding_and_batch_sharding():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world, port = 2, _free_port()
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sequence_sharding_and_batch_sharding_over_gpus(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
@@ -119,4 +120,4 @@ def test_two_gpu_sequence_sharding_and_batch_sharding():
     results = dict(q.get(timeout=300) for _ in range(world))
     for p in procs:
         p.join(timeout=60)
-    assert results == {0: "ok", 1: "ok"}, results
+    assert results == {r: "ok" for r in range(world)}, results
