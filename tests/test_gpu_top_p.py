@@ -121,7 +121,7 @@ def test_limits_greedy_and_whole_vocabulary(capi, device):
 
 
 @pytest.mark.parametrize("kind,vocab", [("normal", 128256), ("flat", 32003), ("two_levels", 128256), ("peaked", 1001),
-                                        ("one_hot", 4096)])
+                                        ("one_hot", 4096), ("normal", 37), ("flat", 8)])
 def test_several_ctas_per_row_change_no_bit(capi, device, kind, vocab):
     """Small batches run as a cluster of 8, 4 or 2 CTAs per row (up to 15, 33, 74 rows), larger ones with one CTA per
     row.  The draw is keyed by (seed, row, step) and all sums are integers, so the same rows give the same tokens,
